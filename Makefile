@@ -1,0 +1,50 @@
+# Builds the sm_100a library, the per-stage command-line programs and the oracle.
+#   make lib        ft_gemm_b200/lib/libft_gemm_b200.so   (C-ABI of include/ft_gemm.h)
+#   make cli        build/stage_abft_fp8_gemm, build/fault_campaign, build/cublaslt_fp8_bench
+#   make oracle     oracle/_build/libftq_oracle.so (CPU checker; test infrastructure)
+#   make fault_campaign FAULT_TRIALS=1000   (mirrors the reference Makefile's campaign target)
+NVCC      ?= nvcc
+ARCH      ?= -gencode arch=compute_100a,code=sm_100a
+NVCCFLAGS ?= -O3 -std=c++17 -lineinfo $(ARCH) -Xcompiler -fPIC -Xptxas -v
+CSRC      := ft_gemm_b200/csrc
+LIB       := ft_gemm_b200/lib/libft_gemm_b200.so
+OBJS      := build/obj/prepare.o build/obj/abft_gemm.o build/obj/api.o
+HDRS      := include/ft_gemm.h $(CSRC)/kernels.h $(CSRC)/sm100_ptx.cuh
+
+FAULT_TRIALS    ?= 100
+FAULT_MIN_VALUE ?= 1
+FAULT_MAX_VALUE ?= 256
+FAULT_SEED      ?= 12345
+FAULT_REL_TOL   ?= 0.00002
+
+all: lib cli oracle
+
+lib: $(LIB)
+
+build/obj/%.o: $(CSRC)/%.cu $(HDRS)
+	@mkdir -p build/obj
+	$(NVCC) $(NVCCFLAGS) -c -o $@ $<
+
+$(LIB): $(OBJS)
+	@mkdir -p ft_gemm_b200/lib
+	$(NVCC) $(ARCH) -shared -o $@ $(OBJS)
+
+cli: build/stage_abft_fp8_gemm build/fault_campaign
+
+build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(LIB)
+	$(NVCC) -O2 -std=c++17 -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+
+build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(LIB)
+	$(NVCC) -O2 -std=c++17 -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+
+oracle:
+	$(MAKE) -C oracle
+
+fault_campaign: build/fault_campaign
+	./build/fault_campaign --m 4096 --n 4096 --k 4096 --warmup 1 --repeat 1 --rel-tol $(FAULT_REL_TOL) \
+	  --fault-min-value $(FAULT_MIN_VALUE) --fault-max-value $(FAULT_MAX_VALUE) --fault-trials $(FAULT_TRIALS) --fault-seed $(FAULT_SEED)
+
+clean:
+	rm -rf build/obj
+
+.PHONY: all lib cli oracle fault_campaign clean

@@ -1,0 +1,9 @@
+"""B200-native fault-tolerant FP8 GEMM (ABFT) behind the C-ABI of include/ft_gemm.h."""
+from ._abi import (FT_ABFT_TILE, FT_ERR_CUDA, FT_ERR_INVALID, FT_ERR_TIMEOUT, FT_ERR_UNSUPPORTED, FT_MAX_FAULTS,
+                   FT_MAX_RECORDS, FT_OK, FtGemmError, LIB_PATH, load)
+from .operator import AbftGemm, HostAbftGemm, Report, TileRecord, generate_fp8
+from .sharding import RowShard, gather_reports, shard_rows
+
+__all__ = ["AbftGemm", "HostAbftGemm", "Report", "TileRecord", "generate_fp8", "RowShard", "shard_rows",
+           "gather_reports", "load", "LIB_PATH", "FtGemmError", "FT_OK", "FT_ERR_INVALID", "FT_ERR_CUDA",
+           "FT_ERR_TIMEOUT", "FT_ERR_UNSUPPORTED", "FT_ABFT_TILE", "FT_MAX_FAULTS", "FT_MAX_RECORDS"]

@@ -1,0 +1,409 @@
+// Fused FP8 GEMM + ABFT checker/corrector for sm_100a.
+//
+// Replaces the reference's wgmma_tma_k128_cluster_abft_kernel
+// (src/s4_cluster_multicast_abft_fp8_gemm.cu:301-519) with the same operator
+// semantics -- C[N,M] column-major = A[M,K] * B[N,K]^T in FP32, checked per 64x64
+// ABFT tile against cached expected row/column checksums, single faults located
+// at the (row, column) intersection and corrected by 0.5*(row_delta+col_delta)
+// (src/s4:432-503) -- on a different machine model:
+//
+//   * persistent CTAs, one per SM, each walking 128x256 output tiles;
+//   * warp 0: TMA producer, 4-stage ring of (128x128 A, 256x128 B) FP8 tiles with
+//     128-byte swizzle, mbarrier full/empty pairs;
+//   * warp 1: one thread issues tcgen05.mma kind::f8f6f4 (M128 N256 K32) from
+//     shared-memory descriptors into one of two 256-column TMEM accumulators;
+//   * warps 2-5: epilogue.  Each thread owns one accumulator row; per 64-column
+//     group it loads 64 values from TMEM into registers, forms the row sum
+//     serially, the column sums by a transpose-reduce butterfly of warp
+//     shuffles, exchanges them with its partner warp (the other 32 rows of the
+//     64-row ABFT tile), decides, corrects the faulty element in its registers and
+//     only then stores.  The epilogue of tile i runs while the main loop of tile
+//     i+1 fills the other accumulator.
+//
+// Every wait is bounded: on expiry the kernel sets report->status and leaves.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace ftg {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 128;  // FP8 elements = bytes = one 128-byte swizzle row
+constexpr int kUmmaK = 32;
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kBlockK;
+constexpr int kBBytes = kBlockN * kBlockK;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemColumns = 512;
+constexpr int kAccumulators = 2;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
+constexpr int kGroups = kBlockN / kGroupCols;
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
+constexpr int kTileGroupM = 16;  // m-blocks walked together so that concurrent tiles share A and B in L2
+
+struct RowInfo {
+  int count;
+  int first;
+  float delta;
+  int pad;
+};
+
+struct EpilogueScratch {
+  float colpart[2][kGroupCols];  // [warp half][column]: column sums over that warp's 32 rows
+  RowInfo rows[2];               // [warp half]
+};
+
+struct SharedTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[kAccumulators];
+  uint64_t tmem_empty[kAccumulators];
+  uint32_t tmem_base;
+  int abort_flag;
+  EpilogueScratch scratch[2][2];  // [row pair][parity]
+};
+
+constexpr int kSmemBytes = kStages * kStageBytes + static_cast<int>(sizeof(SharedTail)) + 1024;
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
+  int per_group = kTileGroupM * num_n;
+  int g = t / per_group;
+  int first_m = g * kTileGroupM;
+  int group_m = min(kTileGroupM, num_m - first_m);
+  int in_group = t - g * per_group;
+  mb = first_m + in_group % group_m;
+  nb = in_group / group_m;
+}
+
+__device__ __forceinline__ bool any_over_epilogue(bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, 3, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(flag))
+      : "memory");
+  return out != 0;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kABytes;
+  SharedTail& tail = *reinterpret_cast<SharedTail*>(smem + kStages * kStageBytes);
+  volatile int* abort_flag = &tail.abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = p.m / kBlockM;
+  const int num_n = p.n / kBlockN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = p.k / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&tail.full[s], 1);
+      mbar_init(&tail.empty[s], 1);
+    }
+    for (int a = 0; a < kAccumulators; ++a) {
+      mbar_init(&tail.tmem_full[a], 1);
+      mbar_init(&tail.tmem_empty[a], kEpilogueThreads);
+    }
+    tail.abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail.tmem_base, kTmemColumns);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tail.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, num_m, num_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, kWaitTimeoutNs)) {
+            alive = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&tail.full[s], kStageBytes);
+          tma_load_2d(smem_a + s * kABytes, &tmap_a, &tail.full[s], kb * kBlockK, mb * kBlockM);
+          tma_load_2d(smem_b + s * kBBytes, &tmap_b, &tail.full[s], kb * kBlockK, nb * kBlockN);
+          if (++s == kStages) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_e4m3_f32(kBlockM, kBlockN);
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        if (!mbar_wait_bounded(&tail.tmem_empty[acc], acc_phase ^ 1, abort_flag, kWaitTimeoutNs)) break;
+        tcgen05_fence_after();
+        uint32_t tmem_d = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&tail.full[s], phase, abort_flag, kWaitTimeoutNs)) {
+            alive = false;
+            break;
+          }
+          tcgen05_fence_after();
+          uint64_t desc_a = make_smem_desc_sw128(smem_u32(smem_a + s * kABytes));
+          uint64_t desc_b = make_smem_desc_sw128(smem_u32(smem_b + s * kBBytes));
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            // advancing K by 32 bytes inside the 128-byte swizzle row = +2 in the (address >> 4) field
+            umma_f8f6f4(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&tail.empty[s]);
+          if (++s == kStages) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (alive) umma_commit(&tail.tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int pair = quarter >> 1;  // which 64-row ABFT band of the 128-row tile
+    const int half = quarter & 1;   // which 32 rows of that band
+    const int r_local = half * 32 + lane;
+    const int tile_cols = p.n / kGroupCols;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    float max_ratio = 0.0f;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int mb, nb;
+      tile_coords(t, num_m, num_n, mb, nb);
+      bool ok = mbar_wait_bounded(&tail.tmem_full[acc], acc_phase, abort_flag, kWaitTimeoutNs);
+      if (any_over_epilogue(!ok)) break;
+      tcgen05_fence_after();
+      const int grow = mb * kBlockM + quarter * 32 + lane;
+      const int tile_row = mb * 2 + pair;
+#pragma unroll 1
+      for (int g = 0; g < kGroups; ++g) {
+        const int tile_id = tile_row * tile_cols + nb * kGroups + g;
+        const size_t cache = static_cast<size_t>(tile_id) * kGroupCols;
+        const float exp_row = __ldg(p.expected_rows + cache + r_local);
+        const float scale_row = __ldg(p.row_scales + cache + r_local);
+        const float exp_col0 = __ldg(p.expected_cols + cache + lane);
+        const float exp_col1 = __ldg(p.expected_cols + cache + 32 + lane);
+        const float scale_col0 = __ldg(p.col_scales + cache + lane);
+        const float scale_col1 = __ldg(p.col_scales + cache + 32 + lane);
+
+        float v[kGroupCols];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN + g * kGroupCols;
+        tmem_ld_32x32b_x32(taddr, v);
+        tmem_ld_32x32b_x32(taddr + 32, v + 32);
+        tmem_wait_ld();
+        if (g == kGroups - 1) {
+          // the accumulator is now entirely in registers: hand it back to the MMA warp
+          tcgen05_fence_before();
+          mbar_arrive(&tail.tmem_empty[acc]);
+        }
+
+        // test hook: faults enter the accumulator values before any checksum
+        if (p.faults.count > 0) {
+#pragma unroll
+          for (int f = 0; f < FT_MAX_FAULTS; ++f) {
+            if (f < p.faults.count && p.faults.tile[f] == tile_id) {
+              int fr = min(p.faults.row[f], kGroupCols - 1);
+              int fc = min(p.faults.col[f], kGroupCols - 1);
+              if (fr == r_local) {
+#pragma unroll
+                for (int c = 0; c < kGroupCols; ++c) {
+                  if (c == fc) v[c] += p.faults.value[f];
+                }
+              }
+            }
+          }
+        }
+
+        // actual row checksum: ascending columns, one accumulator (src/s4:458-464)
+        float row_sum = 0.0f;
+#pragma unroll
+        for (int c = 0; c < kGroupCols; ++c) row_sum += v[c];
+        const float row_delta = exp_row - row_sum;
+        const float row_thr = __fmaf_rn(p.rel_tol, fmaxf(1.0f, scale_row), p.abs_tol);
+        const bool row_bad = fabsf(row_delta) > row_thr;
+        if (!row_bad) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(row_delta), row_thr));
+
+        // column sums over this warp's 32 rows: transpose-reduce butterfly
+        float w[32];
+        {
+          const bool upper = (lane & 16) != 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float send = upper ? v[i] : v[i + 32];
+            float keep = upper ? v[i + 32] : v[i];
+            w[i] = keep + __shfl_xor_sync(0xffffffffU, send, 16);
+          }
+          int n = 16;
+#pragma unroll
+          for (int off = 8; off >= 1; off >>= 1) {
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < n; ++i) {
+              float send = up ? w[i] : w[i + n];
+              float keep = up ? w[i + n] : w[i];
+              w[i] = keep + __shfl_xor_sync(0xffffffffU, send, off);
+            }
+            n >>= 1;
+          }
+        }
+        // w[0], w[1] = sums of columns 2*lane, 2*lane+1 over 32 rows
+        EpilogueScratch& sc = tail.scratch[pair][g & 1];
+        *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(w[0], w[1]);
+        const uint32_t row_mask = __ballot_sync(0xffffffffU, row_bad);
+        const int first_lane = row_mask != 0 ? __ffs(row_mask) - 1 : 0;
+        const float first_delta = __shfl_sync(0xffffffffU, row_delta, first_lane);
+        if (lane == 0) {
+          sc.rows[half].count = __popc(row_mask);
+          sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
+          sc.rows[half].delta = first_delta;
+        }
+        if (pair == 0) {
+          named_barrier_sync<1, 64>();
+        } else {
+          named_barrier_sync<2, 64>();
+        }
+
+        // every warp of the pair checks all 64 columns (lane: columns lane, lane+32)
+        const float col_sum0 = sc.colpart[0][lane] + sc.colpart[1][lane];
+        const float col_sum1 = sc.colpart[0][32 + lane] + sc.colpart[1][32 + lane];
+        const float col_delta0 = exp_col0 - col_sum0;
+        const float col_delta1 = exp_col1 - col_sum1;
+        const float col_thr0 = __fmaf_rn(p.rel_tol, fmaxf(1.0f, scale_col0), p.abs_tol);
+        const float col_thr1 = __fmaf_rn(p.rel_tol, fmaxf(1.0f, scale_col1), p.abs_tol);
+        const bool col_bad0 = fabsf(col_delta0) > col_thr0;
+        const bool col_bad1 = fabsf(col_delta1) > col_thr1;
+        if (!col_bad0) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(col_delta0), col_thr0));
+        if (!col_bad1) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(col_delta1), col_thr1));
+        const uint32_t col_mask0 = __ballot_sync(0xffffffffU, col_bad0);
+        const uint32_t col_mask1 = __ballot_sync(0xffffffffU, col_bad1);
+        const int bad_rows = sc.rows[0].count + sc.rows[1].count;
+        const int bad_cols = __popc(col_mask0) + __popc(col_mask1);
+
+        if ((bad_rows | bad_cols) != 0) {  // uniform over the pair
+          const int bad_row = sc.rows[0].count != 0 ? sc.rows[0].first : sc.rows[1].first;
+          const float bad_row_delta = sc.rows[0].count != 0 ? sc.rows[0].delta : sc.rows[1].delta;
+          int bad_col = -1;
+          float bad_col_delta = 0.0f;
+          {
+            const float d0 = __shfl_sync(0xffffffffU, col_delta0, col_mask0 != 0 ? __ffs(col_mask0) - 1 : 0);
+            const float d1 = __shfl_sync(0xffffffffU, col_delta1, col_mask1 != 0 ? __ffs(col_mask1) - 1 : 0);
+            if (col_mask0 != 0) {
+              bad_col = __ffs(col_mask0) - 1;
+              bad_col_delta = d0;
+            } else if (col_mask1 != 0) {
+              bad_col = 32 + __ffs(col_mask1) - 1;
+              bad_col_delta = d1;
+            }
+          }
+          const bool correct = bad_rows == 1 && bad_cols == 1;
+          if (correct && r_local == bad_row) {
+            // src/s4:493-497: C[row,col] += 0.5 * (row_delta + col_delta), in registers
+            const float both = bad_row_delta + bad_col_delta;
+#pragma unroll
+            for (int c = 0; c < kGroupCols; ++c) {
+              if (c == bad_col) v[c] = __fmaf_rn(0.5f, both, v[c]);
+            }
+          }
+          if (half == 0 && lane == 0) {
+            atomicAdd(&p.report->bad_tiles, 1);
+            if (correct) {
+              atomicAdd(&p.report->corrected_tiles, 1);
+            } else {
+              atomicAdd(&p.report->multi_fault_tiles, 1);
+            }
+            int slot = atomicAdd(&p.report->record_count, 1);
+            if (slot < FT_MAX_RECORDS) {
+              ft_tile_record rec;
+              rec.tile = tile_id;
+              rec.bad_row_count = bad_rows;
+              rec.bad_col_count = bad_cols;
+              rec.bad_row = bad_rows != 0 ? bad_row : -1;
+              rec.bad_col = bad_col;
+              rec.row_delta = bad_rows != 0 ? bad_row_delta : 0.0f;
+              rec.col_delta = bad_col_delta;
+              rec.corrected = correct ? 1 : 0;
+              p.report->records[slot] = rec;
+            }
+          }
+        }
+
+        // C is column-major [N,M]: for a fixed column the 32 lanes write 32 consecutive floats
+        float* cptr = p.c + static_cast<size_t>(nb * kBlockN + g * kGroupCols) * p.m + grow;
+#pragma unroll
+        for (int c = 0; c < kGroupCols; ++c) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    // one atomic per warp for the clean-noise statistic
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) max_ratio = fmaxf(max_ratio, __shfl_xor_sync(0xffffffffU, max_ratio, off));
+    if (lane == 0) atomicMax(&p.report->max_clean_ratio_bits, __float_as_int(max_ratio));
+  }
+
+  // ------------------------------------------------------------------- teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if (tail.abort_flag != 0) {
+    if (threadIdx.x == 0) atomicExch(&p.report->status, 1);
+    // give copies and MMAs still in flight time to land before TMEM and smem go away
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemColumns);
+  }
+}
+
+int abft_gemm_smem_bytes() { return kSmemBytes; }
+
+cudaError_t configure_abft_gemm() {
+  return cudaFuncSetAttribute(abft_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid,
+                             cudaStream_t stream) {
+  abft_gemm_fp8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, params);
+  return cudaGetLastError();
+}
+
+}  // namespace ftg

@@ -1,0 +1,393 @@
+// C-ABI layer: handle, expected-checksum cache ownership, tensor maps, report.
+// See include/ft_gemm.h for the contract of each entry point and the reference
+// lines it replaces.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "kernels.h"
+
+using namespace ftg;
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  std::vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return code;
+}
+
+#define FT_CUDA(call)                                                                              \
+  do {                                                                                             \
+    cudaError_t err_ = (call);                                                                     \
+    if (err_ != cudaSuccess) return fail(FT_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(err_)); \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &query) == cudaSuccess &&
+        query == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  }
+  return fn;
+}
+
+// [rows, k] FP8, k contiguous; box = 128 bytes of k x box_rows rows, 128-byte swizzle.
+int make_operand_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return fail(FT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(k)};
+  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t elem[2] = {1u, 1u};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return FT_OK;
+}
+
+}  // namespace
+
+struct ft_gemm_handle {
+  int device = 0;
+  int m = 0, n = 0, k = 0;
+  int sm_count = 0;
+  int grid = 0;
+  ft_options options{};
+  const void* a = nullptr;
+  const void* b = nullptr;
+  // cache (one allocation)
+  float* cache_base = nullptr;
+  size_t cache_bytes = 0;
+  float *a_sums = nullptr, *a_mags = nullptr, *b_sums = nullptr, *b_mags = nullptr;
+  float *expected_rows = nullptr, *expected_cols = nullptr, *row_scales = nullptr, *col_scales = nullptr;
+  DeviceReport* report = nullptr;
+  CUtensorMap tmap_a{}, tmap_b{};
+  cudaEvent_t ev0 = nullptr, ev_mid = nullptr, ev1 = nullptr;
+  bool prepare_timed = false;
+  cudaStream_t last_stream = nullptr;
+  // device buffers owned by the host-buffer entry point
+  void* own_a = nullptr;
+  void* own_b = nullptr;
+  float* own_c = nullptr;
+  cudaStream_t own_stream = nullptr;
+};
+
+namespace {
+
+int check_shape(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0 || m % 128 != 0 || n % 256 != 0 || k % 128 != 0) {
+    return fail(FT_ERR_INVALID, "Invalid options. Require M%%128==0, N%%256==0, K%%128==0, and positive shape (got M=%d N=%d K=%d).",
+                m, n, k);
+  }
+  long long tiles = static_cast<long long>(m / 64) * (n / 64);
+  if (tiles * 64 > 0x7fffffffLL) return fail(FT_ERR_INVALID, "shape too large: %lld ABFT tiles", tiles);
+  return FT_OK;
+}
+
+int fill_cache(ft_gemm_handle* h, int which, cudaStream_t stream) {
+  const int band_rows_a = h->m / 64, band_rows_b = h->n / 64;
+  FT_CUDA(cudaEventRecord(h->ev0, stream));
+  if (which & 1) FT_CUDA(launch_band_sums(h->a, h->a_sums, h->a_mags, h->m, h->k, stream));
+  if (which & 2) FT_CUDA(launch_band_sums(h->b, h->b_sums, h->b_mags, h->n, h->k, stream));
+  FT_CUDA(cudaEventRecord(h->ev_mid, stream));
+  // expected_rows[(I,J),r] = sum_k A[64I+r,k] * b_sums[J,k]
+  FT_CUDA(launch_expected(h->a, h->b_sums, h->b_mags, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0, stream));
+  // expected_cols[(I,J),c] = sum_k a_sums[I,k] * B[64J+c,k]
+  FT_CUDA(launch_expected(h->b, h->a_sums, h->a_mags, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1, stream));
+  FT_CUDA(cudaEventRecord(h->ev1, stream));
+  h->prepare_timed = true;
+  h->last_stream = stream;
+  return FT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+void ft_options_default(ft_options* options) {
+  if (options == nullptr) return;
+  std::memset(options, 0, sizeof(*options));
+  options->abs_tol = 1.0e-2f;
+  options->rel_tol = 2.0e-5f;
+  options->sm_limit = 0;
+}
+
+const char* ft_gemm_last_error(void) { return g_error; }
+int ft_gemm_abi_version(void) { return 1; }
+
+int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void* b, int m, int n, int k, const ft_options* options,
+                             void* stream_ptr) {
+  if (handle == nullptr || a == nullptr || b == nullptr) return fail(FT_ERR_INVALID, "null handle or operand pointer");
+  *handle = nullptr;
+  int rc = check_shape(m, n, k);
+  if (rc != FT_OK) return rc;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) != 0 || (reinterpret_cast<uintptr_t>(b) & 15) != 0) {
+    return fail(FT_ERR_INVALID, "A and B must be 16-byte aligned");
+  }
+  ft_options opts;
+  ft_options_default(&opts);
+  if (options != nullptr) opts = *options;
+  if (opts.abs_tol < 0.0f || opts.rel_tol < 0.0f || opts.sm_limit < 0) return fail(FT_ERR_INVALID, "negative tolerance or sm_limit");
+
+  int device = 0;
+  FT_CUDA(cudaGetDevice(&device));
+  cudaDeviceProp prop;
+  FT_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    return fail(FT_ERR_UNSUPPORTED, "this library needs an sm_100 GPU (found sm_%d%d)", prop.major, prop.minor);
+  }
+  FT_CUDA(configure_abft_gemm());
+
+  ft_gemm_handle* h = new (std::nothrow) ft_gemm_handle();
+  if (h == nullptr) return fail(FT_ERR_INVALID, "out of host memory");
+  h->device = device;
+  h->m = m;
+  h->n = n;
+  h->k = k;
+  h->options = opts;
+  h->a = a;
+  h->b = b;
+  h->sm_count = prop.multiProcessorCount;
+  int tiles = (m / 128) * (n / 256);
+  h->grid = std::min(tiles, opts.sm_limit > 0 ? std::min(opts.sm_limit, h->sm_count) : h->sm_count);
+
+  size_t a_meta = static_cast<size_t>(m / 64) * k, b_meta = static_cast<size_t>(n / 64) * k;
+  size_t checks = static_cast<size_t>(m / 64) * (n / 64) * 64;
+  size_t floats = 2 * a_meta + 2 * b_meta + 4 * checks;
+  h->cache_bytes = floats * sizeof(float);
+  cudaError_t err = cudaMalloc(&h->cache_base, h->cache_bytes);
+  if (err == cudaSuccess) err = cudaMalloc(&h->report, sizeof(DeviceReport));
+  if (err == cudaSuccess) err = cudaEventCreate(&h->ev0);
+  if (err == cudaSuccess) err = cudaEventCreate(&h->ev_mid);
+  if (err == cudaSuccess) err = cudaEventCreate(&h->ev1);
+  if (err != cudaSuccess) {
+    ft_gemm_fp8_abft_destroy(h);
+    return fail(FT_ERR_CUDA, "allocating the expected-checksum cache (%zu bytes) failed: %s", h->cache_bytes,
+                cudaGetErrorString(err));
+  }
+  float* cursor = h->cache_base;
+  h->a_sums = cursor, cursor += a_meta;
+  h->a_mags = cursor, cursor += a_meta;
+  h->b_sums = cursor, cursor += b_meta;
+  h->b_mags = cursor, cursor += b_meta;
+  h->expected_rows = cursor, cursor += checks;
+  h->expected_cols = cursor, cursor += checks;
+  h->row_scales = cursor, cursor += checks;
+  h->col_scales = cursor, cursor += checks;
+
+  rc = make_operand_map(&h->tmap_a, a, m, k, 128);
+  if (rc == FT_OK) rc = make_operand_map(&h->tmap_b, b, n, k, 256);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (rc == FT_OK) {
+    cudaError_t merr = cudaMemsetAsync(h->report, 0, sizeof(DeviceReport), stream);
+    if (merr != cudaSuccess) rc = fail(FT_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(merr));
+  }
+  if (rc == FT_OK) rc = fill_cache(h, 3, stream);
+  if (rc != FT_OK) {
+    ft_gemm_fp8_abft_destroy(h);
+    return rc;
+  }
+  *handle = h;
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_refresh(ft_gemm_handle* h, int which, void* stream_ptr) {
+  if (h == nullptr || (which & 3) == 0) return fail(FT_ERR_INVALID, "null handle or empty refresh mask");
+  return fill_cache(h, which & 3, static_cast<cudaStream_t>(stream_ptr));
+}
+
+int ft_gemm_fp8_abft_set_tolerance(ft_gemm_handle* h, float abs_tol, float rel_tol) {
+  if (h == nullptr || abs_tol < 0.0f || rel_tol < 0.0f) return fail(FT_ERR_INVALID, "null handle or negative tolerance");
+  h->options.abs_tol = abs_tol;
+  h->options.rel_tol = rel_tol;
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_run(ft_gemm_handle* h, float* c, const ft_fault* faults, int n_faults, void* stream_ptr) {
+  if (h == nullptr || c == nullptr) return fail(FT_ERR_INVALID, "null handle or output pointer");
+  if (n_faults < 0 || n_faults > FT_MAX_FAULTS || (n_faults > 0 && faults == nullptr)) {
+    return fail(FT_ERR_INVALID, "n_faults must be in [0, %d]", FT_MAX_FAULTS);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  GemmParams params{};
+  params.expected_rows = h->expected_rows;
+  params.expected_cols = h->expected_cols;
+  params.row_scales = h->row_scales;
+  params.col_scales = h->col_scales;
+  params.c = c;
+  params.report = h->report;
+  params.m = h->m;
+  params.n = h->n;
+  params.k = h->k;
+  params.abs_tol = h->options.abs_tol;
+  params.rel_tol = h->options.rel_tol;
+  params.faults.count = n_faults;
+  int tile_count = (h->m / 64) * (h->n / 64);
+  for (int i = 0; i < n_faults; ++i) {
+    if (faults[i].tile < 0 || faults[i].tile >= tile_count || faults[i].row < 0 || faults[i].col < 0) {
+      return fail(FT_ERR_INVALID, "fault %d is outside the %d ABFT tiles", i, tile_count);
+    }
+    params.faults.tile[i] = faults[i].tile;
+    params.faults.row[i] = faults[i].row;
+    params.faults.col[i] = faults[i].col;
+    params.faults.value[i] = faults[i].value;
+  }
+  // one small memset in place of the reference's two counter memsets
+  FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
+  FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, stream));
+  h->last_stream = stream;
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_report(ft_gemm_handle* h, ft_report* out) {
+  if (h == nullptr || out == nullptr) return fail(FT_ERR_INVALID, "null handle or report pointer");
+  FT_CUDA(cudaStreamSynchronize(h->last_stream));
+  DeviceReport dev;
+  FT_CUDA(cudaMemcpy(&dev, h->report, sizeof(DeviceReport), cudaMemcpyDeviceToHost));
+  std::memset(out, 0, sizeof(*out));
+  out->status = dev.status != 0 ? FT_ERR_TIMEOUT : FT_OK;
+  out->bad_tiles = dev.bad_tiles;
+  out->corrected_tiles = dev.corrected_tiles;
+  out->multi_fault_tiles = dev.multi_fault_tiles;
+  int kept = std::min(dev.record_count, FT_MAX_RECORDS);
+  out->n_records = kept;
+  out->records_dropped = dev.record_count - kept;
+  std::memcpy(&out->max_clean_ratio, &dev.max_clean_ratio_bits, sizeof(float));
+  std::copy(dev.records, dev.records + kept, out->records);
+  std::sort(out->records, out->records + kept, [](const ft_tile_record& x, const ft_tile_record& y) { return x.tile < y.tile; });
+  if (h->prepare_timed) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, h->ev0, h->ev1) == cudaSuccess) out->prepare_ms = ms;
+    if (cudaEventElapsedTime(&ms, h->ev0, h->ev_mid) == cudaSuccess) out->prepare_input_ms = ms;
+    if (cudaEventElapsedTime(&ms, h->ev_mid, h->ev1) == cudaSuccess) out->prepare_expected_ms = ms;
+  }
+  if (dev.status != 0) return fail(FT_ERR_TIMEOUT, "a device-side wait expired; the output of this run is not valid");
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_cache(ft_gemm_handle* h, ft_cache_view* out) {
+  if (h == nullptr || out == nullptr) return fail(FT_ERR_INVALID, "null handle or view pointer");
+  out->a_sums = h->a_sums;
+  out->a_magnitudes = h->a_mags;
+  out->b_sums = h->b_sums;
+  out->b_magnitudes = h->b_mags;
+  out->expected_rows = h->expected_rows;
+  out->expected_cols = h->expected_cols;
+  out->row_scales = h->row_scales;
+  out->col_scales = h->col_scales;
+  out->bytes = h->cache_bytes;
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_destroy(ft_gemm_handle* h) {
+  if (h == nullptr) return FT_OK;
+  if (h->last_stream != nullptr || h->cache_base != nullptr) cudaStreamSynchronize(h->last_stream);
+  cudaFree(h->cache_base);
+  cudaFree(h->report);
+  if (h->ev0) cudaEventDestroy(h->ev0);
+  if (h->ev_mid) cudaEventDestroy(h->ev_mid);
+  if (h->ev1) cudaEventDestroy(h->ev1);
+  cudaFree(h->own_a);
+  cudaFree(h->own_b);
+  cudaFree(h->own_c);
+  if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  delete h;
+  return FT_OK;
+}
+
+int ft_gemm_generate_fp8(void* out, size_t count, uint32_t seed, int dist, float sigma, float post_scale, void* stream_ptr) {
+  if (out == nullptr && count > 0) return fail(FT_ERR_INVALID, "null output pointer");
+  if (dist != 0 && dist != 1) return fail(FT_ERR_INVALID, "dist must be 0 (uniform) or 1 (normal)");
+  FT_CUDA(launch_generate(out, count, seed, dist, sigma, post_scale, static_cast<cudaStream_t>(stream_ptr)));
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void* b_host, float* c_host, int m, int n, int k,
+                          const ft_options* options, const ft_fault* faults, int n_faults, int prepare, ft_report* report) {
+  if (a_host == nullptr || b_host == nullptr || c_host == nullptr || report == nullptr) {
+    return fail(FT_ERR_INVALID, "null host buffer or report pointer");
+  }
+  int rc = check_shape(m, n, k);
+  if (rc != FT_OK) return rc;
+  ft_gemm_handle* h = reuse != nullptr ? *reuse : nullptr;
+  size_t a_bytes = static_cast<size_t>(m) * k, b_bytes = static_cast<size_t>(n) * k, c_bytes = static_cast<size_t>(m) * n * 4;
+  bool fresh = h == nullptr;
+  if (!fresh && (h->m != m || h->n != n || h->k != k || h->own_a == nullptr)) {
+    return fail(FT_ERR_INVALID, "the handle passed for reuse was not created by this entry point with the same shape");
+  }
+  void *da = nullptr, *db = nullptr;
+  float* dc = nullptr;
+  cudaStream_t stream = nullptr;
+  if (fresh) {
+    FT_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    cudaError_t err = cudaMalloc(&da, a_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(&db, b_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&dc), c_bytes);
+    if (err != cudaSuccess) {
+      cudaFree(da);
+      cudaFree(db);
+      cudaFree(dc);
+      cudaStreamDestroy(stream);
+      return fail(FT_ERR_CUDA, "allocating device operands failed: %s", cudaGetErrorString(err));
+    }
+  } else {
+    da = h->own_a;
+    db = h->own_b;
+    dc = h->own_c;
+    stream = h->own_stream;
+  }
+  cudaError_t err = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream);
+  if (err == cudaSuccess) err = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream);
+  if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "host-to-device copy failed: %s", cudaGetErrorString(err));
+  if (rc == FT_OK && fresh) {
+    rc = ft_gemm_fp8_abft_prepare(&h, da, db, m, n, k, options, stream);
+    if (rc == FT_OK) {
+      h->own_a = da;
+      h->own_b = db;
+      h->own_c = dc;
+      h->own_stream = stream;
+    } else {
+      cudaFree(da);
+      cudaFree(db);
+      cudaFree(dc);
+      cudaStreamDestroy(stream);
+      return rc;
+    }
+  } else if (rc == FT_OK && prepare) {
+    rc = ft_gemm_fp8_abft_refresh(h, 3, stream);
+  }
+  if (rc == FT_OK) rc = ft_gemm_fp8_abft_run(h, dc, faults, n_faults, stream);
+  if (rc == FT_OK) {
+    err = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "device-to-host copy failed: %s", cudaGetErrorString(err));
+  }
+  int report_rc = ft_gemm_fp8_abft_report(h, report);
+  if (rc == FT_OK) rc = report_rc;
+  if (reuse != nullptr) {
+    *reuse = h;
+  } else {
+    ft_gemm_fp8_abft_destroy(h);
+  }
+  return rc;
+}
+
+}  // extern "C"

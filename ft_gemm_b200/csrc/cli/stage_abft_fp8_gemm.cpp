@@ -1,0 +1,105 @@
+// Per-stage program of the B200 ABFT FP8 GEMM.  Same command line, report keys
+// and exit code as the reference's final stage
+// (src/s4_cluster_multicast_abft_fp8_gemm.cu:132-173, 556-784): generate ->
+// prepare (timed) -> first call -> warm-up -> timed repeats -> sampled FP64
+// verification -> `key: value` report; exit 0 iff numerical_pass && abft_pass.
+// Everything on the GPU goes through the C-ABI of ft_gemm.h.
+#include "cli_common.h"
+
+int main(int argc, char** argv) {
+  ArgReader args{argc, argv};
+  CommonOptions o;
+  read_common(args, o);
+  float fault_value = args.get_float("--fault-value", 1.0f);
+  bool inject_fault = args.has_flag("--inject-fault");
+  if (args.has_flag("--help")) {
+    std::printf(
+        "Usage: %s [--m N --n N --k N --warmup N --repeat N]\n"
+        "       [--verify-samples N --verify-abs-tol X --verify-rel-tol X]\n"
+        "       [--abs-tol X --rel-tol X --fault-value X --inject-fault]\n"
+        "       [--dist uniform|normal|llm]\n"
+        "Constraints: M %% 128 == 0, N %% 256 == 0, and K %% 128 == 0.\n",
+        argv[0]);
+    return EXIT_SUCCESS;
+  }
+  if (!common_valid(o) || fault_value <= 0.0f) {
+    std::fprintf(stderr, "Invalid options. Require M%%128==0, N%%256==0, K%%128==0, and positive shape.\n");
+    return EXIT_FAILURE;
+  }
+  CLI_CUDA(cudaSetDevice(0));
+  size_t a_count = static_cast<size_t>(o.m) * o.k, b_count = static_cast<size_t>(o.n) * o.k, c_count = static_cast<size_t>(o.m) * o.n;
+  void *d_a = nullptr, *d_b = nullptr;
+  float* d_c = nullptr;
+  CLI_CUDA(cudaMalloc(&d_a, a_count));
+  CLI_CUDA(cudaMalloc(&d_b, b_count));
+  CLI_CUDA(cudaMalloc(reinterpret_cast<void**>(&d_c), c_count * sizeof(float)));
+  cudaStream_t stream;
+  CLI_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  generate_inputs(o, d_a, d_b, stream);
+  CLI_CUDA(cudaStreamSynchronize(stream));
+
+  ft_options options;
+  ft_options_default(&options);
+  options.abs_tol = o.abft_abs_tolerance;
+  options.rel_tol = o.abft_rel_tolerance;
+  ft_gemm_handle* handle = nullptr;
+  CLI_FT(ft_gemm_fp8_abft_prepare(&handle, d_a, d_b, o.m, o.n, o.k, &options, stream));
+  ft_report report;
+  CLI_FT(ft_gemm_fp8_abft_report(handle, &report));
+  float input_metadata_ms = report.prepare_input_ms, expected_metadata_ms = report.prepare_expected_ms;
+  float metadata_prepare_ms = input_metadata_ms + expected_metadata_ms;
+  ft_cache_view cache;
+  CLI_FT(ft_gemm_fp8_abft_cache(handle, &cache));
+
+  StageTimings timing = time_stage(handle, d_c, o, stream);
+
+  // the run whose output is verified: with the deterministic fault of the
+  // reference (value at local (32, 32) of ABFT tile tile_count/2, src/s4:449-453)
+  int tile_count = (o.m / 64) * (o.n / 64);
+  ft_fault fault{tile_count / 2, 32, 32, fault_value};
+  CLI_FT(ft_gemm_fp8_abft_run(handle, d_c, inject_fault ? &fault : nullptr, inject_fault ? 1 : 0, stream));
+  CLI_FT(ft_gemm_fp8_abft_report(handle, &report));
+
+  float first_call_total_ms = metadata_prepare_ms + timing.first_ms;
+  float amortized_ms = timing.average_ms + metadata_prepare_ms / o.repeat;
+  double operations = 2.0 * static_cast<double>(o.m) * o.n * o.k;
+  double tflops = operations / (timing.average_ms * 1.0e9);
+  double batched_tflops = operations / (timing.batched_average_ms * 1.0e9);
+  double first_call_tflops = operations / (first_call_total_ms * 1.0e9);
+  double amortized_tflops = operations / (amortized_ms * 1.0e9);
+  VerificationResult verification = verify_samples(d_a, d_b, d_c, o);
+  bool numerical_pass = o.verify_samples == 0 || verification.max_tolerance_ratio <= 1.0f;
+  bool abft_pass = inject_fault ? report.bad_tiles == 1 && report.corrected_tiles == 1 : report.bad_tiles == 0;
+  bool passed = numerical_pass && abft_pass;
+
+  print_common_header(o, "version", "B200 tcgen05 TMEM-epilogue ABFT FP8 GEMM");
+  std::printf("metadata_cache_bytes: %zu\n", cache.bytes);
+  std::printf("input_metadata_time_ms: %.6f\n", input_metadata_ms);
+  std::printf("expected_metadata_time_ms: %.6f\n", expected_metadata_ms);
+  std::printf("metadata_prepare_time_ms: %.6f\n", metadata_prepare_ms);
+  std::printf("first_fused_gemm_abft_time_ms: %.6f\n", timing.first_ms);
+  std::printf("first_call_total_ms: %.6f\n", first_call_total_ms);
+  std::printf("first_call_tflops: %.6f\n", first_call_tflops);
+  std::printf("avg_fused_gemm_abft_time_ms: %.6f\n", timing.average_ms);
+  std::printf("amortized_time_ms: %.6f\n", amortized_ms);
+  std::printf("amortized_tflops: %.6f\n", amortized_tflops);
+  std::printf("fused_gemm_tflops: %.6f\n", tflops);
+  std::printf("batched_avg_fused_gemm_abft_time_ms: %.6f\n", timing.batched_average_ms);
+  std::printf("batched_fused_gemm_tflops: %.6f\n", batched_tflops);
+  std::printf("abft_tolerance: abs=%.6e rel=%.6e\n", o.abft_abs_tolerance, o.abft_rel_tolerance);
+  std::printf("clean_checksum_noise_ratio: %.6e\n", report.max_clean_ratio);
+  std::printf("bad_tiles: %d\n", report.bad_tiles);
+  std::printf("corrected_tiles: %d\n", report.corrected_tiles);
+  std::printf("multi_fault_tiles: %d\n", report.multi_fault_tiles);
+  std::printf("verification_samples: %d\n", verification.checked);
+  std::printf("sampled_max_absolute_error: %.6e\n", verification.max_absolute_error);
+  std::printf("sampled_max_tolerance_ratio: %.6e\n", verification.max_tolerance_ratio);
+  std::printf("verification: %s\n", passed ? "PASS" : "FAIL");
+
+  CLI_FT(ft_gemm_fp8_abft_destroy(handle));
+  CLI_CUDA(cudaStreamDestroy(stream));
+  CLI_CUDA(cudaFree(d_a));
+  CLI_CUDA(cudaFree(d_b));
+  CLI_CUDA(cudaFree(d_c));
+  return passed ? 0 : 1;
+}

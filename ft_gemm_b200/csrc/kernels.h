@@ -1,0 +1,56 @@
+// Internal interface between the C-ABI layer and the kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ft_gemm.h"
+
+namespace ftg {
+
+// Device-side report of one run: counters first, then the per-tile records.
+struct DeviceReport {
+  int status;            // 0, or 1 when a bounded wait expired
+  int bad_tiles;
+  int corrected_tiles;
+  int multi_fault_tiles;
+  int record_count;      // records attempted (may exceed FT_MAX_RECORDS)
+  int max_clean_ratio_bits;  // float bits of max |delta|/threshold over passing checks
+  int pad[2];
+  ft_tile_record records[FT_MAX_RECORDS];
+};
+
+struct FaultParams {
+  int count;
+  int tile[FT_MAX_FAULTS];
+  int row[FT_MAX_FAULTS];
+  int col[FT_MAX_FAULTS];
+  float value[FT_MAX_FAULTS];
+};
+
+struct GemmParams {
+  const float* expected_rows;
+  const float* expected_cols;
+  const float* row_scales;
+  const float* col_scales;
+  float* c;
+  DeviceReport* report;
+  int m, n, k;
+  float abs_tol, rel_tol;
+  FaultParams faults;
+};
+
+cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, float sigma, float post_scale, cudaStream_t stream);
+cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, int k, cudaStream_t stream);
+cudaError_t launch_expected(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
+                            int nbands, int k, int mode, cudaStream_t stream);
+
+// Fused FP8 GEMM + ABFT checker/corrector.  tmap_a / tmap_b describe A[M,K] and
+// B[N,K] with 128-byte-swizzled boxes of (128 K-bytes x 128 rows) and
+// (128 K-bytes x 256 rows).
+cudaError_t configure_abft_gemm();
+cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid,
+                             cudaStream_t stream);
+int abft_gemm_smem_bytes();
+
+}  // namespace ftg

@@ -1,0 +1,230 @@
+// Expected-checksum cache and input generators.
+//
+// The cache is what the reference's S2-S4 programs compute once per (A, B) pair
+// with cache_input_tile_checksums_kernel and cache_expected_tile_checksums_kernel
+// (src/s4_cluster_multicast_abft_fp8_gemm.cu:194-294):
+//   a_sums[I,k]  = sum over the 64 rows of band I of A[.,k]      (+ |.| version)
+//   b_sums[J,k]  = sum over the 64 rows of band J of B[.,k]      (+ |.| version)
+//   expected_rows[(I,J),r] = sum_k A[64I+r,k] * b_sums[J,k],  row_scales with |.|
+//   expected_cols[(I,J),c] = sum_k a_sums[I,k] * B[64J+c,k],  col_scales with |.|
+// The kernels here read A and B with 16-byte loads and keep the reference's
+// summation order, so the cache is bit-identical to the reference's:
+//   band sums: one FP32 accumulator per k, rows added in ascending order;
+//   expected:  32 partial sums per checksum, partial l taking k = l, l+32, ...
+//              in ascending order with one fma per step, then the pairwise tree
+//              (l, l+16), (l, l+8), ..., (l, l+1) of a shuffle-down reduction.
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+
+namespace ftg {
+
+__device__ __forceinline__ uint32_t mix_u32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352dU;
+  x ^= x >> 15;
+  x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+
+__device__ __forceinline__ float fp8_to_float(uint8_t v) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(v), __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// ---------------------------------------------------------------------------
+// generators
+// ---------------------------------------------------------------------------
+__global__ void generate_fp8_kernel(uint8_t* out, size_t count, uint32_t seed, int dist, float sigma, float post_scale) {
+  size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (; index < count; index += stride) {
+    float value;
+    if (dist == 0) {
+      uint32_t bits = mix_u32(seed + static_cast<uint32_t>(index));
+      float unit = static_cast<float>(bits & 0x00ffffffU) / 16777216.0f;
+      value = 2.0f * unit - 1.0f;
+    } else {
+      uint32_t i2 = 2u * static_cast<uint32_t>(index);
+      uint32_t h1 = mix_u32(seed ^ i2);
+      uint32_t h2 = mix_u32(seed ^ (i2 + 1u));
+      float u1 = (static_cast<float>(h1 & 0x00ffffffU) + 1.0f) / 16777216.0f;
+      float u2 = static_cast<float>(h2 & 0x00ffffffU) / 16777216.0f;
+      float z = sqrtf(-2.0f * logf(u1)) * cosf(6.28318530717958647692f * u2);
+      value = z * sigma * post_scale;
+    }
+    out[index] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(value, __NV_SATFINITE, __NV_E4M3));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// band sums: x is [rows, k] FP8; one band = 64 consecutive rows.
+// grid (k / (16 * 128), bands), 128 threads; each thread owns 16 consecutive k.
+// ---------------------------------------------------------------------------
+constexpr int kBandThreads = 128;
+
+__global__ void __launch_bounds__(kBandThreads) band_sums_kernel(const uint8_t* __restrict__ x, float* __restrict__ sums,
+                                                                 float* __restrict__ mags, int k) {
+  int band = blockIdx.y;
+  int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 16;
+  if (k0 >= k) return;
+  const uint8_t* base = x + static_cast<size_t>(band) * 64 * k + k0;
+  float s[16], m[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s[i] = m[i] = 0.0f;
+#pragma unroll 8
+  for (int row = 0; row < 64; ++row) {
+    uint4 packed = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(row) * k));
+    uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        __half2_raw pair = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(words[w] >> (16 * h)), __NV_E4M3);
+        float2 f = __half22float2(__half2(pair));
+        s[w * 4 + h * 2 + 0] += f.x;
+        m[w * 4 + h * 2 + 0] += fabsf(f.x);
+        s[w * 4 + h * 2 + 1] += f.y;
+        m[w * 4 + h * 2 + 1] += fabsf(f.y);
+      }
+    }
+  }
+  float4* so = reinterpret_cast<float4*>(sums + static_cast<size_t>(band) * k + k0);
+  float4* mo = reinterpret_cast<float4*>(mags + static_cast<size_t>(band) * k + k0);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    so[q] = make_float4(s[4 * q], s[4 * q + 1], s[4 * q + 2], s[4 * q + 3]);
+    mo[q] = make_float4(m[4 * q], m[4 * q + 1], m[4 * q + 2], m[4 * q + 3]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// expected checksums.
+// x is [rows, k] FP8 (A for the row checksums, B for the column checksums);
+// band_sums / band_mags are the [nbands, k] sums of the OTHER operand.
+// A CTA covers 64 rows of x (8 warps x 8 rows) and 8 bands; lane l owns the
+// partial sums of k = l (mod 32).
+// mode 0 (x = A): out index = ((row/64) * nbands + band) * 64 + row % 64
+// mode 1 (x = B): out index = (band * (rows/64) + row/64) * 64 + row % 64
+// ---------------------------------------------------------------------------
+constexpr int kExpRows = 8;   // rows of x per warp
+constexpr int kExpBands = 8;  // bands per CTA
+
+template <int N>
+__device__ __forceinline__ void transpose_reduce(float (&v)[N], int lane) {
+  // After the call v[i], i < N/32, holds the sum over all 32 lanes of the
+  // original v[(N/32) * lane + i].  Lane pairs are combined as (l, l^16), then
+  // (l, l^8), ... (l, l^1): the same pairing as a shuffle-down tree read at lane 0.
+  int n = N / 2;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      float send = upper ? v[i] : v[i + n];
+      float keep = upper ? v[i + n] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffU, send, off);
+    }
+    n >>= 1;
+  }
+}
+
+__global__ void __launch_bounds__(256) expected_checksums_kernel(const uint8_t* __restrict__ x, const float* __restrict__ band_sums,
+                                                                 const float* __restrict__ band_mags, float* __restrict__ expected,
+                                                                 float* __restrict__ scales, int rows, int nbands, int k, int mode) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int row0 = blockIdx.x * 64 + warp * kExpRows;
+  int band0 = blockIdx.y * kExpBands;
+  const uint8_t* xr[kExpRows];
+#pragma unroll
+  for (int r = 0; r < kExpRows; ++r) xr[r] = x + static_cast<size_t>(row0 + r) * k;
+  const float* bs[kExpBands];
+  const float* bm[kExpBands];
+#pragma unroll
+  for (int j = 0; j < kExpBands; ++j) {
+    int band = min(band0 + j, nbands - 1);
+    bs[j] = band_sums + static_cast<size_t>(band) * k;
+    bm[j] = band_mags + static_cast<size_t>(band) * k;
+  }
+  // v[0..63]: expected partials [r*8+j]; v[64..127]: scale partials
+  float v[2 * kExpRows * kExpBands];
+#pragma unroll
+  for (int i = 0; i < 2 * kExpRows * kExpBands; ++i) v[i] = 0.0f;
+
+#pragma unroll 2
+  for (int kk = lane; kk < k; kk += 32) {
+    float av[kExpRows], sv[kExpBands], mv[kExpBands];
+#pragma unroll
+    for (int r = 0; r < kExpRows; ++r) av[r] = fp8_to_float(__ldg(xr[r] + kk));
+#pragma unroll
+    for (int j = 0; j < kExpBands; ++j) {
+      sv[j] = __ldg(bs[j] + kk);
+      mv[j] = __ldg(bm[j] + kk);
+    }
+#pragma unroll
+    for (int r = 0; r < kExpRows; ++r) {
+      float aabs = fabsf(av[r]);
+#pragma unroll
+      for (int j = 0; j < kExpBands; ++j) {
+        if (mode == 0) {
+          v[r * kExpBands + j] = __fmaf_rn(av[r], sv[j], v[r * kExpBands + j]);
+          v[64 + r * kExpBands + j] = __fmaf_rn(aabs, mv[j], v[64 + r * kExpBands + j]);
+        } else {
+          v[r * kExpBands + j] = __fmaf_rn(sv[j], av[r], v[r * kExpBands + j]);
+          v[64 + r * kExpBands + j] = __fmaf_rn(mv[j], aabs, v[64 + r * kExpBands + j]);
+        }
+      }
+    }
+  }
+  transpose_reduce<2 * kExpRows * kExpBands>(v, lane);
+  // lane holds original indices 4*lane + i
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int idx = 4 * lane + i;
+    int which = idx >> 6;
+    int r = (idx >> 3) & 7;
+    int j = idx & 7;
+    int band = band0 + j;
+    if (band < nbands) {
+      int row = row0 + r;
+      size_t tile = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band : static_cast<size_t>(band) * (rows >> 6) + (row >> 6);
+      size_t out = tile * 64 + (row & 63);
+      if (which == 0) {
+        expected[out] = v[i];
+      } else {
+        scales[out] = v[i];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host launchers
+// ---------------------------------------------------------------------------
+cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, float sigma, float post_scale, cudaStream_t stream) {
+  if (count == 0) return cudaSuccess;
+  size_t blocks = (count + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  generate_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<uint8_t*>(out), count, seed, dist, sigma,
+                                                                         post_scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, int k, cudaStream_t stream) {
+  dim3 grid((k / 16 + kBandThreads - 1) / kBandThreads, rows / 64);
+  band_sums_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const uint8_t*>(x), sums, mags, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_expected(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
+                            int nbands, int k, int mode, cudaStream_t stream) {
+  dim3 grid(rows / 64, (nbands + kExpBands - 1) / kExpBands);
+  expected_checksums_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), band_sums, band_mags, expected, scales, rows,
+                                                      nbands, k, mode);
+  return cudaGetLastError();
+}
+
+}  // namespace ftg

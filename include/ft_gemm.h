@@ -1,0 +1,167 @@
+/*
+ * ft_gemm.h -- C-ABI of the B200 fault-tolerant FP8 GEMM library.
+ *
+ * The reference project (chaiduo/FT-GEMM) has no library boundary: every stage is
+ * a standalone program whose main() owns the device buffers and launches the
+ * kernels in the fixed ABFT order  prepare expected checksums -> GEMM -> actual
+ * checksums -> compare -> single-point correct.  The entry points below are that
+ * kernel-launch interface made callable: each one cites the reference lines it
+ * replaces.  All pointers are plain device or host pointers, `stream` is a
+ * cudaStream_t passed as void* (NULL = the default stream); no function exits the
+ * process, traps or allocates behind the caller's back except where stated.
+ *
+ * Operator contract (same as the reference's S1-S4 programs,
+ * src/s4_cluster_multicast_abft_fp8_gemm.cu:744-745):
+ *   A  [M,K]  FP8 E4M3, K contiguous
+ *   B  [N,K]  FP8 E4M3, K contiguous
+ *   C  [N,M]  FP32 column-major: element (row r, column c) at C[c*M + r]
+ *   ABFT tiles are 64x64; tile_id = (r/64) * (N/64) + (c/64)
+ *   M % 128 == 0, N % 256 == 0, K % 128 == 0 (the reference's own constraint,
+ *   src/s4_cluster_multicast_abft_fp8_gemm.cu:163-169)
+ *
+ * Every function returns FT_OK (0) or a negative FT_ERR_* code; the text of the
+ * last error of the calling thread is available from ft_gemm_last_error().
+ * A handle may be used by one host thread at a time.
+ */
+#ifndef FT_GEMM_H
+#define FT_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FT_OK 0
+#define FT_ERR_INVALID (-1)   /* bad shape, pointer or option */
+#define FT_ERR_CUDA (-2)      /* a CUDA call failed; see ft_gemm_last_error() */
+#define FT_ERR_TIMEOUT (-3)   /* a device-side wait gave up; results are not valid */
+#define FT_ERR_UNSUPPORTED (-4) /* not an sm_100 device */
+
+#define FT_ABFT_TILE 64
+#define FT_MAX_FAULTS 4
+#define FT_MAX_RECORDS 64
+
+typedef struct ft_gemm_handle ft_gemm_handle;
+
+/* Options of the checker; defaults are the reference's
+ * (src/s4_cluster_multicast_abft_fp8_gemm.cu:98-99). */
+typedef struct {
+  float abs_tol;  /* default 1e-2 */
+  float rel_tol;  /* default 2e-5 */
+  int sm_limit;   /* 0 = one persistent CTA per SM; >0 caps the grid (testing) */
+  int reserved[5];
+} ft_options;
+
+/* A test fault: `value` is added to the accumulator element (row, col) of ABFT
+ * tile `tile` after the main loop and before the checksums
+ * (src/s4_random_fault_campaign.cu:321-322, 464-466; row and col are clamped to
+ * 63 like there). */
+typedef struct {
+  int tile;
+  int row;
+  int col;
+  float value;
+} ft_fault;
+
+/* One record per tile whose checker fired (src/s4:489-499 keeps only two global
+ * counters; the per-tile detail is what its shared-memory state holds). */
+typedef struct {
+  int tile;          /* ABFT tile id */
+  int bad_row_count; /* checksums over threshold */
+  int bad_col_count;
+  int bad_row;       /* lowest bad local row, -1 if none */
+  int bad_col;       /* lowest bad local column, -1 if none */
+  float row_delta;   /* expected - actual of bad_row */
+  float col_delta;   /* expected - actual of bad_col */
+  int corrected;     /* 1 iff exactly one row and one column were bad */
+} ft_tile_record;
+
+typedef struct {
+  int status;            /* FT_OK or FT_ERR_TIMEOUT */
+  int bad_tiles;         /* tiles with rows>0 || cols>0 (src/s4:490) */
+  int corrected_tiles;   /* tiles with rows==1 && cols==1 (src/s4:493-499) */
+  int multi_fault_tiles; /* bad but not corrected: reported, never silently fixed */
+  int n_records;         /* valid entries of records[], sorted by tile id */
+  int records_dropped;   /* bad tiles beyond FT_MAX_RECORDS */
+  float max_clean_ratio; /* max |delta| / threshold over checks that passed: the clean-run noise level */
+  float prepare_ms;      /* device time of the last prepare (band sums + expected checksums) */
+  float prepare_input_ms;    /* of which: band sums (the reference's input_metadata_time_ms) */
+  float prepare_expected_ms; /* of which: expected checksums (expected_metadata_time_ms) */
+  ft_tile_record records[FT_MAX_RECORDS];
+} ft_report;
+
+/* Pointers into the handle's expected-checksum cache (device memory, owned by
+ * the handle), laid out exactly as the reference's buffers
+ * (src/s4_cluster_multicast_abft_fp8_gemm.cu:584-598). */
+typedef struct {
+  const float* a_sums;        /* [M/64, K] */
+  const float* a_magnitudes;  /* [M/64, K] */
+  const float* b_sums;        /* [N/64, K] */
+  const float* b_magnitudes;  /* [N/64, K] */
+  const float* expected_rows; /* [tiles*64] */
+  const float* expected_cols; /* [tiles*64] */
+  const float* row_scales;    /* [tiles*64] */
+  const float* col_scales;    /* [tiles*64] */
+  size_t bytes;               /* total size of the eight arrays */
+} ft_cache_view;
+
+void ft_options_default(ft_options* options);
+
+/* Replaces the reference's cudaMalloc of the metadata buffers, its two prepare
+ * launches cache_input_tile_checksums_kernel + cache_expected_tile_checksums_kernel
+ * and its tensor-map construction (src/s4_cluster_multicast_abft_fp8_gemm.cu:
+ * 584-598, 608-617, 634-655).  Allocates the cache (freed by _destroy), fills it
+ * from A and B on `stream` and returns a handle bound to these A, B pointers.
+ * The cache is valid while the contents of A and B are unchanged. */
+int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a_e4m3, const void* b_e4m3, int m, int n, int k,
+                             const ft_options* options, void* stream);
+
+/* Recomputes the cache of an existing handle after A and/or B changed in place
+ * (same pointers, same shape).  which: bit 0 = A changed, bit 1 = B changed. */
+int ft_gemm_fp8_abft_refresh(ft_gemm_handle* handle, int which, void* stream);
+
+/* Replaces one enqueue_gemm() of the reference together with the two counter
+ * memsets in front of it (src/s4_cluster_multicast_abft_fp8_gemm.cu:657-672,
+ * 693-694): zeroes the handle's report and launches the fused GEMM + checker +
+ * corrector on `stream`.  Asynchronous.  `faults` may be NULL (n_faults = 0). */
+int ft_gemm_fp8_abft_run(ft_gemm_handle* handle, float* c, const ft_fault* faults, int n_faults, void* stream);
+
+/* Replaces the reference's read-back of bad_tiles / corrected_tiles
+ * (src/s4_cluster_multicast_abft_fp8_gemm.cu:711-714): waits for the stream of the
+ * last _run and copies its report to host memory.  Returns FT_ERR_TIMEOUT (and
+ * sets out->status) when a device-side wait gave up. */
+int ft_gemm_fp8_abft_report(ft_gemm_handle* handle, ft_report* out);
+
+/* Frees the cache (the reference's cudaFree block, src/s4:771-783). */
+int ft_gemm_fp8_abft_destroy(ft_gemm_handle* handle);
+
+int ft_gemm_fp8_abft_cache(ft_gemm_handle* handle, ft_cache_view* out);
+
+/* Tolerances can be changed between runs without re-preparing (they are kernel
+ * arguments in the reference, src/s4:306-307). */
+int ft_gemm_fp8_abft_set_tolerance(ft_gemm_handle* handle, float abs_tol, float rel_tol);
+
+/* The same operator with HOST buffers: copies A and B to the device, prepares
+ * (when `reuse` is NULL) or reuses the cache of *reuse, runs, copies C back and
+ * fills `report`.  a, b, c should be pinned for full copy bandwidth.  When
+ * `reuse` is non-NULL and *reuse is NULL a new handle with its own device
+ * buffers is created and returned there for later calls; destroy it with
+ * ft_gemm_fp8_abft_destroy. */
+int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void* b_host, float* c_host, int m, int n, int k,
+                          const ft_options* options, const ft_fault* faults, int n_faults, int prepare, ft_report* report);
+
+/* Seeded input generators on the device.  dist 0: the reference's
+ * E4M3(2u-1), u = (mix(seed+i) & 0xffffff) / 2^24
+ * (src/s0_tiled_abft_fp8_gemm.cu:93-110, bit-exact).  dist 1: E4M3(z * sigma *
+ * post_scale) with z ~ N(0,1) by Box-Muller over two hash draws. */
+int ft_gemm_generate_fp8(void* out_e4m3, size_t count, uint32_t seed, int dist, float sigma, float post_scale, void* stream);
+
+const char* ft_gemm_last_error(void);
+int ft_gemm_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,76 @@
+"""Generates the golden fixtures in this directory from the reference's OWN kernels.
+
+Needs a GPU and the harness binaries oracle/_ref/ref_harness_s0 and
+oracle/_ref/ref_harness_s4 (built by `make -C oracle ref` where the reference
+checkout is available; they compile the reference's .cu files in place and launch
+its kernels unmodified).  Usage, on a machine with a GPU:
+
+    python tests/golden/make_golden.py OUTDIR
+
+writes one .npz per case into OUTDIR; the committed fixtures were produced this
+way on a B200 and copied here.  Inputs are stored only for the smallest case of
+each family (they pin the generator); the larger cases store outputs and are
+checked against oracle-generated inputs.
+"""
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF = os.path.join(ROOT, "oracle", "_ref")
+
+S4_CASES = [(128, 256, 128, True), (64, 200, 96, True), (256, 512, 384, False), (128, 256, 1024, False)]
+S0_CASES = [(64, 64, 64, True), (40, 56, 48, True), (96, 80, 160, False)]
+S0_SCENARIOS = ("clean", "inject", "two_rc", "same_row", "cancel")
+
+
+def _read(path, dtype):
+    return np.fromfile(path, dtype=dtype)
+
+
+def run_s4(m, n, k, keep_inputs, outdir):
+    with tempfile.TemporaryDirectory() as tmp:
+        subprocess.run([os.path.join(REF, "ref_harness_s4"), str(m), str(n), str(k), tmp], check=True)
+        data = {name: _read(os.path.join(tmp, name + ".f32"), np.float32) for name in
+                ("a_sums", "a_mags", "b_sums", "b_mags", "expected_rows", "row_scales", "expected_cols", "col_scales")}
+        a = _read(os.path.join(tmp, "a.u8"), np.uint8)
+        b = _read(os.path.join(tmp, "b.u8"), np.uint8)
+        if keep_inputs:
+            data["a"], data["b"] = a, b
+        else:  # a short fingerprint instead of the bytes
+            data["a_head"], data["b_head"] = a[:256], b[:256]
+            data["a_sum"], data["b_sum"] = np.uint64(a.astype(np.uint64).sum()), np.uint64(b.astype(np.uint64).sum())
+        data["shape"] = np.array([m, n, k], dtype=np.int32)
+        np.savez_compressed(os.path.join(outdir, f"s4_prepare_{m}x{n}x{k}.npz"), **data)
+
+
+def run_s0(m, n, k, keep_inputs, outdir):
+    with tempfile.TemporaryDirectory() as tmp:
+        subprocess.run([os.path.join(REF, "ref_harness_s0"), str(m), str(n), str(k), tmp], check=True)
+        data = {name: _read(os.path.join(tmp, name + ".f32"), np.float32) for name in
+                ("c_gemm", "expected_rows", "expected_cols", "row_scales", "col_scales")}
+        for s in S0_SCENARIOS:
+            data["c_" + s] = _read(os.path.join(tmp, f"c_{s}.f32"), np.float32)
+            data["counters_" + s] = _read(os.path.join(tmp, f"counters_{s}.i32"), np.int32)
+        if keep_inputs:
+            data["a"] = _read(os.path.join(tmp, "a.u8"), np.uint8)
+            data["b"] = _read(os.path.join(tmp, "b.u8"), np.uint8)
+        data["shape"] = np.array([m, n, k], dtype=np.int32)
+        np.savez_compressed(os.path.join(outdir, f"s0_path_{m}x{n}x{k}.npz"), **data)
+
+
+def main():
+    outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    os.makedirs(outdir, exist_ok=True)
+    for case in S4_CASES:
+        run_s4(*case, outdir)
+    for case in S0_CASES:
+        run_s0(*case, outdir)
+    print("golden fixtures written to", outdir, sorted(os.listdir(outdir)))
+
+
+if __name__ == "__main__":
+    main()
