@@ -70,6 +70,7 @@ def load():
     lib.ft_gemm_fp8_abft_report.argtypes = [vp, ctypes.POINTER(FtReport)]
     lib.ft_gemm_fp8_abft_destroy.argtypes = [vp]
     lib.ft_gemm_fp8_abft_cache.argtypes = [vp, ctypes.POINTER(FtCacheView)]
+    lib.ft_gemm_fp8_abft_cache_read.argtypes = [vp, ci, vp, ctypes.c_size_t]
     lib.ft_gemm_fp8_abft_set_tolerance.argtypes = [vp, cf, cf]
     lib.ft_gemm_fp8_abft_host.argtypes = [ctypes.POINTER(vp), vp, vp, vp, ci, ci, ci, ctypes.POINTER(FtOptions),
                                           ctypes.POINTER(FtFault), ci, ci, ctypes.POINTER(FtReport)]
@@ -78,7 +79,8 @@ def load():
     lib.ft_gemm_last_error.restype = ctypes.c_char_p
     lib.ft_gemm_abi_version.argtypes = []
     for name in ("ft_gemm_fp8_abft_prepare", "ft_gemm_fp8_abft_refresh", "ft_gemm_fp8_abft_run", "ft_gemm_fp8_abft_report",
-                 "ft_gemm_fp8_abft_destroy", "ft_gemm_fp8_abft_cache", "ft_gemm_fp8_abft_set_tolerance",
+                 "ft_gemm_fp8_abft_destroy", "ft_gemm_fp8_abft_cache", "ft_gemm_fp8_abft_cache_read",
+                 "ft_gemm_fp8_abft_set_tolerance",
                  "ft_gemm_fp8_abft_host", "ft_gemm_generate_fp8", "ft_gemm_abi_version"):
         getattr(lib, name).restype = ci
     _lib = lib

@@ -298,6 +298,18 @@ int ft_gemm_fp8_abft_cache(ft_gemm_handle* h, ft_cache_view* out) {
   return FT_OK;
 }
 
+int ft_gemm_fp8_abft_cache_read(ft_gemm_handle* h, int which, float* host_out, size_t count) {
+  if (h == nullptr || host_out == nullptr || which < 0 || which > 7) return fail(FT_ERR_INVALID, "null pointer or bad array index");
+  const float* arrays[8] = {h->a_sums, h->a_mags, h->b_sums, h->b_mags, h->expected_rows, h->expected_cols, h->row_scales, h->col_scales};
+  size_t a_meta = static_cast<size_t>(h->m / 64) * h->k, b_meta = static_cast<size_t>(h->n / 64) * h->k;
+  size_t checks = static_cast<size_t>(h->m / 64) * (h->n / 64) * 64;
+  size_t sizes[8] = {a_meta, a_meta, b_meta, b_meta, checks, checks, checks, checks};
+  if (count > sizes[which]) return fail(FT_ERR_INVALID, "array %d holds %zu floats, %zu requested", which, sizes[which], count);
+  FT_CUDA(cudaStreamSynchronize(h->last_stream));
+  FT_CUDA(cudaMemcpy(host_out, arrays[which], count * sizeof(float), cudaMemcpyDeviceToHost));
+  return FT_OK;
+}
+
 int ft_gemm_fp8_abft_destroy(ft_gemm_handle* h) {
   if (h == nullptr) return FT_OK;
   if (h->last_stream != nullptr || h->cache_base != nullptr) cudaStreamSynchronize(h->last_stream);

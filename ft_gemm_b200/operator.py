@@ -150,14 +150,12 @@ class AbftGemm:
                   "expected_rows": (tiles, 64), "expected_cols": (tiles, 64), "row_scales": (tiles, 64),
                   "col_scales": (tiles, 64)}
         out = {}
-        torch.cuda.synchronize(self.a.device)
-        for name, shape in shapes.items():
-            count = shape[0] * shape[1]
-            host = torch.empty(count, dtype=torch.float32)
-            rc = torch.cuda.cudart().cudaMemcpy(host.data_ptr(), getattr(view, name), count * 4, 2)
-            if int(rc) != 0:
-                raise RuntimeError(f"cudaMemcpy of {name} failed: {rc}")
-            out[name] = host.reshape(shape)
+        for which, (name, shape) in enumerate(shapes.items()):
+            host = torch.empty(shape, dtype=torch.float32)
+            with torch.cuda.device(self.a.device):
+                _abi.check(self.lib.ft_gemm_fp8_abft_cache_read(self.handle, which, ctypes.c_void_p(host.data_ptr()),
+                                                                host.numel()))
+            out[name] = host
         return out
 
     def close(self):

@@ -139,6 +139,12 @@ int ft_gemm_fp8_abft_destroy(ft_gemm_handle* handle);
 
 int ft_gemm_fp8_abft_cache(ft_gemm_handle* handle, ft_cache_view* out);
 
+/* Inspection helper (the reference never reads its metadata back): waits for the
+ * handle's stream and copies `count` floats of one cache array to host memory.
+ * which: 0 a_sums, 1 a_magnitudes, 2 b_sums, 3 b_magnitudes, 4 expected_rows,
+ * 5 expected_cols, 6 row_scales, 7 col_scales. */
+int ft_gemm_fp8_abft_cache_read(ft_gemm_handle* handle, int which, float* host_out, size_t count);
+
 /* Tolerances can be changed between runs without re-preparing (they are kernel
  * arguments in the reference, src/s4:306-307). */
 int ft_gemm_fp8_abft_set_tolerance(ft_gemm_handle* handle, float abs_tol, float rel_tol);

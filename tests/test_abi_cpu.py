@@ -1,0 +1,81 @@
+"""CPU checks of the drop-in boundary: the shared library loads without a GPU,
+exports every symbol include/ft_gemm.h declares, and rejects bad arguments
+before touching CUDA.  No compute is launched here."""
+import ctypes
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "ft_gemm.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ft_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_north_star_entry_points():
+    names = declared_functions()
+    for required in ("ft_gemm_fp8_abft_prepare", "ft_gemm_fp8_abft_run", "ft_gemm_fp8_abft_report", "ft_gemm_fp8_abft_destroy"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in ft_gemm.h but not exported"
+    out = subprocess.run(["nm", "-D", "--defined-only", lib_path], capture_output=True, text=True, check=True).stdout
+    for name in declared_functions():
+        assert re.search(rf"\bT {name}\b", out), name
+
+
+def test_header_compiles_as_c(tmp_path):
+    src = tmp_path / "t.c"
+    src.write_text('#include "ft_gemm.h"\nint main(void){ft_options o; ft_report r; (void)o; (void)r; return FT_OK;}\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-c", str(src), "-o",
+                    str(tmp_path / "t.o")], check=True)
+
+
+def test_python_struct_sizes_match_the_header(tmp_path, lib_path):
+    src = tmp_path / "s.c"
+    src.write_text('#include <stdio.h>\n#include "ft_gemm.h"\nint main(void){printf("%zu %zu %zu %zu %zu\\n", sizeof(ft_options),'
+                   ' sizeof(ft_fault), sizeof(ft_tile_record), sizeof(ft_report), sizeof(ft_cache_view)); return 0;}\n')
+    exe = tmp_path / "s"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    sizes = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    from ft_gemm_b200 import _abi
+    assert sizes == [ctypes.sizeof(_abi.FtOptions), ctypes.sizeof(_abi.FtFault), ctypes.sizeof(_abi.FtTileRecord),
+                     ctypes.sizeof(_abi.FtReport), ctypes.sizeof(_abi.FtCacheView)]
+
+
+def test_argument_errors_without_a_gpu():
+    import ft_gemm_b200 as ftg
+    from ft_gemm_b200 import _abi
+    lib = ftg.load()
+    assert lib.ft_gemm_abi_version() == 1
+    opts = _abi.FtOptions()
+    lib.ft_options_default(ctypes.byref(opts))
+    assert opts.abs_tol == pytest.approx(1e-2) and opts.rel_tol == pytest.approx(2e-5)  # src/s4:98-99
+    handle = ctypes.c_void_p()
+    fake = ctypes.c_void_p(0x1000)
+    # the reference's shape rule (src/s4:163-169), checked before any CUDA call
+    for m, n, k in [(0, 256, 128), (64, 256, 128), (128, 128, 128), (128, 256, 64), (-128, 256, 128)]:
+        rc = lib.ft_gemm_fp8_abft_prepare(ctypes.byref(handle), fake, fake, m, n, k, None, None)
+        assert rc == ftg.FT_ERR_INVALID and b"M%128==0" in lib.ft_gemm_last_error()
+    assert lib.ft_gemm_fp8_abft_prepare(ctypes.byref(handle), None, fake, 128, 256, 128, None, None) == ftg.FT_ERR_INVALID
+    assert lib.ft_gemm_fp8_abft_run(None, fake, None, 0, None) == ftg.FT_ERR_INVALID
+    assert lib.ft_gemm_fp8_abft_report(None, None) == ftg.FT_ERR_INVALID
+    assert lib.ft_gemm_fp8_abft_destroy(None) == ftg.FT_OK
+    assert lib.ft_gemm_generate_fp8(fake, 16, 1, 7, 1.0, 1.0, None) == ftg.FT_ERR_INVALID
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from ft_gemm_b200 import _abi
+    monkeypatch.setattr(_abi, "_lib", None)
+    monkeypatch.setattr(_abi, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _abi.load()
