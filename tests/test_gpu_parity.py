@@ -155,7 +155,7 @@ def test_exhaustive_single_fault_sweep_one_tile(ftg, oracle):
     worst = 0.0
     for row in range(64):
         for col in range(64):
-            value = 1.0 + ((row * 64 + col) % 97) * (1.0 if (row + col) % 2 else -1.0)
+            value = (1.0 + (row * 64 + col) % 97) * (1.0 if (row + col) % 2 else -1.0)
             op.run(c, [(tile, row, col, value)])
             rep = op.report()
             assert (rep.bad_tiles, rep.corrected_tiles) == (1, 1), (row, col, rep)
