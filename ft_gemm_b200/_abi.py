@@ -74,6 +74,8 @@ def load():
     lib.ft_gemm_fp8_abft_set_tolerance.argtypes = [vp, cf, cf]
     lib.ft_gemm_fp8_abft_host.argtypes = [ctypes.POINTER(vp), vp, vp, vp, ci, ci, ci, ctypes.POINTER(FtOptions),
                                           ctypes.POINTER(FtFault), ci, ci, ctypes.POINTER(FtReport)]
+    lib.ft_gemm_fp8_abft_expected_noalloc.argtypes = [vp, vp, ci, ci, ci, vp, vp, vp, vp, vp]
+    lib.ft_gemm_fp8_abft_expected_noalloc.restype = ci
     lib.ft_gemm_generate_fp8.argtypes = [vp, ctypes.c_size_t, ctypes.c_uint32, ci, cf, cf, vp]
     lib.ft_gemm_last_error.argtypes = []
     lib.ft_gemm_last_error.restype = ctypes.c_char_p

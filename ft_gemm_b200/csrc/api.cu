@@ -26,6 +26,21 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+}  // namespace
+
+namespace ftg {
+// error reporting shared with the other translation units of the C-ABI
+int noalloc_fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  std::vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return code;
+}
+}  // namespace ftg
+
+namespace {
+
 #define FT_CUDA(call)                                                                              \
   do {                                                                                             \
     cudaError_t err_ = (call);                                                                     \

@@ -164,6 +164,26 @@ int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void
  * post_scale) with z ~ N(0,1) by Box-Muller over two hash draws. */
 int ft_gemm_generate_fp8(void* out_e4m3, size_t count, uint32_t seed, int dist, float sigma, float post_scale, void* stream);
 
+/* No counterpart in the reference (its programs allocate everything up front in
+ * main()).  Fills the four expected-checksum arrays for A[M,K], B[N,K] exactly as
+ * ft_gemm_fp8_abft_prepare does, but allocates nothing: the caller passes the
+ * outputs (each (M/64)*(N/64)*64 floats of device memory) and the intermediate
+ * band sums are kept in an array built into the library, 16 MiB on every GPU that
+ * loads it.  It exists for callers that cannot call cudaMalloc where they need
+ * new checksums -- a serving loop that refreshes them whenever A changes while
+ * the framework's allocator owns the device memory, or that cannot take the
+ * device-wide stall cudaMalloc causes.
+ *   - Shapes with 2*(M/64 + N/64)*K*4 bytes > FT_NOALLOC_MAX_SCRATCH_BYTES are
+ *     rejected with FT_ERR_INVALID (8192^3 fits exactly); use _prepare for them.
+ *   - The first call on each device looks the array's device address up (with
+ *     that device current); make that first call before any stream capture.
+ *   - All calls on a device share the array, which keeps the previous call's
+ *     contents: every used element is rewritten before it is read, but two calls
+ *     whose kernels overlap on the GPU (different streams) race on it. */
+#define FT_NOALLOC_MAX_SCRATCH_BYTES (16u << 20)
+int ft_gemm_fp8_abft_expected_noalloc(const void* a_e4m3, const void* b_e4m3, int m, int n, int k, float* expected_rows,
+                                      float* expected_cols, float* row_scales, float* col_scales, void* stream);
+
 const char* ft_gemm_last_error(void);
 int ft_gemm_abi_version(void);
 
