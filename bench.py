@@ -31,14 +31,18 @@ M_PER_RANK, N_DIM, K_DIM = 8192, 8192, 8192
 SEED_A, SEED_B = 0x12345678, 0x9ABCDEF0
 
 
-def _peaks():
+def _peaks(timed_seconds):
+    """FP8 tensor peak for the roofline.  MEASURED_PEAKS.json holds cuBLAS bf16 figures only; dense FP8 runs at twice
+    the bf16 rate on this part.  A timed region shorter than 0.1 s never reaches the power cap, so it is compared
+    with the burst figure; a longer one with the sustained figure."""
+    burst = timed_seconds < 0.1
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        # the denominators are measured for bf16; dense FP8 on this part runs at twice the bf16 rate
-        return 2.0 * float(p["bf16_tflops_sustained"]), "2 x measured sustained cuBLAS bf16 (MEASURED_PEAKS.json)"
-    return 2.0 * 1400.0, "2 x fallback sustained bf16 (1.4 PFLOP/s)"
+        key = "bf16_tflops" if burst else "bf16_tflops_sustained"
+        return 2.0 * float(p[key]), f"2 x measured cuBLAS bf16 {'burst' if burst else 'sustained'} (MEASURED_PEAKS.json {key}); of measured"
+    return 2.0 * (1590.0 if burst else 1400.0), f"2 x fallback bf16 {'burst 1.59' if burst else 'sustained 1.4'} PFLOP/s; of fallback"
 
 
 class ClockSampler:
@@ -261,7 +265,7 @@ def main():
             cublaslt = {"error": str(exc)[:160]}
 
     if rank == 0:
-        peak, peak_note = _peaks()
+        peak, peak_note = _peaks(elapsed_ms * 1e-3)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "fp8_e4m3 in, f32 accumulate", "data": "synthetic",

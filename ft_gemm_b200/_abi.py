@@ -21,7 +21,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libf
 
 class FtOptions(ctypes.Structure):
     _fields_ = [("abs_tol", ctypes.c_float), ("rel_tol", ctypes.c_float), ("sm_limit", ctypes.c_int),
-                ("reserved", ctypes.c_int * 5)]
+                ("single_cta", ctypes.c_int), ("reserved", ctypes.c_int * 4)]
 
 
 class FtFault(ctypes.Structure):
@@ -67,6 +67,8 @@ def load():
     lib.ft_gemm_fp8_abft_prepare.argtypes = [ctypes.POINTER(vp), vp, vp, ci, ci, ci, ctypes.POINTER(FtOptions), vp]
     lib.ft_gemm_fp8_abft_refresh.argtypes = [vp, ci, vp]
     lib.ft_gemm_fp8_abft_run.argtypes = [vp, vp, ctypes.POINTER(FtFault), ci, vp]
+    lib.ft_gemm_fp8_abft_run_profiled.argtypes = [vp, vp, vp, ci, ctypes.POINTER(ci), vp]
+    lib.ft_gemm_fp8_abft_run_profiled.restype = ci
     lib.ft_gemm_fp8_abft_report.argtypes = [vp, ctypes.POINTER(FtReport)]
     lib.ft_gemm_fp8_abft_destroy.argtypes = [vp]
     lib.ft_gemm_fp8_abft_cache.argtypes = [vp, ctypes.POINTER(FtCacheView)]

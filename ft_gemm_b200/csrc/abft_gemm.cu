@@ -7,11 +7,15 @@
 // at the (row, column) intersection and corrected by 0.5*(row_delta+col_delta)
 // (src/s4:432-503) -- on a different machine model:
 //
-//   * persistent CTAs, one per SM, each walking 128x256 output tiles;
-//   * warp 0: TMA producer, 4-stage ring of (128x128 A, 256x128 B) FP8 tiles with
-//     128-byte swizzle, mbarrier full/empty pairs;
-//   * warp 1: one thread issues tcgen05.mma kind::f8f6f4 (M128 N256 K32) from
-//     shared-memory descriptors into one of two 256-column TMEM accumulators;
+//   * persistent CTAs, one per SM, each owning 128 rows x 256 columns of an
+//     output tile.  In the pair form (kPair) two CTAs of a cluster share one
+//     256x256 tile: each stages its own 128 rows of A and HALF of the B tile, and
+//     the leader CTA issues one tcgen05.mma.cta_group::2 (M256 N256 K32) for
+//     both, which halves the shared-memory traffic per MMA;
+//   * warp 0: TMA producer, ring of (A, B) FP8 stages with 128-byte swizzle,
+//     mbarrier full/empty pairs;
+//   * warp 1: one thread issues tcgen05.mma kind::f8f6f4 from shared-memory
+//     descriptors into one of two 256-column TMEM accumulators;
 //   * warps 2-5: epilogue.  Each thread owns one accumulator row; per 64-column
 //     group it loads 64 values from TMEM into registers, forms the row sum
 //     serially, the column sums by a transpose-reduce butterfly of warp
@@ -30,14 +34,11 @@
 
 namespace ftg {
 
-constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
-constexpr int kBlockK = 128;  // FP8 elements = bytes = one 128-byte swizzle row
+constexpr int kBlockM = 128;   // rows of C per CTA
+constexpr int kBlockN = 256;   // columns of C per tile
+constexpr int kBlockK = 128;   // FP8 elements = bytes = one 128-byte swizzle row
 constexpr int kUmmaK = 32;
-constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockK;
-constexpr int kBBytes = kBlockN * kBlockK;
-constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemColumns = 512;
 constexpr int kAccumulators = 2;
 constexpr int kThreads = 192;
@@ -45,7 +46,19 @@ constexpr int kEpilogueThreads = 128;
 constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
 constexpr int kGroups = kBlockN / kGroupCols;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
-constexpr int kTileGroupM = 16;  // m-blocks walked together so that concurrent tiles share A and B in L2
+constexpr int kTileGroupRows = 2048;  // rows walked together so that concurrent tiles share A and B in L2
+constexpr int kMaxStages = 6;
+
+template <bool kPair>
+struct Config {
+  static constexpr int kBRows = kPair ? kBlockN / 2 : kBlockN;  // rows of B staged by one CTA
+  static constexpr int kBBytes = kBRows * kBlockK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = kPair ? 6 : 4;
+  static constexpr int kTileM = kPair ? 2 * kBlockM : kBlockM;  // rows of C per scheduled tile
+  static constexpr uint32_t kExpectTx = kPair ? 2 * kStageBytes : kStageBytes;
+  static constexpr uint32_t kEmptyArrivals = kPair ? 2 * kEpilogueThreads : kEpilogueThreads;
+};
 
 struct RowInfo {
   int count;
@@ -60,8 +73,8 @@ struct EpilogueScratch {
 };
 
 struct SharedTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[kAccumulators];
   uint64_t tmem_empty[kAccumulators];
   uint32_t tmem_base;
@@ -69,13 +82,17 @@ struct SharedTail {
   EpilogueScratch scratch[2][2];  // [row pair][parity]
 };
 
-constexpr int kSmemBytes = kStages * kStageBytes + static_cast<int>(sizeof(SharedTail)) + 1024;
+template <bool kPair>
+constexpr int smem_bytes() {
+  return Config<kPair>::kStages * Config<kPair>::kStageBytes + static_cast<int>(sizeof(SharedTail)) + 1024;
+}
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
-  int per_group = kTileGroupM * num_n;
+// tile index -> (row block of kTileM rows, column block of 256 columns)
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int group, int& mb, int& nb) {
+  int per_group = group * num_n;
   int g = t / per_group;
-  int first_m = g * kTileGroupM;
-  int group_m = min(kTileGroupM, num_m - first_m);
+  int first_m = g * group;
+  int group_m = min(group, num_m - first_m);
   int in_group = t - g * per_group;
   mb = first_m + in_group % group_m;
   nb = in_group / group_m;
@@ -94,31 +111,38 @@ __device__ __forceinline__ bool any_over_epilogue(bool flag) {
   return out != 0;
 }
 
+template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ GemmParams p) {
+  using Cfg = Config<kPair>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + kStages * kABytes;
-  SharedTail& tail = *reinterpret_cast<SharedTail*>(smem + kStages * kStageBytes);
+  uint8_t* smem_b = smem + Cfg::kStages * kABytes;
+  SharedTail& tail = *reinterpret_cast<SharedTail*>(smem + Cfg::kStages * Cfg::kStageBytes);
   volatile int* abort_flag = &tail.abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = p.m / kBlockM;
+  const uint32_t rank = kPair ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+  const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int num_m = p.m / Cfg::kTileM;
   const int num_n = p.n / kBlockN;
   const int num_tiles = num_m * num_n;
   const int num_kb = p.k / kBlockK;
+  constexpr int kGroupM = kTileGroupRows / Cfg::kTileM;
+  const bool profiling = p.profile != nullptr;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&tail.full[s], 1);
       mbar_init(&tail.empty[s], 1);
     }
     for (int a = 0; a < kAccumulators; ++a) {
       mbar_init(&tail.tmem_full[a], 1);
-      mbar_init(&tail.tmem_empty[a], kEpilogueThreads);
+      mbar_init(&tail.tmem_empty[a], Cfg::kEmptyArrivals);
     }
     tail.abort_flag = 0;
     fence_barrier_init();
@@ -126,11 +150,20 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     prefetch_tensormap(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(&tail.tmem_base, kTmemColumns);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(&tail.tmem_base, kTmemColumns);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&tail.tmem_base, kTmemColumns);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (kPair) {  // the peer's barriers must be initialised before anything remote touches them
+    cluster_arrive();
+    cluster_wait();
+  }
   tcgen05_fence_after();
   const uint32_t tmem_base = tail.tmem_base;
 
@@ -140,79 +173,130 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int s = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      long long waited = 0;
+      for (int t = worker; t < num_tiles && alive; t += workers) {
         int mb, nb;
-        tile_coords(t, num_m, num_n, mb, nb);
+        tile_coords(t, num_m, num_n, kGroupM, mb, nb);
+        const int a_row = mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM;
+        const int b_row = nb * kBlockN + static_cast<int>(rank) * Cfg::kBRows;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long t0 = profiling ? clock64() : 0;
           if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, kWaitTimeoutNs)) {
             alive = false;
             break;
           }
-          mbar_arrive_expect_tx(&tail.full[s], kStageBytes);
-          tma_load_2d(smem_a + s * kABytes, &tmap_a, &tail.full[s], kb * kBlockK, mb * kBlockM);
-          tma_load_2d(smem_b + s * kBBytes, &tmap_b, &tail.full[s], kb * kBlockK, nb * kBlockN);
-          if (++s == kStages) {
+          if (profiling) waited += clock64() - t0;
+          if (kPair) {
+            // both CTAs' bytes are counted on the leader's barrier
+            if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], Cfg::kExpectTx);
+            const uint32_t leader_full = map_to_cta(smem_u32(&tail.full[s]), 0);
+            tma_load_2d_pair(smem_a + s * kABytes, &tmap_a, leader_full, kb * kBlockK, a_row);
+            tma_load_2d_pair(smem_b + s * Cfg::kBBytes, &tmap_b, leader_full, kb * kBlockK, b_row);
+          } else {
+            mbar_arrive_expect_tx(&tail.full[s], Cfg::kExpectTx);
+            tma_load_2d(smem_a + s * kABytes, &tmap_a, &tail.full[s], kb * kBlockK, a_row);
+            tma_load_2d(smem_b + s * Cfg::kBBytes, &tmap_b, &tail.full[s], kb * kBlockK, b_row);
+          }
+          if (++s == Cfg::kStages) {
             s = 0;
             phase ^= 1;
           }
         }
       }
+      if (profiling) p.profile[blockIdx.x * 8 + 0] = waited;
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(kBlockM, kBlockN);
+    // ------------------------------------------------------------- MMA issuer (the leader only, in the pair form)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_e4m3_f32(Cfg::kTileM, kBlockN);
       int s = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      long long wait_full = 0, wait_tmem = 0;
+      const long long role_start = profiling ? clock64() : 0;
+      for (int t = worker; t < num_tiles && alive; t += workers) {
+        long long t0 = profiling ? clock64() : 0;
         if (!mbar_wait_bounded(&tail.tmem_empty[acc], acc_phase ^ 1, abort_flag, kWaitTimeoutNs)) break;
+        if (profiling) wait_tmem += clock64() - t0;
         tcgen05_fence_after();
         uint32_t tmem_d = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          t0 = profiling ? clock64() : 0;
           if (!mbar_wait_bounded(&tail.full[s], phase, abort_flag, kWaitTimeoutNs)) {
             alive = false;
             break;
           }
+          if (profiling) wait_full += clock64() - t0;
           tcgen05_fence_after();
           uint64_t desc_a = make_smem_desc_sw128(smem_u32(smem_a + s * kABytes));
-          uint64_t desc_b = make_smem_desc_sw128(smem_u32(smem_b + s * kBBytes));
+          uint64_t desc_b = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::kBBytes));
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             // advancing K by 32 bytes inside the 128-byte swizzle row = +2 in the (address >> 4) field
-            umma_f8f6f4(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+            if (kPair) {
+              umma_f8f6f4_pair(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+            } else {
+              umma_f8f6f4(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+            }
           }
-          umma_commit(&tail.empty[s]);
-          if (++s == kStages) {
+          if (kPair) {  // the stage is free in both CTAs once these MMAs have read it
+            umma_commit_pair(smem_u32(&tail.empty[s]));
+            umma_commit_pair(map_to_cta(smem_u32(&tail.empty[s]), 1));
+          } else {
+            umma_commit(&tail.empty[s]);
+          }
+          if (++s == Cfg::kStages) {
             s = 0;
             phase ^= 1;
           }
         }
-        if (alive) umma_commit(&tail.tmem_full[acc]);
+        if (alive) {
+          if (kPair) {
+            umma_commit_pair(smem_u32(&tail.tmem_full[acc]));
+            umma_commit_pair(map_to_cta(smem_u32(&tail.tmem_full[acc]), 1));
+          } else {
+            umma_commit(&tail.tmem_full[acc]);
+          }
+        }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
+      }
+      if (profiling) {
+        p.profile[blockIdx.x * 8 + 1] = wait_full;
+        p.profile[blockIdx.x * 8 + 2] = wait_tmem;
+        p.profile[blockIdx.x * 8 + 3] = clock64() - role_start;
       }
     }
   } else {
     // ------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    const int pair = quarter >> 1;  // which 64-row ABFT band of the 128-row tile
+    const int pair = quarter >> 1;  // which 64-row ABFT band of this CTA's 128 rows
     const int half = quarter & 1;   // which 32 rows of that band
     const int r_local = half * 32 + lane;
     const int tile_cols = p.n / kGroupCols;
     int acc = 0;
     uint32_t acc_phase = 0;
     float max_ratio = 0.0f;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    long long epi_wait = 0, tiles_done = 0;
+    const long long epi_start = profiling ? clock64() : 0;
+    for (int t = worker; t < num_tiles; t += workers) {
       int mb, nb;
-      tile_coords(t, num_m, num_n, mb, nb);
-      bool ok = mbar_wait_bounded(&tail.tmem_full[acc], acc_phase, abort_flag, kWaitTimeoutNs);
+      tile_coords(t, num_m, num_n, kGroupM, mb, nb);
+      const long long t0 = profiling ? clock64() : 0;
+      // one thread polls the barrier; the other 127 sleep in the hardware barrier below until it has seen the phase
+      bool ok = true;
+      if (warp == 2 && lane == 0) ok = mbar_wait_bounded(&tail.tmem_full[acc], acc_phase, abort_flag, kWaitTimeoutNs);
       if (any_over_epilogue(!ok)) break;
+      if (profiling) {
+        epi_wait += clock64() - t0;
+        ++tiles_done;
+      }
       tcgen05_fence_after();
-      const int grow = mb * kBlockM + quarter * 32 + lane;
-      const int tile_row = mb * 2 + pair;
+      const int row0 = mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM;  // first row of this CTA's part
+      const int grow = row0 + quarter * 32 + lane;
+      const int tile_row = row0 / kGroupCols + pair;
 #pragma unroll 1
       for (int g = 0; g < kGroups; ++g) {
         const int tile_id = tile_row * tile_cols + nb * kGroups + g;
@@ -230,9 +314,13 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
         if (g == kGroups - 1) {
-          // the accumulator is now entirely in registers: hand it back to the MMA warp
+          // the accumulator is now entirely in registers: hand it back to the MMA warp (of the leader)
           tcgen05_fence_before();
-          mbar_arrive(&tail.tmem_empty[acc]);
+          if (kPair) {
+            mbar_arrive_cluster(map_to_cta(smem_u32(&tail.tmem_empty[acc]), 0));
+          } else {
+            mbar_arrive(&tail.tmem_empty[acc]);
+          }
         }
 
         // test hook: faults enter the accumulator values before any checksum
@@ -317,7 +405,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int bad_rows = sc.rows[0].count + sc.rows[1].count;
         const int bad_cols = __popc(col_mask0) + __popc(col_mask1);
 
-        if ((bad_rows | bad_cols) != 0) {  // uniform over the pair
+        if ((bad_rows | bad_cols) != 0) {  // uniform over the pair of warps
           const int bad_row = sc.rows[0].count != 0 ? sc.rows[0].first : sc.rows[1].first;
           const float bad_row_delta = sc.rows[0].count != 0 ? sc.rows[0].delta : sc.rows[1].delta;
           int bad_col = -1;
@@ -377,6 +465,11 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) max_ratio = fmaxf(max_ratio, __shfl_xor_sync(0xffffffffU, max_ratio, off));
     if (lane == 0) atomicMax(&p.report->max_clean_ratio_bits, __float_as_int(max_ratio));
+    if (profiling && warp == 2 && lane == 0) {
+      p.profile[blockIdx.x * 8 + 4] = epi_wait;
+      p.profile[blockIdx.x * 8 + 5] = clock64() - epi_start;
+      p.profile[blockIdx.x * 8 + 6] = tiles_done;
+    }
   }
 
   // ------------------------------------------------------------------- teardown
@@ -388,22 +481,48 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
     __syncthreads();
   }
+  if (kPair) {  // neither CTA may leave while its partner can still reach its barriers or shared memory
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kTmemColumns);
+    if (kPair) {
+      tmem_dealloc_pair(tmem_base, kTmemColumns);
+    } else {
+      tmem_dealloc(tmem_base, kTmemColumns);
+    }
   }
 }
 
-int abft_gemm_smem_bytes() { return kSmemBytes; }
+int abft_gemm_smem_bytes(bool pair) { return pair ? smem_bytes<true>() : smem_bytes<false>(); }
 
 cudaError_t configure_abft_gemm() {
-  return cudaFuncSetAttribute(abft_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t err =
+      cudaFuncSetAttribute(abft_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<false>());
+  if (err != cudaSuccess) return err;
+  return cudaFuncSetAttribute(abft_gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<true>());
 }
 
-cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid,
+cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid, bool pair,
                              cudaStream_t stream) {
-  abft_gemm_fp8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, params);
-  return cudaGetLastError();
+  if (!pair) {
+    abft_gemm_fp8_kernel<false><<<grid, kThreads, smem_bytes<false>(), stream>>>(tmap_a, tmap_b, params);
+    return cudaGetLastError();
+  }
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 2;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = smem_bytes<true>();
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, abft_gemm_fp8_kernel<true>, tmap_a, tmap_b, params);
 }
 
 }  // namespace ftg

@@ -96,6 +96,7 @@ struct ft_gemm_handle {
   float *expected_rows = nullptr, *expected_cols = nullptr, *row_scales = nullptr, *col_scales = nullptr;
   DeviceReport* report = nullptr;
   CUtensorMap tmap_a{}, tmap_b{};
+  bool pair = false;  // 2-CTA form: clusters of two CTAs per 256x256 tile
   cudaEvent_t ev0 = nullptr, ev_mid = nullptr, ev1 = nullptr;
   bool prepare_timed = false;
   cudaStream_t last_stream = nullptr;
@@ -144,6 +145,7 @@ void ft_options_default(ft_options* options) {
   options->abs_tol = 1.0e-2f;
   options->rel_tol = 2.0e-5f;
   options->sm_limit = 0;
+  options->single_cta = 0;
 }
 
 const char* ft_gemm_last_error(void) { return g_error; }
@@ -182,8 +184,15 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   h->a = a;
   h->b = b;
   h->sm_count = prop.multiProcessorCount;
-  int tiles = (m / 128) * (n / 256);
-  h->grid = std::min(tiles, opts.sm_limit > 0 ? std::min(opts.sm_limit, h->sm_count) : h->sm_count);
+  h->pair = (m % 256 == 0) && opts.single_cta == 0;
+  int sm_cap = opts.sm_limit > 0 ? std::min(opts.sm_limit, h->sm_count) : h->sm_count;
+  if (h->pair) {
+    int tiles = (m / 256) * (n / 256);
+    h->grid = 2 * std::max(1, std::min(tiles, sm_cap / 2));
+  } else {
+    int tiles = (m / 128) * (n / 256);
+    h->grid = std::min(tiles, sm_cap);
+  }
 
   size_t a_meta = static_cast<size_t>(m / 64) * k, b_meta = static_cast<size_t>(n / 64) * k;
   size_t checks = static_cast<size_t>(m / 64) * (n / 64) * 64;
@@ -210,7 +219,7 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   h->col_scales = cursor, cursor += checks;
 
   rc = make_operand_map(&h->tmap_a, a, m, k, 128);
-  if (rc == FT_OK) rc = make_operand_map(&h->tmap_b, b, n, k, 256);
+  if (rc == FT_OK) rc = make_operand_map(&h->tmap_b, b, n, k, h->pair ? 128 : 256);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (rc == FT_OK) {
     cudaError_t merr = cudaMemsetAsync(h->report, 0, sizeof(DeviceReport), stream);
@@ -268,8 +277,41 @@ int ft_gemm_fp8_abft_run(ft_gemm_handle* h, float* c, const ft_fault* faults, in
   }
   // one small memset in place of the reference's two counter memsets
   FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
-  FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, stream));
+  FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, h->pair, stream));
   h->last_stream = stream;
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_run_profiled(ft_gemm_handle* h, float* c, unsigned long long* counters_host, int max_ctas, int* ctas,
+                                  void* stream_ptr) {
+  if (h == nullptr || c == nullptr || counters_host == nullptr || max_ctas <= 0) return fail(FT_ERR_INVALID, "null pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  unsigned long long* dev = nullptr;
+  size_t bytes = static_cast<size_t>(h->grid) * 8 * sizeof(unsigned long long);
+  FT_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), bytes));
+  FT_CUDA(cudaMemsetAsync(dev, 0, bytes, stream));
+  GemmParams params{};
+  params.expected_rows = h->expected_rows;
+  params.expected_cols = h->expected_cols;
+  params.row_scales = h->row_scales;
+  params.col_scales = h->col_scales;
+  params.c = c;
+  params.report = h->report;
+  params.m = h->m;
+  params.n = h->n;
+  params.k = h->k;
+  params.abs_tol = h->options.abs_tol;
+  params.rel_tol = h->options.rel_tol;
+  params.profile = dev;
+  cudaError_t err = cudaMemsetAsync(h->report, 0, 32, stream);
+  if (err == cudaSuccess) err = launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, h->pair, stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+  int n = std::min(h->grid, max_ctas);
+  if (err == cudaSuccess) err = cudaMemcpy(counters_host, dev, static_cast<size_t>(n) * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaFree(dev);
+  h->last_stream = stream;
+  if (ctas != nullptr) *ctas = h->grid;
+  if (err != cudaSuccess) return fail(FT_ERR_CUDA, "profiled run failed: %s", cudaGetErrorString(err));
   return FT_OK;
 }
 

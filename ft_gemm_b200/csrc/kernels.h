@@ -38,6 +38,10 @@ struct GemmParams {
   int m, n, k;
   float abs_tol, rel_tol;
   FaultParams faults;
+  // optional per-CTA cycle counters (8 x uint64 per CTA), nullptr in normal runs:
+  // [0] producer waiting for a free stage, [1] MMA waiting for a full stage, [2] MMA waiting for a drained
+  // accumulator, [3] MMA role total, [4] epilogue waiting for an accumulator, [5] epilogue total, [6] tiles, [7] spare
+  unsigned long long* profile;
 };
 
 cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, float sigma, float post_scale, cudaStream_t stream);
@@ -49,8 +53,10 @@ cudaError_t launch_expected(const void* x, const float* band_sums, const float* 
 // B[N,K] with 128-byte-swizzled boxes of (128 K-bytes x 128 rows) and
 // (128 K-bytes x 256 rows).
 cudaError_t configure_abft_gemm();
-cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid,
+// pair = true launches the 2-CTA form (clusters of two CTAs sharing a 256x256 tile;
+// tmap_b must then have a 128-row box, grid must be even and M a multiple of 256).
+cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid, bool pair,
                              cudaStream_t stream);
-int abft_gemm_smem_bytes();
+int abft_gemm_smem_bytes(bool pair);
 
 }  // namespace ftg

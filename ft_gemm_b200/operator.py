@@ -86,7 +86,7 @@ class AbftGemm:
     """Prepared ABFT FP8 GEMM for one (A[M,K], B[N,K]) pair of E4M3 tensors."""
 
     def __init__(self, a: torch.Tensor, b: torch.Tensor, abs_tol: float = 1.0e-2, rel_tol: float = 2.0e-5,
-                 sm_limit: int = 0, stream: Optional[torch.cuda.Stream] = None):
+                 sm_limit: int = 0, single_cta: bool = False, stream: Optional[torch.cuda.Stream] = None):
         _check_operand(a, "A")
         _check_operand(b, "B")
         if a.shape[1] != b.shape[1]:
@@ -98,6 +98,7 @@ class AbftGemm:
         options = _abi.FtOptions()
         self.lib.ft_options_default(ctypes.byref(options))
         options.abs_tol, options.rel_tol, options.sm_limit = abs_tol, rel_tol, sm_limit
+        options.single_cta = int(single_cta)
         self.handle = ctypes.c_void_p()
         with torch.cuda.device(a.device):
             _abi.check(self.lib.ft_gemm_fp8_abft_prepare(ctypes.byref(self.handle), ctypes.c_void_p(a.data_ptr()),
@@ -123,6 +124,16 @@ class AbftGemm:
         with torch.cuda.device(self.a.device):
             _abi.check(self.lib.ft_gemm_fp8_abft_run(self.handle, ctypes.c_void_p(c.data_ptr()), arr, count,
                                                      _stream_ptr(stream)))
+
+    def run_profiled(self, c: torch.Tensor):
+        """Runs once and returns a [ctas, 8] int64 tensor of per-role wait/total cycle counters (see ft_gemm.h)."""
+        out = torch.zeros((512, 8), dtype=torch.int64)
+        ctas = ctypes.c_int(0)
+        with torch.cuda.device(self.a.device):
+            _abi.check(self.lib.ft_gemm_fp8_abft_run_profiled(self.handle, ctypes.c_void_p(c.data_ptr()),
+                                                              ctypes.c_void_p(out.data_ptr()), 512, ctypes.byref(ctas),
+                                                              _stream_ptr(None)))
+        return out[:ctas.value]
 
     def refresh(self, a_changed: bool = True, b_changed: bool = True, stream: Optional[torch.cuda.Stream] = None):
         with torch.cuda.device(self.a.device):

@@ -51,7 +51,8 @@ typedef struct {
   float abs_tol;  /* default 1e-2 */
   float rel_tol;  /* default 2e-5 */
   int sm_limit;   /* 0 = one persistent CTA per SM; >0 caps the grid (testing) */
-  int reserved[5];
+  int single_cta; /* 0 = pair two CTAs on one 256x256 tile when M % 256 == 0; 1 = always one CTA per 128x256 tile */
+  int reserved[4];
 } ft_options;
 
 /* A test fault: `value` is added to the accumulator element (row, col) of ABFT
@@ -127,6 +128,16 @@ int ft_gemm_fp8_abft_refresh(ft_gemm_handle* handle, int which, void* stream);
  * 693-694): zeroes the handle's report and launches the fused GEMM + checker +
  * corrector on `stream`.  Asynchronous.  `faults` may be NULL (n_faults = 0). */
 int ft_gemm_fp8_abft_run(ft_gemm_handle* handle, float* c, const ft_fault* faults, int n_faults, void* stream);
+
+/* Diagnostic variant of _run without faults: additionally records, per CTA, how
+ * many clock cycles each role spent waiting (8 counters per CTA: producer waiting
+ * for a free stage, MMA waiting for a full stage, MMA waiting for a drained
+ * accumulator, MMA role total, epilogue waiting for an accumulator, epilogue
+ * total, tiles processed, spare).  Synchronous; `counters_host` receives
+ * min(ctas, max_ctas) * 8 values and *ctas the grid size.  The reference has no
+ * such hook; its timing is event-based only (src/s4:692-702). */
+int ft_gemm_fp8_abft_run_profiled(ft_gemm_handle* handle, float* c, unsigned long long* counters_host, int max_ctas, int* ctas,
+                                  void* stream);
 
 /* Replaces the reference's read-back of bad_tiles / corrected_tiles
  * (src/s4_cluster_multicast_abft_fp8_gemm.cu:711-714): waits for the stream of the
