@@ -29,13 +29,16 @@ $(LIB): $(OBJS)
 	@mkdir -p ft_gemm_b200/lib
 	$(NVCC) $(ARCH) -shared -o $@ $(OBJS)
 
-cli: build/stage_abft_fp8_gemm build/fault_campaign
+cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench
 
 build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(LIB)
-	$(NVCC) -O2 -std=c++17 -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(LIB)
-	$(NVCC) -O2 -std=c++17 -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+
+build/cublaslt_fp8_bench: $(CSRC)/cli/cublaslt_fp8_bench.cpp $(CSRC)/cli/cli_common.h $(LIB)
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -lcublasLt -lcublas -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 oracle:
 	$(MAKE) -C oracle

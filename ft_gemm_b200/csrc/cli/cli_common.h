@@ -212,10 +212,12 @@ inline void print_common_header(const CommonOptions& o, const char* version_key,
   int tile_count = (o.m / 64) * (o.n / 64);
   int cta_tiles = (o.m / 128) * (o.n / 256);
   std::printf("%s: %s\n", version_key, version);
-  std::printf("instruction_tile: 128x256x32, cta_tile: 128x256x128, tma_stage_k: 128, stages: 4\n");
+  bool pair = o.m % 256 == 0;
+  std::printf("instruction_tile: %s, cta_tile: 128x256x128, tma_stage_k: 128, stages: %d\n", pair ? "256x256x32 (2 CTAs)" : "128x256x32",
+              pair ? 6 : 4);
   std::printf("threads_per_cta: 192, producer_warps: 1, mma_warps: 1, epilogue_warps: 4, tmem_accumulators: 2\n");
   std::printf("pipeline: TMA producer || tcgen05.mma issuer || TMEM epilogue with fused ABFT verifier (persistent)\n");
   std::printf("layout: A=[M,K] row-major, B=[N,K] column-major, C=[N,M] column-major\n");
   std::printf("shape: M=%d N=%d K=%d, abft_tiles=%d, cta_tiles=%d\n", o.m, o.n, o.k, tile_count, cta_tiles);
-  std::printf("cluster_shape: 1x1x1, input_distribution: %s\n", o.dist.c_str());
+  std::printf("cluster_shape: %s, input_distribution: %s\n", pair ? "2x1x1" : "1x1x1", o.dist.c_str());
 }
