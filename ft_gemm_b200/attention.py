@@ -1,0 +1,138 @@
+"""Host-side mirror of the reference's fault-tolerant attention operator.
+
+The reference's attention programs prepare K/V metadata, launch the fused forward
+with a fault description and read nine counters back
+(src/ft_flash_attention_a14.cu:1363-1519).  `FtAttention` is that sequence over
+the C-ABI of include/ft_attention.h; torch only supplies device memory and the
+stream handle.
+"""
+import ctypes
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _abi
+from .operator import TileRecord, _stream_ptr
+
+FAULT_NONE, FAULT_SCORE, FAULT_OUTPUT = 0, 1, 4
+
+
+class FtAttnOptions(ctypes.Structure):
+    _fields_ = [("score_abs_tol", ctypes.c_float), ("score_rel_tol", ctypes.c_float), ("pv_abs_tol", ctypes.c_float),
+                ("pv_rel_tol", ctypes.c_float), ("reserved", ctypes.c_int * 4)]
+
+
+class FtAttnFault(ctypes.Structure):
+    _fields_ = [("stage", ctypes.c_int), ("batch", ctypes.c_int), ("head", ctypes.c_int), ("query", ctypes.c_int),
+                ("index", ctypes.c_int), ("value", ctypes.c_float)]
+
+
+class FtAttnReport(ctypes.Structure):
+    _fields_ = [("status", ctypes.c_int), ("score_detected", ctypes.c_int), ("score_corrected", ctypes.c_int),
+                ("score_uncorrected", ctypes.c_int), ("pv_detected", ctypes.c_int), ("pv_corrected", ctypes.c_int),
+                ("failed_rows", ctypes.c_int), ("n_records", ctypes.c_int), ("max_score_noise", ctypes.c_float),
+                ("prepare_ms", ctypes.c_float), ("records", _abi.FtTileRecord * 16)]
+
+
+@dataclass
+class AttnReport:
+    status: int
+    score_detected: int
+    score_corrected: int
+    score_uncorrected: int
+    pv_detected: int
+    pv_corrected: int
+    failed_rows: int
+    max_score_noise: float
+    prepare_ms: float
+    records: List[TileRecord] = field(default_factory=list)
+
+
+_bound = False
+
+
+def _lib():
+    global _bound
+    lib = _abi.load()
+    if not _bound:
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        lib.ft_attn_options_default.argtypes = [ctypes.POINTER(FtAttnOptions)]
+        lib.ft_attn_options_default.restype = None
+        lib.ft_attention_fp16_abft_prepare.argtypes = [ctypes.POINTER(vp), vp, vp, vp, ci, ci, ci, ci,
+                                                       ctypes.POINTER(FtAttnOptions), vp]
+        lib.ft_attention_fp16_abft_run.argtypes = [vp, vp, ctypes.POINTER(FtAttnFault), vp]
+        lib.ft_attention_fp16_abft_report.argtypes = [vp, ctypes.POINTER(FtAttnReport)]
+        lib.ft_attention_fp16_abft_destroy.argtypes = [vp]
+        for name in ("ft_attention_fp16_abft_prepare", "ft_attention_fp16_abft_run", "ft_attention_fp16_abft_report",
+                     "ft_attention_fp16_abft_destroy"):
+            getattr(lib, name).restype = ci
+        _bound = True
+    return lib
+
+
+def shard_heads(batch_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    """(first, count) of the (batch, head) pairs rank `rank` owns: attention shards by heads, nothing is exchanged
+    except the counters."""
+    base, extra = divmod(batch_heads, world)
+    count = base + (1 if rank < extra else 0)
+    return rank * base + min(rank, extra), count
+
+
+class FtAttention:
+    """Prepared fault-tolerant attention forward for one (Q, K, V) triple of [B, H, N, D] FP16 tensors."""
+
+    def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, score_abs_tol: float = 1.0e-2,
+                 score_rel_tol: float = 2.0e-5, pv_abs_tol: float = 2.0e-3, pv_rel_tol: float = 2.0e-3,
+                 stream: Optional[torch.cuda.Stream] = None):
+        for t, name in ((q, "Q"), (k, "K"), (v, "V")):
+            if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 4 or not t.is_contiguous() or t.shape != q.shape:
+                raise ValueError(f"{name} must be a contiguous [B, H, N, D] float16 CUDA tensor of the same shape as Q")
+        self.lib = _lib()
+        self.q, self.k, self.v = q, k, v
+        self.batch, self.heads, self.seq, self.dim = q.shape
+        options = FtAttnOptions()
+        self.lib.ft_attn_options_default(ctypes.byref(options))
+        options.score_abs_tol, options.score_rel_tol = score_abs_tol, score_rel_tol
+        options.pv_abs_tol, options.pv_rel_tol = pv_abs_tol, pv_rel_tol
+        self.handle = ctypes.c_void_p()
+        with torch.cuda.device(q.device):
+            _abi.check(self.lib.ft_attention_fp16_abft_prepare(
+                ctypes.byref(self.handle), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                ctypes.c_void_p(v.data_ptr()), self.batch, self.heads, self.seq, self.dim, ctypes.byref(options),
+                _stream_ptr(stream)))
+
+    def new_output(self) -> torch.Tensor:
+        return torch.empty(self.q.shape, dtype=torch.float32, device=self.q.device)
+
+    def run(self, out: torch.Tensor, fault: Optional[Tuple[int, int, int, int, int, float]] = None,
+            stream: Optional[torch.cuda.Stream] = None):
+        """fault = (stage, batch, head, query, index, value) with the reference's stage numbers (1 score, 4 output)."""
+        if not out.is_cuda or out.dtype != torch.float32 or not out.is_contiguous() or out.shape != self.q.shape:
+            raise ValueError("out must be a contiguous float32 CUDA tensor shaped like Q")
+        cf = FtAttnFault(*fault) if fault is not None else None
+        with torch.cuda.device(self.q.device):
+            _abi.check(self.lib.ft_attention_fp16_abft_run(self.handle, ctypes.c_void_p(out.data_ptr()),
+                                                           ctypes.byref(cf) if cf is not None else None, _stream_ptr(stream)))
+
+    def report(self, allow_timeout: bool = False) -> AttnReport:
+        rep = FtAttnReport()
+        with torch.cuda.device(self.q.device):
+            code = self.lib.ft_attention_fp16_abft_report(self.handle, ctypes.byref(rep))
+        if code != _abi.FT_OK and not (allow_timeout and code == _abi.FT_ERR_TIMEOUT):
+            _abi.check(code)
+        records = [TileRecord(r.tile, r.bad_row_count, r.bad_col_count, r.bad_row, r.bad_col, r.row_delta, r.col_delta,
+                              r.corrected) for r in rep.records[:rep.n_records]]
+        return AttnReport(rep.status, rep.score_detected, rep.score_corrected, rep.score_uncorrected, rep.pv_detected,
+                          rep.pv_corrected, rep.failed_rows, rep.max_score_noise, rep.prepare_ms, records)
+
+    def close(self):
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            self.lib.ft_attention_fp16_abft_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

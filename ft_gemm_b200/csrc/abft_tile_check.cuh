@@ -1,0 +1,140 @@
+// The 64x64 ABFT tile verifier shared by the kernels that hold an accumulator
+// tile in registers after a TMEM load (one thread = one row, 64 columns): the
+// checker of the reference's epilogue (src/s4_cluster_multicast_abft_fp8_gemm.cu:
+// 456-499) in register form.
+//
+//   row checksum    serial sum of the thread's 64 values (the reference's order)
+//   column checksum transpose-reduce butterfly over the warp's 32 rows, combined
+//                   with the partner warp (the other 32 rows of the tile) through
+//                   shared memory and one 64-thread named barrier
+//   decision        bad <=> |expected - actual| > abs + rel * max(1, scale)
+//   correction      iff exactly one bad row and one bad column:
+//                   v[row][col] += 0.5 * (row_delta + col_delta), in registers
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+
+namespace ftg {
+
+struct TileRowInfo {
+  int count;
+  int first;
+  float delta;
+  int pad;
+};
+
+struct TileScratch {
+  float colpart[2][64];  // [warp half][column]: column sums over that warp's 32 rows
+  TileRowInfo rows[2];   // [warp half]
+};
+
+struct TileDecision {
+  int bad_rows;
+  int bad_cols;
+  int bad_row;  // lowest bad local row (0..63), -1 if none
+  int bad_col;
+  float row_delta;
+  float col_delta;
+  bool corrected;
+};
+
+// Called by the two warps (64 threads) that own the tile's rows; `half` says
+// which 32 rows this warp holds, `pair` selects the named barrier (1 + pair).
+// `sc` must not be reused by the same warps before they have passed the barrier of
+// their NEXT call (callers alternate between two scratch areas).
+__device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane, int half, int pair, TileScratch& sc, float exp_row,
+                                                        float scale_row, float exp_col0, float exp_col1, float scale_col0,
+                                                        float scale_col1, float abs_tol, float rel_tol, float& max_ratio) {
+  const int r_local = half * 32 + lane;
+  float row_sum = 0.0f;
+#pragma unroll
+  for (int c = 0; c < 64; ++c) row_sum += v[c];
+  const float row_delta = exp_row - row_sum;
+  const float row_thr = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_row), abs_tol);
+  const bool row_bad = fabsf(row_delta) > row_thr;
+  if (!row_bad) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(row_delta), row_thr));
+
+  float w[32];
+  {
+    const bool upper = (lane & 16) != 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float send = upper ? v[i] : v[i + 32];
+      float keep = upper ? v[i + 32] : v[i];
+      w[i] = keep + __shfl_xor_sync(0xffffffffU, send, 16);
+    }
+    int n = 16;
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) {
+      const bool up = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        float send = up ? w[i] : w[i + n];
+        float keep = up ? w[i + n] : w[i];
+        w[i] = keep + __shfl_xor_sync(0xffffffffU, send, off);
+      }
+      n >>= 1;
+    }
+  }
+  *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(w[0], w[1]);
+  const uint32_t row_mask = __ballot_sync(0xffffffffU, row_bad);
+  const int first_lane = row_mask != 0 ? __ffs(row_mask) - 1 : 0;
+  const float first_delta = __shfl_sync(0xffffffffU, row_delta, first_lane);
+  if (lane == 0) {
+    sc.rows[half].count = __popc(row_mask);
+    sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
+    sc.rows[half].delta = first_delta;
+  }
+  if (pair == 0) {
+    named_barrier_sync<1, 64>();
+  } else {
+    named_barrier_sync<2, 64>();
+  }
+  const float col_delta0 = exp_col0 - (sc.colpart[0][lane] + sc.colpart[1][lane]);
+  const float col_delta1 = exp_col1 - (sc.colpart[0][32 + lane] + sc.colpart[1][32 + lane]);
+  const float col_thr0 = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_col0), abs_tol);
+  const float col_thr1 = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_col1), abs_tol);
+  const bool col_bad0 = fabsf(col_delta0) > col_thr0;
+  const bool col_bad1 = fabsf(col_delta1) > col_thr1;
+  if (!col_bad0) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(col_delta0), col_thr0));
+  if (!col_bad1) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(col_delta1), col_thr1));
+  const uint32_t col_mask0 = __ballot_sync(0xffffffffU, col_bad0);
+  const uint32_t col_mask1 = __ballot_sync(0xffffffffU, col_bad1);
+
+  TileDecision d;
+  d.bad_rows = sc.rows[0].count + sc.rows[1].count;
+  d.bad_cols = __popc(col_mask0) + __popc(col_mask1);
+  d.bad_row = -1;
+  d.bad_col = -1;
+  d.row_delta = 0.0f;
+  d.col_delta = 0.0f;
+  d.corrected = false;
+  if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps
+    if (d.bad_rows != 0) {
+      d.bad_row = sc.rows[0].count != 0 ? sc.rows[0].first : sc.rows[1].first;
+      d.row_delta = sc.rows[0].count != 0 ? sc.rows[0].delta : sc.rows[1].delta;
+    }
+    const float d0 = __shfl_sync(0xffffffffU, col_delta0, col_mask0 != 0 ? __ffs(col_mask0) - 1 : 0);
+    const float d1 = __shfl_sync(0xffffffffU, col_delta1, col_mask1 != 0 ? __ffs(col_mask1) - 1 : 0);
+    if (col_mask0 != 0) {
+      d.bad_col = __ffs(col_mask0) - 1;
+      d.col_delta = d0;
+    } else if (col_mask1 != 0) {
+      d.bad_col = 32 + __ffs(col_mask1) - 1;
+      d.col_delta = d1;
+    }
+    d.corrected = d.bad_rows == 1 && d.bad_cols == 1;
+    if (d.corrected && r_local == d.bad_row) {
+      const float both = d.row_delta + d.col_delta;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        if (c == d.bad_col) v[c] = __fmaf_rn(0.5f, both, v[c]);
+      }
+    }
+  }
+  return d;
+}
+
+}  // namespace ftg

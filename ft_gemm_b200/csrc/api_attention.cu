@@ -1,0 +1,252 @@
+// C-ABI of the fault-tolerant attention forward: see include/ft_attention.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <new>
+
+#include "attention_kernels.h"
+#include "kernels.h"
+
+using namespace ftg;
+
+namespace ftg {
+int noalloc_fail(int code, const char* fmt, ...);  // sets the thread's last-error text (api.cu)
+}
+
+namespace {
+
+#define ATTN_CUDA(call)                                                                                      \
+  do {                                                                                                       \
+    cudaError_t err_ = (call);                                                                               \
+    if (err_ != cudaSuccess) return noalloc_fail(FT_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(err_)); \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// [rows, cols] FP16, cols contiguous; box = 64 columns (128 bytes) x 128 rows, 128-byte swizzle.
+int make_f16_map(CUtensorMap* map, const void* base, size_t rows, size_t cols) {
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &query) != cudaSuccess ||
+        query != cudaDriverEntryPointSuccess) {
+      return noalloc_fail(FT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    }
+    encode = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {64u, 128u};
+  cuuint32_t elem[2] = {1u, 1u};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return noalloc_fail(FT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return FT_OK;
+}
+
+}  // namespace
+
+struct ft_attn_handle {
+  int batch = 0, heads = 0, seq = 0, dim = 0;
+  ft_attn_options options{};
+  const void *q = nullptr, *k = nullptr, *v = nullptr;
+  void* vt = nullptr;
+  float* cache = nullptr;  // one allocation: band sums, expected checksums, V sums
+  size_t cache_bytes = 0;
+  float *q_sums = nullptr, *q_mags = nullptr, *k_sums = nullptr, *k_mags = nullptr;
+  float *expected_rows = nullptr, *expected_cols = nullptr, *row_scales = nullptr, *col_scales = nullptr;
+  float *v_sum = nullptr, *v_weighted = nullptr;
+  AttnDeviceReport* report = nullptr;
+  CUtensorMap tmap_q{}, tmap_k{}, tmap_vt{};
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaStream_t last_stream = nullptr;
+};
+
+extern "C" {
+
+void ft_attn_options_default(ft_attn_options* o) {
+  if (o == nullptr) return;
+  std::memset(o, 0, sizeof(*o));
+  o->score_abs_tol = 1.0e-2f;
+  o->score_rel_tol = 2.0e-5f;
+  o->pv_abs_tol = 2.0e-3f;
+  o->pv_rel_tol = 2.0e-3f;
+}
+
+int ft_attention_fp16_abft_destroy(ft_attn_handle* h) {
+  if (h == nullptr) return FT_OK;
+  cudaStreamSynchronize(h->last_stream);
+  cudaFree(h->vt);
+  cudaFree(h->cache);
+  cudaFree(h->report);
+  if (h->ev0) cudaEventDestroy(h->ev0);
+  if (h->ev1) cudaEventDestroy(h->ev1);
+  delete h;
+  return FT_OK;
+}
+
+int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const void* k, const void* v, int batch, int heads, int seq,
+                                   int head_dim, const ft_attn_options* options, void* stream_ptr) {
+  if (handle == nullptr || q == nullptr || k == nullptr || v == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or operand pointer");
+  *handle = nullptr;
+  if (batch <= 0 || heads <= 0 || seq <= 0 || seq % 128 != 0 || head_dim != 128) {
+    return noalloc_fail(FT_ERR_INVALID, "Invalid options. Require head_dim == 128, sequence %% 128 == 0 and positive batch/heads (got B=%d H=%d N=%d D=%d).",
+                        batch, heads, seq, head_dim);
+  }
+  if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0) {
+    return noalloc_fail(FT_ERR_INVALID, "Q, K and V must be 16-byte aligned");
+  }
+  ft_attn_options opts;
+  ft_attn_options_default(&opts);
+  if (options != nullptr) opts = *options;
+  if (opts.score_abs_tol < 0 || opts.score_rel_tol < 0 || opts.pv_abs_tol < 0 || opts.pv_rel_tol < 0) {
+    return noalloc_fail(FT_ERR_INVALID, "negative tolerance");
+  }
+  int device = 0;
+  ATTN_CUDA(cudaGetDevice(&device));
+  cudaDeviceProp prop;
+  ATTN_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return noalloc_fail(FT_ERR_UNSUPPORTED, "this library needs an sm_100 GPU (found sm_%d%d)", prop.major, prop.minor);
+  ATTN_CUDA(configure_attention());
+
+  ft_attn_handle* h = new (std::nothrow) ft_attn_handle();
+  if (h == nullptr) return noalloc_fail(FT_ERR_INVALID, "out of host memory");
+  h->batch = batch;
+  h->heads = heads;
+  h->seq = seq;
+  h->dim = head_dim;
+  h->options = opts;
+  h->q = q;
+  h->k = k;
+  h->v = v;
+  const size_t bh = static_cast<size_t>(batch) * heads;
+  const size_t bands = bh * (seq / 64);
+  const size_t band_floats = bands * head_dim;
+  const size_t checks = bh * (seq / 64) * (seq / 64) * 64;
+  const size_t key_floats = bh * seq;
+  const size_t floats = 4 * band_floats + 4 * checks + 2 * key_floats;
+  h->cache_bytes = floats * sizeof(float);
+  cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&h->cache), h->cache_bytes);
+  if (err == cudaSuccess) err = cudaMalloc(&h->vt, bh * seq * head_dim * 2);
+  if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->report), sizeof(AttnDeviceReport));
+  if (err == cudaSuccess) err = cudaEventCreate(&h->ev0);
+  if (err == cudaSuccess) err = cudaEventCreate(&h->ev1);
+  if (err != cudaSuccess) {
+    ft_attention_fp16_abft_destroy(h);
+    return noalloc_fail(FT_ERR_CUDA, "allocating the attention cache (%zu bytes) failed: %s", floats * sizeof(float), cudaGetErrorString(err));
+  }
+  float* cursor = h->cache;
+  h->q_sums = cursor, cursor += band_floats;
+  h->q_mags = cursor, cursor += band_floats;
+  h->k_sums = cursor, cursor += band_floats;
+  h->k_mags = cursor, cursor += band_floats;
+  h->expected_rows = cursor, cursor += checks;
+  h->expected_cols = cursor, cursor += checks;
+  h->row_scales = cursor, cursor += checks;
+  h->col_scales = cursor, cursor += checks;
+  h->v_sum = cursor, cursor += key_floats;
+  h->v_weighted = cursor, cursor += key_floats;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  int rc = make_f16_map(&h->tmap_q, q, bh * seq, head_dim);
+  if (rc == FT_OK) rc = make_f16_map(&h->tmap_k, k, bh * seq, head_dim);
+  if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt, h->vt, bh * head_dim, seq);
+  if (rc == FT_OK) {
+    err = cudaMemsetAsync(h->report, 0, sizeof(AttnDeviceReport), stream);
+    if (err == cudaSuccess) err = cudaEventRecord(h->ev0, stream);
+    if (err == cudaSuccess) err = launch_attn_prepare_v(v, h->vt, h->v_sum, h->v_weighted, static_cast<int>(bh), seq, stream);
+    if (err == cudaSuccess) err = launch_band_sums_f16(q, h->q_sums, h->q_mags, bh * seq, head_dim, stream);
+    if (err == cudaSuccess) err = launch_band_sums_f16(k, h->k_sums, h->k_mags, bh * seq, head_dim, stream);
+    // per head: S = Q K^T is the GEMM A = Q [N, D], B = K [N, D]
+    if (err == cudaSuccess) {
+      err = launch_expected_f16(q, h->k_sums, h->k_mags, h->expected_rows, h->row_scales, seq, seq / 64, head_dim, 0,
+                                static_cast<int>(bh), stream);
+    }
+    if (err == cudaSuccess) {
+      err = launch_expected_f16(k, h->q_sums, h->q_mags, h->expected_cols, h->col_scales, seq, seq / 64, head_dim, 1,
+                                static_cast<int>(bh), stream);
+    }
+    if (err == cudaSuccess) err = cudaEventRecord(h->ev1, stream);
+    if (err != cudaSuccess) rc = noalloc_fail(FT_ERR_CUDA, "attention prepare failed: %s", cudaGetErrorString(err));
+  }
+  h->last_stream = stream;
+  if (rc != FT_OK) {
+    ft_attention_fp16_abft_destroy(h);
+    return rc;
+  }
+  *handle = h;
+  return FT_OK;
+}
+
+int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_fault* fault, void* stream_ptr) {
+  if (h == nullptr || out == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or output pointer");
+  AttnParams params{};
+  params.expected_rows = h->expected_rows;
+  params.expected_cols = h->expected_cols;
+  params.row_scales = h->row_scales;
+  params.col_scales = h->col_scales;
+  params.v_sum = h->v_sum;
+  params.v_weighted = h->v_weighted;
+  params.out = out;
+  params.report = h->report;
+  params.seq = h->seq;
+  params.score_abs_tol = h->options.score_abs_tol;
+  params.score_rel_tol = h->options.score_rel_tol;
+  params.pv_abs_tol = h->options.pv_abs_tol;
+  params.pv_rel_tol = h->options.pv_rel_tol;
+  params.scale_log2 = 1.44269504088896340736f / std::sqrt(static_cast<float>(h->dim));
+  params.fault_stage = FT_ATTN_FAULT_NONE;
+  params.fault_bh = -1;
+  if (fault != nullptr && fault->stage != FT_ATTN_FAULT_NONE) {
+    if (fault->stage != FT_ATTN_FAULT_SCORE && fault->stage != FT_ATTN_FAULT_OUTPUT) {
+      return noalloc_fail(FT_ERR_INVALID, "only the score (1) and output (4) stages can be targeted");
+    }
+    int limit = fault->stage == FT_ATTN_FAULT_SCORE ? h->seq : h->dim;
+    if (fault->batch < 0 || fault->batch >= h->batch || fault->head < 0 || fault->head >= h->heads || fault->query < 0 ||
+        fault->query >= h->seq || fault->index < 0 || fault->index >= limit) {
+      return noalloc_fail(FT_ERR_INVALID, "fault target is outside the tensor");
+    }
+    params.fault_stage = fault->stage;
+    params.fault_bh = fault->batch * h->heads + fault->head;
+    params.fault_query = fault->query;
+    params.fault_index = fault->index;
+    params.fault_value = fault->value;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  ATTN_CUDA(cudaMemsetAsync(h->report, 0, 48, stream));
+  ATTN_CUDA(launch_attention(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
+  h->last_stream = stream;
+  return FT_OK;
+}
+
+int ft_attention_fp16_abft_report(ft_attn_handle* h, ft_attn_report* out) {
+  if (h == nullptr || out == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or report pointer");
+  ATTN_CUDA(cudaStreamSynchronize(h->last_stream));
+  AttnDeviceReport dev;
+  ATTN_CUDA(cudaMemcpy(&dev, h->report, sizeof(dev), cudaMemcpyDeviceToHost));
+  std::memset(out, 0, sizeof(*out));
+  out->status = dev.status != 0 ? FT_ERR_TIMEOUT : FT_OK;
+  out->score_detected = dev.score_detected;
+  out->score_corrected = dev.score_corrected;
+  out->score_uncorrected = dev.score_uncorrected;
+  out->pv_detected = dev.pv_detected;
+  out->pv_corrected = dev.pv_corrected;
+  out->failed_rows = dev.failed_rows;
+  out->n_records = std::min(dev.record_count, 16);
+  std::memcpy(&out->max_score_noise, &dev.max_noise_bits, sizeof(float));
+  std::copy(dev.records, dev.records + out->n_records, out->records);
+  std::sort(out->records, out->records + out->n_records, [](const ft_tile_record& a, const ft_tile_record& b) { return a.tile < b.tile; });
+  float ms = 0.0f;
+  if (cudaEventElapsedTime(&ms, h->ev0, h->ev1) == cudaSuccess) out->prepare_ms = ms;
+  if (dev.status != 0) return noalloc_fail(FT_ERR_TIMEOUT, "a device-side wait expired; the output of this run is not valid");
+  return FT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,46 @@
+// Internal interface between the attention C-ABI layer and its kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/ft_attention.h"
+
+namespace ftg {
+
+struct AttnDeviceReport {
+  int status;
+  int score_detected;
+  int score_corrected;
+  int score_uncorrected;
+  int pv_detected;
+  int pv_corrected;
+  int failed_rows;
+  int record_count;
+  int max_noise_bits;
+  int pad[3];
+  ft_tile_record records[16];
+};
+
+struct AttnParams {
+  const float* expected_rows;  // [B*H][(N/64)^2][64]
+  const float* expected_cols;
+  const float* row_scales;
+  const float* col_scales;
+  const float* v_sum;       // [B*H][N]
+  const float* v_weighted;  // [B*H][N]
+  float* out;               // [B*H][N][D]
+  AttnDeviceReport* report;
+  int seq;
+  float score_abs_tol, score_rel_tol, pv_abs_tol, pv_rel_tol;
+  float scale_log2;  // log2(e) / sqrt(D)
+  int fault_stage, fault_bh, fault_query, fault_index;
+  float fault_value;
+};
+
+cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq,
+                                  cudaStream_t stream);
+cudaError_t configure_attention();
+cudaError_t launch_attention(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
+                             int batch_heads, cudaStream_t stream);
+
+}  // namespace ftg

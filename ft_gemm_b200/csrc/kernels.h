@@ -49,6 +49,12 @@ cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, 
 cudaError_t launch_expected(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
                             int nbands, int k, int mode, cudaStream_t stream);
 
+// FP16 variants for the attention path: `rows` may span many heads for the band sums; the expected
+// kernel treats `batch` problems of [rows, k] x [nbands, k] laid out back to back.
+cudaError_t launch_band_sums_f16(const void* x, float* sums, float* mags, size_t rows, int k, cudaStream_t stream);
+cudaError_t launch_expected_f16(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
+                                int nbands, int k, int mode, int batch, cudaStream_t stream);
+
 // Fused FP8 GEMM + ABFT checker/corrector.  tmap_a / tmap_b describe A[M,K] and
 // B[N,K] with 128-byte-swizzled boxes of (128 K-bytes x 128 rows) and
 // (128 K-bytes x 256 rows).

@@ -13,6 +13,7 @@
 //   expected:  32 partial sums per checksum, partial l taking k = l, l+32, ...
 //              in ascending order with one fma per step, then the pairwise tree
 //              (l, l+16), (l, l+8), ..., (l, l+1) of a shuffle-down reduction.
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -101,6 +102,38 @@ __global__ void __launch_bounds__(kBandThreads) band_sums_kernel(const uint8_t* 
   }
 }
 
+// FP16 operands (attention): one thread owns 8 consecutive k.
+__global__ void __launch_bounds__(kBandThreads) band_sums_f16_kernel(const __half* __restrict__ x, float* __restrict__ sums,
+                                                                     float* __restrict__ mags, int k) {
+  int band = blockIdx.y;
+  int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 8;
+  if (k0 >= k) return;
+  const __half* base = x + static_cast<size_t>(band) * 64 * k + k0;
+  float s[8], m[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = m[i] = 0.0f;
+#pragma unroll 8
+  for (int row = 0; row < 64; ++row) {
+    uint4 packed = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(row) * k));
+    const __half2* h2 = reinterpret_cast<const __half2*>(&packed);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float2 f = __half22float2(h2[w]);
+      s[2 * w] += f.x;
+      m[2 * w] += fabsf(f.x);
+      s[2 * w + 1] += f.y;
+      m[2 * w + 1] += fabsf(f.y);
+    }
+  }
+  float4* so = reinterpret_cast<float4*>(sums + static_cast<size_t>(band) * k + k0);
+  float4* mo = reinterpret_cast<float4*>(mags + static_cast<size_t>(band) * k + k0);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    so[q] = make_float4(s[4 * q], s[4 * q + 1], s[4 * q + 2], s[4 * q + 3]);
+    mo[q] = make_float4(m[4 * q], m[4 * q + 1], m[4 * q + 2], m[4 * q + 3]);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // expected checksums.
 // x is [rows, k] FP8 (A for the row checksums, B for the column checksums);
@@ -132,13 +165,28 @@ __device__ __forceinline__ void transpose_reduce(float (&v)[N], int lane) {
   }
 }
 
-__global__ void __launch_bounds__(256) expected_checksums_kernel(const uint8_t* __restrict__ x, const float* __restrict__ band_sums,
+__device__ __forceinline__ float load_element(const uint8_t* p) { return fp8_to_float(__ldg(p)); }
+__device__ __forceinline__ float load_element(const __half* p) { return __half2float(__ldg(p)); }
+
+// blockIdx.z walks independent problems of the same shape laid out back to back
+// (one per attention head); the GEMM path launches with gridDim.z = 1.
+template <class T>
+__global__ void __launch_bounds__(256) expected_checksums_kernel(const T* __restrict__ x, const float* __restrict__ band_sums,
                                                                  const float* __restrict__ band_mags, float* __restrict__ expected,
                                                                  float* __restrict__ scales, int rows, int nbands, int k, int mode) {
+  {
+    const size_t z = blockIdx.z;
+    const size_t tiles64 = static_cast<size_t>(rows >> 6) * nbands * 64;
+    x += z * rows * k;
+    band_sums += z * nbands * k;
+    band_mags += z * nbands * k;
+    expected += z * tiles64;
+    scales += z * tiles64;
+  }
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int row0 = blockIdx.x * 64 + warp * kExpRows;
   int band0 = blockIdx.y * kExpBands;
-  const uint8_t* xr[kExpRows];
+  const T* xr[kExpRows];
 #pragma unroll
   for (int r = 0; r < kExpRows; ++r) xr[r] = x + static_cast<size_t>(row0 + r) * k;
   const float* bs[kExpBands];
@@ -158,7 +206,7 @@ __global__ void __launch_bounds__(256) expected_checksums_kernel(const uint8_t* 
   for (int kk = lane; kk < k; kk += 32) {
     float av[kExpRows], sv[kExpBands], mv[kExpBands];
 #pragma unroll
-    for (int r = 0; r < kExpRows; ++r) av[r] = fp8_to_float(__ldg(xr[r] + kk));
+    for (int r = 0; r < kExpRows; ++r) av[r] = load_element(xr[r] + kk);
 #pragma unroll
     for (int j = 0; j < kExpBands; ++j) {
       sv[j] = __ldg(bs[j] + kk);
@@ -222,8 +270,27 @@ cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, 
 cudaError_t launch_expected(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
                             int nbands, int k, int mode, cudaStream_t stream) {
   dim3 grid(rows / 64, (nbands + kExpBands - 1) / kExpBands);
-  expected_checksums_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), band_sums, band_mags, expected, scales, rows,
-                                                      nbands, k, mode);
+  expected_checksums_kernel<uint8_t><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), band_sums, band_mags, expected, scales,
+                                                               rows, nbands, k, mode);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_band_sums_f16(const void* x, float* sums, float* mags, size_t rows, int k, cudaStream_t stream) {
+  size_t bands = rows / 64;
+  for (size_t first = 0; first < bands; first += 65535) {  // grid.y limit
+    unsigned count = static_cast<unsigned>(bands - first < 65535 ? bands - first : 65535);
+    dim3 grid((k / 8 + kBandThreads - 1) / kBandThreads, count);
+    band_sums_f16_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const __half*>(x) + first * 64 * k, sums + first * k,
+                                                            mags + first * k, k);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_expected_f16(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
+                                int nbands, int k, int mode, int batch, cudaStream_t stream) {
+  dim3 grid(rows / 64, (nbands + kExpBands - 1) / kExpBands, batch);
+  expected_checksums_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), band_sums, band_mags, expected, scales, rows,
+                                                              nbands, k, mode);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,101 @@
+/*
+ * ft_attention.h -- C-ABI of the fault-tolerant flash-attention forward on B200.
+ *
+ * The reference project's attention chain (src/ft_flash_attention_a0.cu ...
+ * a14.cu) is, like its GEMM stages, a set of standalone programs: main() prepares
+ * K/V metadata (prepare_attention_metadata_kernel, transpose_v_kernel;
+ * src/ft_flash_attention_a14.cu:303-316, 571-621), launches the fused forward
+ * kernel with a fault description (a14:659-1201, parameters a14:640-657) and reads
+ * nine counters back (DeviceStats, a14:98-108).  The entry points below are that
+ * launch interface.
+ *
+ * Operator: O[b,h,q,:] = softmax(Q K^T / sqrt(D)) V, non-causal, for
+ *   Q, K, V  [B, H, N, D]  FP16, D contiguous       (the reference uses FP8 E4M3)
+ *   O        [B, H, N, D]  FP32
+ *   D == 128, N % 128 == 0
+ * Protection:
+ *   - score stage: every 64x64 tile of S = Q K^T is checked with the SAME row /
+ *     column checksum verifier as the GEMM (expected_row = Q rowsum(K-tile),
+ *     expected_col = colsum(Q-tile) K^T, cached by _prepare); a single faulty score
+ *     is located at the row/column intersection and corrected in registers before
+ *     the softmax; tiles with several bad rows or columns are reported;
+ *   - output stage: the reference's projection check of P V (a0:585-662): the
+ *     expected sum and position-weighted sum of each output row are carried
+ *     through the online softmax from per-key sums of V, a single faulty output
+ *     element is located by the ratio of the two deltas and corrected, anything
+ *     else counts as a failed row.
+ */
+#ifndef FT_ATTENTION_H
+#define FT_ATTENTION_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "ft_gemm.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ft_attn_handle ft_attn_handle;
+
+typedef struct {
+  float score_abs_tol; /* default 1e-2: |delta| > abs + rel * max(1, scale), as in the GEMM (src/s4:467) */
+  float score_rel_tol; /* default 2e-5 */
+  float pv_abs_tol;    /* default 2e-3 (src/ft_flash_attention_a0.cu:63-64) */
+  float pv_rel_tol;    /* default 2e-3 */
+  int reserved[4];
+} ft_attn_options;
+
+/* Fault stages use the reference's numbering (src/ft_flash_attention_a0.cu:27-33);
+ * only the two stages this build protects can be targeted. */
+#define FT_ATTN_FAULT_NONE 0
+#define FT_ATTN_FAULT_SCORE 1  /* value added to S[query, index=key] after Q K^T */
+#define FT_ATTN_FAULT_OUTPUT 4 /* value added to the normalised O[query, index=dim] */
+
+typedef struct {
+  int stage;
+  int batch;
+  int head;
+  int query;
+  int index;
+  float value;
+} ft_attn_fault;
+
+typedef struct {
+  int status;            /* FT_OK or FT_ERR_TIMEOUT */
+  int score_detected;    /* score tiles whose checker fired */
+  int score_corrected;   /* of which: one bad row and one bad column, corrected */
+  int score_uncorrected; /* of which: several bad rows/columns, reported only */
+  int pv_detected;       /* output rows whose projection check fired */
+  int pv_corrected;
+  int failed_rows;       /* output rows detected but not locatable */
+  int n_records;
+  float max_score_noise; /* max |delta|/threshold over score checksums that passed */
+  float prepare_ms;
+  /* score-tile records: tile = ((batch*heads + head) * (N/64) + q_band) * (N/64) + key_band */
+  ft_tile_record records[16];
+} ft_attn_report;
+
+void ft_attn_options_default(ft_attn_options* options);
+
+/* Replaces the reference's metadata allocation and prepare launches
+ * (src/ft_flash_attention_a14.cu:1369-1430): builds V^T, the per-key sums of V and
+ * the expected row/column checksums of every 64x64 score tile.  The cache is valid
+ * while Q, K and V are unchanged; it is owned by the handle. */
+int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const void* k, const void* v, int batch, int heads,
+                                   int sequence, int head_dim, const ft_attn_options* options, void* stream);
+
+/* Replaces one launch of the fused forward kernel with its fault parameters
+ * (src/ft_flash_attention_a14.cu:1324-1359).  Asynchronous; `fault` may be NULL. */
+int ft_attention_fp16_abft_run(ft_attn_handle* handle, float* out, const ft_attn_fault* fault, void* stream);
+
+/* Replaces the read-back of DeviceStats (src/ft_flash_attention_a14.cu:1437-1440). */
+int ft_attention_fp16_abft_report(ft_attn_handle* handle, ft_attn_report* out);
+
+int ft_attention_fp16_abft_destroy(ft_attn_handle* handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -9,18 +9,21 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HEADER = os.path.join(ROOT, "include", "ft_gemm.h")
+HEADERS = [os.path.join(ROOT, "include", name) for name in ("ft_gemm.h", "ft_attention.h")]
 
 
 def declared_functions():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(ft_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in HEADERS:
+        text = re.sub(r"/\*.*?\*/", "", open(header).read(), flags=re.S)
+        names.update(re.findall(r"\b(ft_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_declares_the_north_star_entry_points():
     names = declared_functions()
-    for required in ("ft_gemm_fp8_abft_prepare", "ft_gemm_fp8_abft_run", "ft_gemm_fp8_abft_report", "ft_gemm_fp8_abft_destroy"):
+    for required in ("ft_gemm_fp8_abft_prepare", "ft_gemm_fp8_abft_run", "ft_gemm_fp8_abft_report", "ft_gemm_fp8_abft_destroy",
+                     "ft_attention_fp16_abft_prepare", "ft_attention_fp16_abft_run", "ft_attention_fp16_abft_report"):
         assert required in names
 
 
@@ -35,7 +38,7 @@ def test_library_exports_every_declared_symbol(lib_path):
 
 def test_header_compiles_as_c(tmp_path):
     src = tmp_path / "t.c"
-    src.write_text('#include "ft_gemm.h"\nint main(void){ft_options o; ft_report r; (void)o; (void)r; return FT_OK;}\n')
+    src.write_text('#include "ft_gemm.h"\n#include "ft_attention.h"\nint main(void){ft_options o; ft_report r; ft_attn_report a; (void)o; (void)r; (void)a; return FT_OK;}\n')
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-c", str(src), "-o",
                     str(tmp_path / "t.o")], check=True)
 

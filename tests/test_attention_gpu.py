@@ -1,0 +1,154 @@
+"""GPU parity tests of the fault-tolerant attention forward (through the C-ABI)
+against the CPU oracle and an FP64 softmax(QK^T/sqrt(D))V.
+
+Tolerances: outputs agree with the oracle within 2e-3 absolute (the products are
+exact, the differences come from the accumulation order of the tensor core, from
+ex2.approx against libm's exp2f, and from FP16 rounding of probabilities that sit
+on a rounding boundary) and with the FP64 truth within 4e-3; counters and
+located positions must be equal."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from tests import oracle_attention as oa  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ftg():
+    import ft_gemm_b200
+    ft_gemm_b200.load()
+    assert torch.cuda.is_available()
+    return ft_gemm_b200
+
+
+def _qkv(b, h, n, d=128, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return tuple(torch.randn((b, h, n, d), generator=g).to(torch.float16).cuda() for _ in range(3))
+
+
+def _np(t):
+    return t.cpu().numpy()
+
+
+@pytest.mark.parametrize("b,h,n", [(1, 1, 128), (1, 2, 256), (2, 3, 512)])
+def test_clean_forward(ftg, b, h, n):
+    q, k, v = _qkv(b, h, n, seed=n)
+    op = ftg.FtAttention(q, k, v)
+    out = op.new_output()
+    op.run(out)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    assert rep.max_score_noise < 0.1
+    want, stats, _ = oa.forward(_np(q), _np(k), _np(v))
+    assert stats.score_detected == 0
+    np.testing.assert_allclose(_np(out), want, atol=2e-3, rtol=0)
+    np.testing.assert_allclose(_np(out), oa.truth_fp64(_np(q), _np(k), _np(v)), atol=4e-3, rtol=0)
+    op.close()
+
+
+def test_score_faults_match_oracle(ftg):
+    b, h, n = 1, 2, 512
+    q, k, v = _qkv(b, h, n, seed=7)
+    op = ftg.FtAttention(q, k, v)
+    clean = op.new_output()
+    op.run(clean)
+    assert op.report().score_detected == 0
+    out = op.new_output()
+    bands = n // 64
+    # every TMEM lane quarter of the CTA, both 64-column halves, first / middle / last key tile
+    cases = [(0, 0, 0, 3.0), (1, 40, 100, -2.5), (0, 70, 200, 8.0), (1, 100, 511, 1.5), (0, 300, 64, -6.0), (1, 511, 447, 64.0)]
+    for head, query, key, value in cases:
+        fault = (ftg.FAULT_SCORE, 0, head, query, key, value)
+        op.run(out, fault)
+        rep = op.report()
+        want, stats, records = oa.forward(_np(q), _np(k), _np(v), fault=fault)
+        assert stats.min_margin > 1e-3
+        assert (rep.score_detected, rep.score_corrected, rep.score_uncorrected) == (1, 1, 0) == \
+               (stats.score_detected, stats.score_corrected, stats.score_uncorrected)
+        got, exp = rep.records[0], records[0]
+        assert (got.tile, got.bad_row, got.bad_col, got.corrected) == (exp.tile, exp.bad_row, exp.bad_col, 1)
+        assert got.tile == ((head * bands) + query // 64) * bands + key // 64
+        assert got.row_delta == pytest.approx(exp.row_delta, abs=2e-3) and got.col_delta == pytest.approx(exp.col_delta, abs=2e-3)
+        assert (rep.pv_detected, rep.failed_rows) == (0, 0)
+        np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
+    op.close()
+
+
+def test_two_score_faults_in_one_tile_are_reported_not_corrected(ftg):
+    # the C-ABI takes one fault per run, so the second bad checksum comes from a stale cache: K changes after prepare
+    b, h, n = 1, 1, 256
+    q, k, v = _qkv(b, h, n, seed=9)
+    op = ftg.FtAttention(q, k, v)
+    k[0, 0, 5, :] += 1.0  # column 5 of every score tile of key band 0 now disagrees with the cached checksums
+    out = op.new_output()
+    op.run(out)
+    rep = op.report()
+    assert rep.score_detected >= n // 64 and rep.score_corrected == 0 and rep.score_uncorrected == rep.score_detected
+    assert all(r.bad_col_count >= 1 and r.corrected == 0 for r in rep.records)
+    op.close()
+
+
+def test_output_faults_match_oracle(ftg):
+    b, h, n = 2, 2, 256
+    q, k, v = _qkv(b, h, n, seed=11)
+    op = ftg.FtAttention(q, k, v)
+    clean = op.new_output()
+    op.run(clean)
+    out = op.new_output()
+    for batch, head, query, dim, value in [(0, 0, 3, 0, 0.5), (1, 1, 200, 127, -1.0), (0, 1, 64, 64, 0.05), (1, 0, 255, 31, 3.0)]:
+        fault = (ftg.FAULT_OUTPUT, batch, head, query, dim, value)
+        op.run(out, fault)
+        rep = op.report()
+        _, stats, _ = oa.forward(_np(q), _np(k), _np(v), fault=fault)
+        assert (rep.pv_detected, rep.pv_corrected, rep.failed_rows) == (1, 1, 0) == (stats.pv_detected, stats.pv_corrected, stats.failed_rows)
+        assert rep.score_detected == 0
+        np.testing.assert_allclose(_np(out), _np(clean), atol=6e-3, rtol=0)
+    # under the projection tolerance: invisible, as in the reference
+    op.run(out, (ftg.FAULT_OUTPUT, 0, 0, 10, 10, 1e-3))
+    assert op.report().pv_detected == 0
+    op.close()
+
+
+def test_repeat_runs_are_bit_identical_and_arguments_checked(ftg):
+    q, k, v = _qkv(1, 2, 384, seed=13)
+    op = ftg.FtAttention(q, k, v)
+    first = op.new_output()
+    op.run(first, (ftg.FAULT_SCORE, 0, 1, 100, 300, 5.0))
+    for _ in range(5):
+        out = op.new_output()
+        op.run(out, (ftg.FAULT_SCORE, 0, 1, 100, 300, 5.0))
+        assert op.report().score_corrected == 1
+        assert torch.equal(out, first)
+    with pytest.raises(ftg.FtGemmError):
+        op.run(first, (ftg.FAULT_SCORE, 0, 5, 0, 0, 1.0))  # head out of range
+    with pytest.raises(ftg.FtGemmError):
+        op.run(first, (2, 0, 0, 0, 0, 1.0))  # the softmax stage is not a target of this build
+    op.close()
+    with pytest.raises(ftg.FtGemmError):
+        ftg.FtAttention(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous())  # D must be 128
+
+
+def test_config5_shape_properties(ftg):
+    """B=4 H=32 N=4096 D=128: too large for the CPU oracle in full; sampled rows against FP64 and a score fault."""
+    b, h, n = 4, 32, 4096
+    q, k, v = _qkv(b, h, n, seed=17)
+    op = ftg.FtAttention(q, k, v)
+    out = op.new_output()
+    op.run(out)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    for batch, head in [(0, 0), (3, 31), (1, 7)]:
+        rows = torch.tensor([0, 1, 1000, 2047, 2048, 4095])
+        qs = q[batch, head, rows].double()
+        s = qs @ k[batch, head].double().T / 128 ** 0.5
+        want = torch.softmax(s, dim=-1) @ v[batch, head].double()
+        assert float((out[batch, head, rows].double() - want).abs().max()) < 4e-3
+    faulty = op.new_output()
+    op.run(faulty, (ftg.FAULT_SCORE, 2, 5, 2049, 4000, 12.0))
+    rep = op.report()
+    assert (rep.score_detected, rep.score_corrected, rep.pv_detected) == (1, 1, 0)
+    assert float((faulty - out).abs().max()) < 5e-4
+    op.close()

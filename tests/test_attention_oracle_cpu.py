@@ -1,0 +1,70 @@
+"""CPU tests of the attention oracle: FP16 codec against numpy, values against an
+FP64 softmax(QK^T/sqrt(D))V, and the two protected stages' decisions."""
+import numpy as np
+import pytest
+
+from tests import oracle_attention as oa
+
+
+def _qkv(b, h, n, d, seed=0):
+    rng = np.random.default_rng(seed)
+    return tuple(rng.standard_normal((b, h, n, d)).astype(np.float16) for _ in range(3))
+
+
+def test_half_codec_matches_numpy():
+    rng = np.random.default_rng(1)
+    values = np.concatenate([rng.standard_normal(2000) * 10.0 ** rng.integers(-8, 5, 2000), [0.0, 65504.0, 65519.9, 65520.0, 1e9,
+                            6e-8, 2.98e-8, 2.99e-8, 1.0009765625 + 2 ** -12, -3.1415]]).astype(np.float32)
+    for x in values:
+        bits, back = oa.half_roundtrip(float(x))
+        want = np.float32(x).astype(np.float16)
+        assert bits == int(want.view(np.uint16)), x
+        assert back == float(want) or (np.isinf(want) and np.isinf(back))
+
+
+def test_clean_forward_matches_fp64():
+    q, k, v = _qkv(1, 2, 256, 128)
+    out, stats, records = oa.forward(q, k, v)
+    assert (stats.score_detected, stats.pv_detected, stats.failed_rows) == (0, 0, 0) and not records
+    assert stats.max_score_noise < 0.1
+    # FP16 probabilities limit the accuracy: 2^-11 relative per term
+    np.testing.assert_allclose(out, oa.truth_fp64(q, k, v), atol=3e-3, rtol=0)
+
+
+def test_score_fault_is_located_and_corrected():
+    q, k, v = _qkv(1, 2, 256, 128, seed=3)
+    clean, _, _ = oa.forward(q, k, v)
+    for query, key, value in [(0, 0, 2.0), (77, 200, -5.0), (255, 129, 9.0), (128, 63, 1.5)]:
+        out, stats, records = oa.forward(q, k, v, fault=(1, 0, 1, query, key, value))
+        assert (stats.score_detected, stats.score_corrected, stats.score_uncorrected) == (1, 1, 0)
+        rec = records[0]
+        bands = 256 // 64
+        assert rec.tile == ((1 * bands) + query // 64) * bands + key // 64
+        assert (rec.bad_row, rec.bad_col, rec.corrected) == (query % 64, key % 64, 1)
+        assert rec.row_delta == pytest.approx(-value, abs=2e-3)
+        assert stats.pv_detected == 0
+        np.testing.assert_allclose(out, clean, atol=2e-4)
+
+
+def test_uncorrected_score_fault_corrupts_only_its_row():
+    q, k, v = _qkv(1, 1, 128, 128, seed=4)
+    clean, _, _ = oa.forward(q, k, v)
+    # tolerance so loose that the score checker cannot see the fault: the softmax of that row changes
+    out, stats, _ = oa.forward(q, k, v, score_abs=1e3, fault=(1, 0, 0, 5, 9, 40.0))
+    assert stats.score_detected == 0
+    assert np.abs(out[0, 0, 5] - clean[0, 0, 5]).max() > 1e-2
+    mask = np.ones(128, dtype=bool)
+    mask[5] = False
+    np.testing.assert_array_equal(out[0, 0, mask], clean[0, 0, mask])
+
+
+def test_output_fault_is_located_and_corrected():
+    q, k, v = _qkv(1, 2, 256, 128, seed=5)
+    clean, _, _ = oa.forward(q, k, v)
+    for query, dim, value in [(3, 0, 0.5), (200, 127, -1.0), (64, 64, 0.05)]:
+        out, stats, _ = oa.forward(q, k, v, fault=(4, 0, 0, query, dim, value))
+        assert (stats.pv_detected, stats.pv_corrected, stats.failed_rows) == (1, 1, 0)
+        np.testing.assert_allclose(out, clean, atol=5e-3)
+    # below the projection tolerance (2e-3 + 2e-3 * max(1, |expected|)): invisible, as in the reference
+    out, stats, _ = oa.forward(q, k, v, fault=(4, 0, 0, 10, 10, 1e-3))
+    assert stats.pv_detected == 0
