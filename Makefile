@@ -29,12 +29,15 @@ $(LIB): $(OBJS)
 	@mkdir -p ft_gemm_b200/lib
 	$(NVCC) $(ARCH) -shared -o $@ $(OBJS)
 
-cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench
+cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench build/ft_flash_attention
 
 build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(LIB)
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+
+build/ft_flash_attention: $(CSRC)/cli/ft_flash_attention.cpp $(CSRC)/cli/cli_common.h $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 build/cublaslt_fp8_bench: $(CSRC)/cli/cublaslt_fp8_bench.cpp $(CSRC)/cli/cli_common.h $(LIB)

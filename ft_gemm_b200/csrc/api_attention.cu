@@ -185,6 +185,13 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   return FT_OK;
 }
 
+int ft_attention_generate_f16(void* out, size_t count, uint32_t seed, int dist, float sigma, void* stream_ptr) {
+  if (out == nullptr && count > 0) return noalloc_fail(FT_ERR_INVALID, "null output pointer");
+  if (dist != 0 && dist != 1) return noalloc_fail(FT_ERR_INVALID, "dist must be 0 (reference grid) or 1 (normal)");
+  ATTN_CUDA(launch_generate_f16(out, count, seed, dist, sigma, static_cast<cudaStream_t>(stream_ptr)));
+  return FT_OK;
+}
+
 int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_fault* fault, void* stream_ptr) {
   if (h == nullptr || out == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or output pointer");
   AttnParams params{};

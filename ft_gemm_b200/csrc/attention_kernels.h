@@ -39,6 +39,7 @@ struct AttnParams {
 
 cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq,
                                   cudaStream_t stream);
+cudaError_t launch_generate_f16(void* out, size_t count, uint32_t seed, int dist, float sigma, cudaStream_t stream);
 cudaError_t configure_attention();
 cudaError_t launch_attention(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                              int batch_heads, cudaStream_t stream);

@@ -1,0 +1,175 @@
+// Fault-tolerant flash-attention forward on B200.  Same command line, report keys
+// and exit-code rule as the reference's attention programs
+// (src/ft_flash_attention_a14.cu:110-283, 1363-1519): generate -> prepare metadata
+// (timed) -> warm-up -> `repeat` fault-free launches inside one event pair -> one
+// more launch with the requested --fault-stage, whose output is verified against
+// FP64 on the host; exit 0 iff no mismatch and the counters match the fault.
+// Differences that follow from the operator this build protects: inputs are FP16
+// (N(0,1) by default, `--dist grid` for the reference's value grid), only the
+// score and output stages can be targeted, and verification covers
+// `--verify-rows` query rows spread over all heads (all rows when that many exist).
+#include <cuda_fp16.h>
+
+#include "cli_common.h"
+#include "ft_attention.h"
+
+static float half_bits_to_float(uint16_t h) {
+  __half_raw raw;
+  raw.x = h;
+  return __half2float(__half(raw));
+}
+
+int main(int argc, char** argv) {
+  ArgReader args{argc, argv};
+  int batch = args.get_int("--batch", 1), heads = args.get_int("--heads", 2), sequence = args.get_int("--sequence", 128);
+  int head_dim = args.get_int("--head-dim", 128), warmup = args.get_int("--warmup", 2), repeat = args.get_int("--repeat", 10);
+  int fault_batch = args.get_int("--fault-batch", 0), fault_head = args.get_int("--fault-head", 0);
+  int fault_query = args.get_int("--fault-query", -1), fault_index = args.get_int("--fault-index", -1);
+  float fault_value = args.get_float("--fault-value", 1.0f);
+  ft_attn_options opt;
+  ft_attn_options_default(&opt);
+  opt.score_abs_tol = args.get_float("--score-abs-tol", opt.score_abs_tol);
+  opt.score_rel_tol = args.get_float("--score-rel-tol", opt.score_rel_tol);
+  opt.pv_abs_tol = args.get_float("--pv-abs-tol", opt.pv_abs_tol);
+  opt.pv_rel_tol = args.get_float("--pv-rel-tol", opt.pv_rel_tol);
+  float verify_abs = args.get_float("--verify-abs-tol", 3.0e-3f), verify_rel = args.get_float("--verify-rel-tol", 2.0e-2f);
+  int verify_rows = args.get_int("--verify-rows", 256);
+  std::string stage_name = args.get_string("--fault-stage", "none");
+  std::string dist = args.get_string("--dist", "normal");
+  bool causal = args.has_flag("--causal");
+  if (args.has_flag("--help")) {
+    std::printf(
+        "Usage: %s [--batch N --heads N --sequence N --head-dim 128 --warmup N --repeat N]\n"
+        "       [--fault-stage none|score|output --fault-batch N --fault-head N --fault-query N --fault-index N --fault-value X]\n"
+        "       [--score-abs-tol X --score-rel-tol X --pv-abs-tol X --pv-rel-tol X]\n"
+        "       [--verify-abs-tol X --verify-rel-tol X --verify-rows N --dist normal|grid]\n",
+        argv[0]);
+    return EXIT_SUCCESS;
+  }
+  int stage = stage_name == "none" ? FT_ATTN_FAULT_NONE : stage_name == "score" ? FT_ATTN_FAULT_SCORE : stage_name == "output" ? FT_ATTN_FAULT_OUTPUT : -1;
+  if (fault_query < 0) fault_query = sequence / 2;
+  if (fault_index < 0) fault_index = stage == FT_ATTN_FAULT_OUTPUT ? head_dim / 2 : sequence / 2;  // a0:193-199
+  if (batch <= 0 || heads <= 0 || sequence <= 0 || sequence % 128 != 0 || head_dim != 128 || warmup < 0 || repeat <= 0 || stage < 0 ||
+      causal || (dist != "normal" && dist != "grid") || verify_rows <= 0) {
+    std::fprintf(stderr,
+                 "Invalid options. Require head_dim == 128, sequence %% 128 == 0, non-causal, --fault-stage none|score|output "
+                 "(the softmax stages of the reference are not protected by this build).\n");
+    return EXIT_FAILURE;
+  }
+  CLI_CUDA(cudaSetDevice(0));
+  size_t count = static_cast<size_t>(batch) * heads * sequence * head_dim;
+  void *d_q, *d_k, *d_v;
+  float* d_out;
+  CLI_CUDA(cudaMalloc(&d_q, count * 2));
+  CLI_CUDA(cudaMalloc(&d_k, count * 2));
+  CLI_CUDA(cudaMalloc(&d_v, count * 2));
+  CLI_CUDA(cudaMalloc(reinterpret_cast<void**>(&d_out), count * sizeof(float)));
+  cudaStream_t stream;
+  CLI_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  int dist_id = dist == "grid" ? 0 : 1;
+  CLI_FT(ft_attention_generate_f16(d_q, count, 0x12345678U, dist_id, 1.0f, stream));
+  CLI_FT(ft_attention_generate_f16(d_k, count, 0x9abcdef0U, dist_id, 1.0f, stream));
+  CLI_FT(ft_attention_generate_f16(d_v, count, 0x31415926U, dist_id, 1.0f, stream));
+  CLI_CUDA(cudaStreamSynchronize(stream));
+
+  ft_attn_handle* handle = nullptr;
+  CLI_FT(ft_attention_fp16_abft_prepare(&handle, d_q, d_k, d_v, batch, heads, sequence, head_dim, &opt, stream));
+  ft_attn_report report;
+  CLI_FT(ft_attention_fp16_abft_report(handle, &report));
+  float metadata_ms = report.prepare_ms;
+  for (int i = 0; i < warmup; ++i) CLI_FT(ft_attention_fp16_abft_run(handle, d_out, nullptr, stream));
+  CLI_CUDA(cudaStreamSynchronize(stream));
+  cudaEvent_t start, stop;
+  CLI_CUDA(cudaEventCreate(&start));
+  CLI_CUDA(cudaEventCreate(&stop));
+  CLI_CUDA(cudaEventRecord(start, stream));
+  for (int i = 0; i < repeat; ++i) CLI_FT(ft_attention_fp16_abft_run(handle, d_out, nullptr, stream));
+  CLI_CUDA(cudaEventRecord(stop, stream));
+  CLI_CUDA(cudaEventSynchronize(stop));
+  float total_ms = 0.0f;
+  CLI_CUDA(cudaEventElapsedTime(&total_ms, start, stop));
+  float average_ms = total_ms / repeat;
+  ft_attn_fault fault{stage, fault_batch, fault_head, fault_query, fault_index, fault_value};
+  CLI_FT(ft_attention_fp16_abft_run(handle, d_out, stage == FT_ATTN_FAULT_NONE ? nullptr : &fault, stream));
+  CLI_FT(ft_attention_fp16_abft_report(handle, &report));
+
+  // FP64 verification of sampled query rows (the reference checks every row, a14:1203-1267)
+  size_t total_rows = static_cast<size_t>(batch) * heads * sequence;
+  size_t rows_to_check = std::min<size_t>(total_rows, static_cast<size_t>(verify_rows));
+  float max_absolute_error = 0.0f, max_tolerance_ratio = 0.0f;
+  int mismatches = 0;
+  std::vector<uint16_t> q_row(head_dim), k_head(static_cast<size_t>(sequence) * head_dim), v_head(k_head.size());
+  std::vector<float> o_row(head_dim);
+  std::vector<double> scores(sequence);
+  long cached_head = -1;
+  for (size_t s = 0; s < rows_to_check; ++s) {
+    size_t row = rows_to_check == total_rows ? s : s * (total_rows / rows_to_check) + (s % 7) * 13 % (total_rows / rows_to_check);
+    long bh = static_cast<long>(row / sequence);
+    if (bh != cached_head) {
+      size_t offset = static_cast<size_t>(bh) * sequence * head_dim;
+      CLI_CUDA(cudaMemcpy(k_head.data(), static_cast<uint16_t*>(d_k) + offset, k_head.size() * 2, cudaMemcpyDeviceToHost));
+      CLI_CUDA(cudaMemcpy(v_head.data(), static_cast<uint16_t*>(d_v) + offset, v_head.size() * 2, cudaMemcpyDeviceToHost));
+      cached_head = bh;
+    }
+    CLI_CUDA(cudaMemcpy(q_row.data(), static_cast<uint16_t*>(d_q) + row * head_dim, head_dim * 2, cudaMemcpyDeviceToHost));
+    CLI_CUDA(cudaMemcpy(o_row.data(), d_out + row * head_dim, head_dim * sizeof(float), cudaMemcpyDeviceToHost));
+    double maximum = -1e300;
+    for (int key = 0; key < sequence; ++key) {
+      double dot = 0.0;
+      for (int d = 0; d < head_dim; ++d) dot += static_cast<double>(half_bits_to_float(q_row[d])) * half_bits_to_float(k_head[static_cast<size_t>(key) * head_dim + d]);
+      scores[key] = dot / std::sqrt(static_cast<double>(head_dim));
+      maximum = std::max(maximum, scores[key]);
+    }
+    double denominator = 0.0;
+    for (int key = 0; key < sequence; ++key) {
+      scores[key] = std::exp(scores[key] - maximum);
+      denominator += scores[key];
+    }
+    for (int d = 0; d < head_dim; ++d) {
+      double reference = 0.0;
+      for (int key = 0; key < sequence; ++key) reference += scores[key] * half_bits_to_float(v_head[static_cast<size_t>(key) * head_dim + d]);
+      reference /= denominator;
+      float absolute_error = static_cast<float>(std::fabs(o_row[d] - reference));
+      float tolerance = verify_abs + verify_rel * std::max(1.0f, static_cast<float>(std::fabs(reference)));
+      max_absolute_error = std::max(max_absolute_error, absolute_error);
+      max_tolerance_ratio = std::max(max_tolerance_ratio, absolute_error / tolerance);
+      mismatches += absolute_error > tolerance;
+    }
+  }
+  bool fault_pass;
+  if (stage == FT_ATTN_FAULT_SCORE) {
+    fault_pass = report.score_detected > 0 && report.score_corrected > 0 && report.failed_rows == 0;
+  } else if (stage == FT_ATTN_FAULT_OUTPUT) {
+    fault_pass = report.pv_detected > 0 && report.pv_corrected > 0 && report.failed_rows == 0;
+  } else {
+    fault_pass = report.score_detected == 0 && report.pv_detected == 0 && report.failed_rows == 0;
+  }
+  bool passed = mismatches == 0 && fault_pass;
+  double attention_flops = 4.0 * batch * heads * static_cast<double>(sequence) * sequence * head_dim;
+
+  std::printf("version: FT-FlashAttention B200 tcgen05 TMEM softmax with ABFT score tiles and output projections\n");
+  std::printf("layout: Q/K/V=[B,H,N,D], FP16; O=FP32\n");
+  std::printf("shape: B=%d H=%d N=%d D=%d causal=0\n", batch, heads, sequence, head_dim);
+  std::printf("query_tile: 128, key_tile: 128\n");
+  std::printf("input_distribution: %s\n", dist.c_str());
+  std::printf("avg_no_fault_time_ms: %.6f\n", average_ms);
+  std::printf("approx_attention_tflops: %.6f\n", attention_flops / (average_ms * 1.0e9));
+  std::printf("metadata_prepare_time_ms: %.6f\n", metadata_ms);
+  std::printf("first_call_approx_time_ms: %.6f\n", metadata_ms + average_ms);
+  std::printf("fault_stage: %s\n", stage_name.c_str());
+  std::printf("fault_target: batch=%d head=%d query=%d index=%d delta=%+.6e\n", fault_batch, fault_head, fault_query, fault_index, fault_value);
+  std::printf("score_detected: %d\n", report.score_detected);
+  std::printf("score_corrected: %d\n", report.score_corrected);
+  std::printf("score_uncorrected: %d\n", report.score_uncorrected);
+  std::printf("score_checksum_noise_ratio: %.6e\n", report.max_score_noise);
+  std::printf("pv_detected: %d\n", report.pv_detected);
+  std::printf("pv_corrected: %d\n", report.pv_corrected);
+  std::printf("failed_rows: %d\n", report.failed_rows);
+  std::printf("verified_rows: %zu\n", rows_to_check);
+  std::printf("max_absolute_error: %.6e\n", max_absolute_error);
+  std::printf("max_tolerance_ratio: %.6e\n", max_tolerance_ratio);
+  std::printf("mismatches: %d\n", mismatches);
+  std::printf("verification: %s\n", passed ? "PASS" : "FAIL");
+  CLI_FT(ft_attention_fp16_abft_destroy(handle));
+  return passed ? 0 : 1;
+}

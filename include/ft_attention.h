@@ -95,6 +95,12 @@ int ft_attention_fp16_abft_report(ft_attn_handle* handle, ft_attn_report* out);
 
 int ft_attention_fp16_abft_destroy(ft_attn_handle* handle);
 
+/* Seeded FP16 inputs on the device.  dist 0: the grid ((mix(seed+i) % 17) - 8) / 16
+ * of the reference's attention generator (src/ft_flash_attention_a0.cu:231-238);
+ * dist 1: N(0, sigma^2).  The reference seeds Q, K, V with 0x12345678, 0x9abcdef0,
+ * 0x31415926 (a0:771-773). */
+int ft_attention_generate_f16(void* out_f16, size_t count, uint32_t seed, int dist, float sigma, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
