@@ -165,8 +165,21 @@ __device__ __forceinline__ void transpose_reduce(float (&v)[N], int lane) {
   }
 }
 
-__device__ __forceinline__ float load_element(const uint8_t* p) { return fp8_to_float(__ldg(p)); }
-__device__ __forceinline__ float load_element(const __half* p) { return __half2float(__ldg(p)); }
+constexpr int kExpChunk = 128;  // k per staged slice
+
+__device__ __forceinline__ float element_to_float(uint8_t v) { return fp8_to_float(v); }
+__device__ __forceinline__ float element_to_float(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* global_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(global_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // blockIdx.z walks independent problems of the same shape laid out back to back
 // (one per attention head); the GEMM path launches with gridDim.z = 1.
@@ -183,49 +196,69 @@ __global__ void __launch_bounds__(256) expected_checksums_kernel(const T* __rest
     expected += z * tiles64;
     scales += z * tiles64;
   }
-  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int row0 = blockIdx.x * 64 + warp * kExpRows;
-  int band0 = blockIdx.y * kExpBands;
-  const T* xr[kExpRows];
+  // Two-stage shared-memory ring over k: per stage the 64 x 128 slice of x and the
+  // 8 x 128 slices of the band sums and magnitudes, filled with 16-byte cp.async
+  // copies while the previous slice is consumed.
+  __shared__ __align__(16) T sx[2][64][kExpChunk];
+  __shared__ __align__(16) float sbs[2][kExpBands][kExpChunk];
+  __shared__ __align__(16) float sbm[2][kExpBands][kExpChunk];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * 64 + warp * kExpRows;
+  const int band0 = blockIdx.y * kExpBands;
+  constexpr int kXChunksPerRow = kExpChunk * static_cast<int>(sizeof(T)) / 16;
+  auto stage_copy = [&](int stage, int k0) {
 #pragma unroll
-  for (int r = 0; r < kExpRows; ++r) xr[r] = x + static_cast<size_t>(row0 + r) * k;
-  const float* bs[kExpBands];
-  const float* bm[kExpBands];
-#pragma unroll
-  for (int j = 0; j < kExpBands; ++j) {
-    int band = min(band0 + j, nbands - 1);
-    bs[j] = band_sums + static_cast<size_t>(band) * k;
-    bm[j] = band_mags + static_cast<size_t>(band) * k;
-  }
+    for (int i = threadIdx.x; i < 64 * kXChunksPerRow; i += 256) {
+      const int r = i / kXChunksPerRow, ch = i % kXChunksPerRow;
+      cp_async_16(reinterpret_cast<uint8_t*>(&sx[stage][r][0]) + ch * 16,
+                  reinterpret_cast<const uint8_t*>(x + static_cast<size_t>(blockIdx.x * 64 + r) * k + k0) + ch * 16);
+    }
+    {
+      const int j = threadIdx.x >> 5, ch = threadIdx.x & 31;  // 8 bands x 32 chunks of 4 floats
+      const size_t src = static_cast<size_t>(min(band0 + j, nbands - 1)) * k + k0 + ch * 4;
+      cp_async_16(&sbs[stage][j][ch * 4], band_sums + src);
+      cp_async_16(&sbm[stage][j][ch * 4], band_mags + src);
+    }
+    cp_async_commit();
+  };
   // v[0..63]: expected partials [r*8+j]; v[64..127]: scale partials
   float v[2 * kExpRows * kExpBands];
 #pragma unroll
   for (int i = 0; i < 2 * kExpRows * kExpBands; ++i) v[i] = 0.0f;
 
-#pragma unroll 2
-  for (int kk = lane; kk < k; kk += 32) {
-    float av[kExpRows], sv[kExpBands], mv[kExpBands];
-#pragma unroll
-    for (int r = 0; r < kExpRows; ++r) av[r] = load_element(xr[r] + kk);
-#pragma unroll
-    for (int j = 0; j < kExpBands; ++j) {
-      sv[j] = __ldg(bs[j] + kk);
-      mv[j] = __ldg(bm[j] + kk);
+  const int chunks = k / kExpChunk;
+  stage_copy(0, 0);
+  for (int c = 0; c < chunks; ++c) {
+    const int stage = c & 1;
+    if (c + 1 < chunks) {
+      stage_copy(stage ^ 1, (c + 1) * kExpChunk);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
+    __syncthreads();
 #pragma unroll
-    for (int r = 0; r < kExpRows; ++r) {
-      float aabs = fabsf(av[r]);
+    for (int it = 0; it < kExpChunk / 32; ++it) {  // lane l takes k = l (mod 32), ascending
+      const int kk = it * 32 + lane;
+      float av[kExpRows], sv[kExpBands], mv[kExpBands];
+#pragma unroll
+      for (int r = 0; r < kExpRows; ++r) av[r] = element_to_float(sx[stage][warp * kExpRows + r][kk]);
 #pragma unroll
       for (int j = 0; j < kExpBands; ++j) {
-        if (mode == 0) {
+        sv[j] = sbs[stage][j][kk];
+        mv[j] = sbm[stage][j][kk];
+      }
+#pragma unroll
+      for (int r = 0; r < kExpRows; ++r) {
+        const float aabs = fabsf(av[r]);
+#pragma unroll
+        for (int j = 0; j < kExpBands; ++j) {
           v[r * kExpBands + j] = __fmaf_rn(av[r], sv[j], v[r * kExpBands + j]);
           v[64 + r * kExpBands + j] = __fmaf_rn(aabs, mv[j], v[64 + r * kExpBands + j]);
-        } else {
-          v[r * kExpBands + j] = __fmaf_rn(sv[j], av[r], v[r * kExpBands + j]);
-          v[64 + r * kExpBands + j] = __fmaf_rn(mv[j], aabs, v[64 + r * kExpBands + j]);
         }
       }
     }
+    __syncthreads();  // the stage is refilled by the copy issued in the next iteration
   }
   transpose_reduce<2 * kExpRows * kExpBands>(v, lane);
   // lane holds original indices 4*lane + i
