@@ -41,10 +41,11 @@ struct TileDecision {
 };
 
 // Called by the two warps (64 threads) that own the tile's rows; `half` says
-// which 32 rows this warp holds, `pair` selects the named barrier (1 + pair).
+// which 32 rows this warp holds, `barrier_id` is the named barrier those two warps
+// (and nobody else) synchronise on.
 // `sc` must not be reused by the same warps before they have passed the barrier of
 // their NEXT call (callers alternate between two scratch areas).
-__device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane, int half, int pair, TileScratch& sc, float exp_row,
+__device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane, int half, int barrier_id, TileScratch& sc, float exp_row,
                                                         float scale_row, float exp_col0, float exp_col1, float scale_col0,
                                                         float scale_col1, float abs_tol, float rel_tol, float& max_ratio) {
   const int r_local = half * 32 + lane;
@@ -87,11 +88,7 @@ __device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane
     sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
     sc.rows[half].delta = first_delta;
   }
-  if (pair == 0) {
-    named_barrier_sync<1, 64>();
-  } else {
-    named_barrier_sync<2, 64>();
-  }
+  asm volatile("bar.sync %0, 64;" ::"r"(barrier_id) : "memory");
   const float col_delta0 = exp_col0 - (sc.colpart[0][lane] + sc.colpart[1][lane]);
   const float col_delta1 = exp_col1 - (sc.colpart[0][32 + lane] + sc.colpart[1][32 + lane]);
   const float col_thr0 = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_col0), abs_tol);

@@ -3,21 +3,23 @@
 //
 // Replaces the reference's fused attention kernels (final form
 // src/ft_flash_attention_a14.cu:659-1201) and its metadata kernels (a14:303-316,
-// 571-621).  One CTA owns 128 queries of one (batch, head) and streams 128-key
-// tiles:
-//   warp 0   TMA producer: Q once, K and V^T tiles through two-stage rings;
-//   warp 1   one thread issues tcgen05.mma kind::f16: S_j = Q K_j^T into one of two
-//            128-column TMEM buffers, O += P_j V_j into a third;
-//   warps 2-5 one thread per query row.  Pass 1 over S_j: the 64x64 ABFT tile
-//            verifier of the GEMM epilogue (abft_tile_check.cuh) on both 64-column
-//            halves, corrected scores written back to TMEM, row maximum.  Then the
-//            online-softmax rescale of O in TMEM.  Pass 2: P = exp2(...) rounded to
-//            FP16 into shared memory in the MMA's swizzled layout, while the
-//            expected output projections  sum_j p_j * vsum_j  and
-//            sum_j p_j * vweighted_j  are accumulated (src/ft_flash_attention_a0.cu:
-//            585-611).  After the last tile the output row is checked against those
-//            projections, a single faulty element located and corrected
-//            (a0:613-662), normalised and stored.
+// 571-621).  One CTA owns 256 queries of one (batch, head) as two 128-query tiles
+// A and B that share every 128-key K / V^T tile:
+//   warpgroup 0  warp 0: TMA producer (Q once, K and V^T tiles); warp 1: one thread
+//                issues tcgen05.mma kind::f16 -- S_A, S_B = Q_{A,B} K_j^T into two
+//                128-column TMEM buffers, O_{A,B} += P_{A,B} V_j into two more;
+//                the group gives most of its registers away (setmaxnreg);
+//   warpgroups 1, 2  softmax / verifier of tile A and of tile B, one thread per
+//                query row, running concurrently.  Pass 1 over S_j: the 64x64 ABFT
+//                tile verifier of the GEMM epilogue (abft_tile_check.cuh) on both
+//                64-column halves, corrected scores written back to TMEM, row
+//                maximum.  Then the online-softmax rescale of O in TMEM.  Pass 2:
+//                P = exp2(...) rounded to FP16 into shared memory in the MMA's
+//                swizzled layout, while the expected output projections
+//                sum_j p_j * vsum_j and sum_j p_j * vweighted_j are accumulated
+//                (src/ft_flash_attention_a0.cu:585-611).  After the last tile the
+//                output row is checked against those projections, a single faulty
+//                element located and corrected (a0:613-662), normalised and stored.
 // Every wait is bounded; on expiry the kernel reports status and leaves.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -30,25 +32,26 @@
 
 namespace ftg {
 
-constexpr int kAttnTile = 128;             // queries per CTA, keys per tile, head dimension
+constexpr int kAttnTile = 128;             // queries per tile, keys per tile, head dimension
+constexpr int kAttnQTiles = 2;             // query tiles per CTA
 constexpr int kAttnSlabBytes = 128 * 128;  // 128 rows x 64 FP16 (one 128-byte swizzle row each)
 constexpr int kAttnTileBytes = 2 * kAttnSlabBytes;
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 384;
 constexpr uint64_t kAttnTimeoutNs = 2000000000ull;
-constexpr uint32_t kTmemS = 0;    // two score buffers at columns 0 and 128
-constexpr uint32_t kTmemO = 256;  // output accumulator
+constexpr uint32_t kTmemS = 0;    // score buffers of tile A, B at columns 0, 128
+constexpr uint32_t kTmemO = 256;  // output accumulators of tile A, B at columns 256, 384
 
 struct AttnShared {
-  uint64_t q_full;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, p_empty;
+  uint64_t q_full, k_full, k_empty, v_full, v_empty;
+  uint64_t s_full[kAttnQTiles], s_empty[kAttnQTiles];
+  uint64_t p_full[kAttnQTiles], p_empty[kAttnQTiles];
   uint32_t tmem_base;
   int abort_flag;
-  float2 v_meta[2][kAttnTile];  // per key of the current tile: {sum_d V, sum_d w_d V}
-  TileScratch scratch[2][2];  // [row pair][parity]
+  float2 v_meta[kAttnQTiles][2][kAttnTile];  // [query tile][parity][key]: {sum_d V, sum_d w_d V}
+  TileScratch scratch[kAttnQTiles][2][2];    // [query tile][row pair][parity]
 };
 
+// Q (2 tiles), K, V^T, P (2 tiles)
 constexpr int kAttnSmemBytes = 6 * kAttnTileBytes + static_cast<int>(sizeof(AttnShared)) + 1024;
 
 // ---------------------------------------------------------------------------
@@ -86,395 +89,6 @@ cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* 
   dim3 grid(seq / 32, batch_heads);
   attn_prepare_v_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(v), static_cast<__half*>(vt), v_sum, v_weighted, seq);
   return cudaGetLastError();
-}
-
-// ---------------------------------------------------------------------------
-// forward kernel
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ bool attn_any(bool flag) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %1, 0;\n\t"
-      "barrier.cta.red.or.pred q, 3, 128, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(out)
-      : "r"(static_cast<uint32_t>(flag))
-      : "memory");
-  return out != 0;
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// One thread of the 128 polls; the others sleep in the hardware barrier.  Returns
-// false (for all 128) when the wait was abandoned.
-__device__ __forceinline__ bool attn_wait_all(uint64_t* bar, uint32_t parity, volatile int* abort_flag, bool poller) {
-  bool ok = true;
-  if (poller) ok = mbar_wait_bounded(bar, parity, abort_flag, kAttnTimeoutNs);
-  return !attn_any(!ok);
-}
-
-// Adds `value` to one element of a TMEM column in place; executed by the whole
-// warp that owns the row's lane quarter.
-__device__ __forceinline__ void tmem_add_to_element(uint32_t taddr_column, int lane, int target_lane, float value) {
-  float x;
-  tmem_ld_32x32b_x1(taddr_column, x);
-  tmem_wait_ld();
-  if (lane == target_lane) x += value;
-  tmem_st_32x32b_x1(taddr_column, x);
-  tmem_wait_st();
-}
-
-__global__ void __launch_bounds__(kAttnThreads, 1)
-ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                        const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* smem_q = smem;
-  uint8_t* smem_k = smem + kAttnTileBytes;       // 2 stages
-  uint8_t* smem_v = smem + 3 * kAttnTileBytes;   // 2 stages
-  uint8_t* smem_p = smem + 5 * kAttnTileBytes;
-  AttnShared& sh = *reinterpret_cast<AttnShared*>(smem + 6 * kAttnTileBytes);
-  volatile int* abort_flag = &sh.abort_flag;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int bh = blockIdx.y;
-  const int q0 = blockIdx.x * kAttnTile;
-  const int seq = p.seq;
-  const int num_tiles = seq / kAttnTile;
-  const int row_base = bh * seq;  // first row of this head in the [B*H*N, D] matrices
-
-  if (threadIdx.x == 0) {
-    mbar_init(&sh.q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&sh.k_full[s], 1);
-      mbar_init(&sh.k_empty[s], 1);
-      mbar_init(&sh.v_full[s], 1);
-      mbar_init(&sh.v_empty[s], 1);
-      mbar_init(&sh.s_full[s], 1);
-      mbar_init(&sh.s_empty[s], 128);
-    }
-    mbar_init(&sh.p_full, 128);
-    mbar_init(&sh.p_empty, 1);
-    sh.abort_flag = 0;
-    fence_barrier_init();
-    prefetch_tensormap(&tmap_q);
-    prefetch_tensormap(&tmap_k);
-    prefetch_tensormap(&tmap_vt);
-  }
-  if (warp == 1) {
-    tmem_alloc(&sh.tmem_base, 512);
-    tmem_relinquish();
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  tcgen05_fence_after();
-  const uint32_t tmem_base = sh.tmem_base;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------- producer
-    if (lane == 0) {
-      mbar_arrive_expect_tx(&sh.q_full, kAttnTileBytes);
-      tma_load_2d(smem_q, &tmap_q, &sh.q_full, 0, row_base + q0);
-      tma_load_2d(smem_q + kAttnSlabBytes, &tmap_q, &sh.q_full, 64, row_base + q0);
-      for (int j = 0; j < num_tiles; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait_bounded(&sh.k_empty[st], ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
-        mbar_arrive_expect_tx(&sh.k_full[st], kAttnTileBytes);
-        tma_load_2d(smem_k + st * kAttnTileBytes, &tmap_k, &sh.k_full[st], 0, row_base + j * kAttnTile);
-        tma_load_2d(smem_k + st * kAttnTileBytes + kAttnSlabBytes, &tmap_k, &sh.k_full[st], 64, row_base + j * kAttnTile);
-        if (!mbar_wait_bounded(&sh.v_empty[st], ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
-        mbar_arrive_expect_tx(&sh.v_full[st], kAttnTileBytes);
-        tma_load_2d(smem_v + st * kAttnTileBytes, &tmap_vt, &sh.v_full[st], j * kAttnTile, bh * kAttnTile);
-        tma_load_2d(smem_v + st * kAttnTileBytes + kAttnSlabBytes, &tmap_vt, &sh.v_full[st], j * kAttnTile + 64, bh * kAttnTile);
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16_f32(kAttnTile, kAttnTile);
-      bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kAttnTimeoutNs);
-      for (int j = 0; j <= num_tiles && alive; ++j) {
-        if (j < num_tiles) {  // S_j = Q K_j^T
-          const int st = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
-          if (!mbar_wait_bounded(&sh.k_full[st], ph, abort_flag, kAttnTimeoutNs) ||
-              !mbar_wait_bounded(&sh.s_empty[st], ph ^ 1, abort_flag, kAttnTimeoutNs)) {
-            alive = false;
-            break;
-          }
-          tcgen05_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            uint64_t da = make_smem_desc_sw128(smem_u32(smem_q + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
-            uint64_t db = make_smem_desc_sw128(smem_u32(smem_k + st * kAttnTileBytes + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
-            umma_f16(tmem_base + kTmemS + st * kAttnTile, da, db, idesc, kk != 0 ? 1u : 0u);
-          }
-          umma_commit(&sh.k_empty[st]);
-          umma_commit(&sh.s_full[st]);
-        }
-        if (j > 0) {  // O += P_i V_i for the previous tile
-          const int i = j - 1;
-          const int st = i & 1;
-          const uint32_t ph = (i >> 1) & 1;
-          if (!mbar_wait_bounded(&sh.p_full, i & 1, abort_flag, kAttnTimeoutNs) ||
-              !mbar_wait_bounded(&sh.v_full[st], ph, abort_flag, kAttnTimeoutNs)) {
-            alive = false;
-            break;
-          }
-          tcgen05_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            uint64_t da = make_smem_desc_sw128(smem_u32(smem_p + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
-            uint64_t db = make_smem_desc_sw128(smem_u32(smem_v + st * kAttnTileBytes + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
-            umma_f16(tmem_base + kTmemO, da, db, idesc, (i | kk) != 0 ? 1u : 0u);
-          }
-          umma_commit(&sh.v_empty[st]);
-          umma_commit(&sh.p_empty);
-        }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------- softmax / verifier: one thread per query row
-    const int quarter = warp & 3;
-    const int pair = quarter >> 1;
-    const int half = quarter & 1;
-    const int r_local = half * 32 + lane;
-    const int row_in_cta = quarter * 32 + lane;
-    const bool poller = warp == 2 && lane == 0;
-    const int tile_cols = seq / 64;
-    const size_t head_cache = static_cast<size_t>(bh) * tile_cols * tile_cols * 64;
-    const int q_band = q0 / 64 + pair;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const bool fault_here = p.fault_bh == bh && p.fault_query >= q0 && p.fault_query < q0 + kAttnTile;
-    const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE;
-    const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT;
-    const int fault_row = p.fault_query - q0;  // row in this CTA, when fault_here
-
-    float m_run = -INFINITY, l_run = 0.0f, exp_sum = 0.0f, exp_weighted = 0.0f, max_ratio = 0.0f;
-    bool alive = true;
-
-    for (int j = 0; j < num_tiles; ++j) {
-      const int buf = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      {  // per-key sums of V for this tile (read in pass 2; published by the barrier inside the wait below)
-        const int t = threadIdx.x - 64;
-        sh.v_meta[buf][t] = make_float2(__ldg(p.v_sum + static_cast<size_t>(bh) * seq + j * kAttnTile + t),
-                                        __ldg(p.v_weighted + static_cast<size_t>(bh) * seq + j * kAttnTile + t));
-      }
-      // cached expected checksums of the four 64x64 tiles this thread takes part in: fetched before the wait
-      float exp_row[2], scale_row[2], exp_col0[2], exp_col1[2], scale_col0[2], scale_col1[2];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
-        exp_row[c] = __ldg(p.expected_rows + cache + r_local);
-        scale_row[c] = __ldg(p.row_scales + cache + r_local);
-        exp_col0[c] = __ldg(p.expected_cols + cache + lane);
-        exp_col1[c] = __ldg(p.expected_cols + cache + 32 + lane);
-        scale_col0[c] = __ldg(p.col_scales + cache + lane);
-        scale_col1[c] = __ldg(p.col_scales + cache + 32 + lane);
-      }
-      if (!attn_wait_all(&sh.s_full[buf], ph, abort_flag, poller)) {
-        alive = false;
-        break;
-      }
-      tcgen05_fence_after();
-      const uint32_t s_addr = lane_addr + kTmemS + buf * kAttnTile;
-
-      // test hook: the fault enters the accumulator itself, before any checksum
-      if (score_fault && p.fault_index / kAttnTile == j && fault_row / 32 == quarter) {
-        tmem_add_to_element(s_addr + p.fault_index % kAttnTile, lane, fault_row % 32, p.fault_value);
-      }
-
-      // ---- pass 1: verify both 64x64 score tiles of this thread's band, track the row maximum
-      float row_max = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int key_band = j * 2 + c;
-        float v[64];
-        tmem_ld_32x32b_x32(s_addr + c * 64, v);
-        tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
-        tmem_wait_ld();
-        TileDecision d = abft_check_tile(v, lane, half, pair, sh.scratch[pair][c], exp_row[c], scale_row[c], exp_col0[c], exp_col1[c],
-                                         scale_col0[c], scale_col1[c], p.score_abs_tol, p.score_rel_tol, max_ratio);
-        if ((d.bad_rows | d.bad_cols) != 0) {
-          if (d.corrected && d.bad_row / 32 == half) {
-            // the corrected score must also be what pass 2 reads back
-            tmem_add_to_element(s_addr + c * 64 + d.bad_col, lane, d.bad_row % 32, 0.5f * (d.row_delta + d.col_delta));
-          }
-          if (half == 0 && lane == 0) {
-            atomicAdd(&p.report->score_detected, 1);
-            atomicAdd(d.corrected ? &p.report->score_corrected : &p.report->score_uncorrected, 1);
-            int slot = atomicAdd(&p.report->record_count, 1);
-            if (slot < 16) {
-              ft_tile_record rec;
-              rec.tile = (bh * tile_cols + q_band) * tile_cols + key_band;
-              rec.bad_row_count = d.bad_rows;
-              rec.bad_col_count = d.bad_cols;
-              rec.bad_row = d.bad_row;
-              rec.bad_col = d.bad_col;
-              rec.row_delta = d.row_delta;
-              rec.col_delta = d.col_delta;
-              rec.corrected = d.corrected ? 1 : 0;
-              p.report->records[slot] = rec;
-            }
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, v[i]);
-      }
-
-      // ---- online softmax state (log2 domain)
-      const float m_new = fmaxf(m_run, row_max * p.scale_log2);
-      const float alpha = fast_exp2(m_run - m_new);  // 0 for the first tile (m_run = -inf)
-
-      if (j > 0) {
-        // PV of the previous tile must have finished: the P buffer is free and O is quiescent
-        if (!attn_wait_all(&sh.p_empty, (j - 1) & 1, abort_flag, poller)) {
-          alive = false;
-          break;
-        }
-        tcgen05_fence_after();
-        if (__any_sync(0xffffffffU, alpha != 1.0f)) {
-#pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
-            float o[32];
-            tmem_ld_32x32b_x32(lane_addr + kTmemO + cc * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st_32x32b_x32(lane_addr + kTmemO + cc * 32, o);
-          }
-          tmem_wait_st();
-        }
-      }
-
-      // ---- pass 2: probabilities, FP16 P tile for the MMA, expected output projections
-      float l_tile = 0.0f, es_tile = 0.0f, ew_tile = 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[64];
-        tmem_ld_32x32b_x32(s_addr + c * 64, v);
-        tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
-        tmem_wait_ld();
-        if (c == 1) {  // both halves are in registers: the score buffer can be overwritten by S_{j+2}
-          tcgen05_fence_before();
-          mbar_arrive(&sh.s_empty[buf]);
-        }
-        uint8_t* p_row = smem_p + c * kAttnSlabBytes + (row_in_cta >> 3) * 1024 + (row_in_cta & 7) * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint32_t packed[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i0 = ch * 8 + 2 * e;
-            const float p0 = fast_exp2(__fmaf_rn(v[i0], p.scale_log2, -m_new));
-            const float p1 = fast_exp2(__fmaf_rn(v[i0 + 1], p.scale_log2, -m_new));
-            l_tile += p0;
-            l_tile += p1;
-            const __half2 h = __floats2half2_rn(p0, p1);
-            const float2 r = __half22float2(h);  // what the MMA will multiply by V
-            const float4 meta = *reinterpret_cast<const float4*>(&sh.v_meta[buf][c * 64 + i0]);  // two keys
-            es_tile = __fmaf_rn(r.x, meta.x, es_tile);
-            es_tile = __fmaf_rn(r.y, meta.z, es_tile);
-            ew_tile = __fmaf_rn(r.x, meta.y, ew_tile);
-            ew_tile = __fmaf_rn(r.y, meta.w, ew_tile);
-            packed[e] = *reinterpret_cast<const uint32_t*>(&h);
-          }
-          // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-          *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_cta & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        }
-      }
-      l_run = __fmaf_rn(alpha, l_run, l_tile);
-      exp_sum = __fmaf_rn(alpha, exp_sum, es_tile);
-      exp_weighted = __fmaf_rn(alpha, exp_weighted, ew_tile);
-      m_run = m_new;
-      fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
-      tcgen05_fence_before();
-      mbar_arrive(&sh.p_full);
-    }
-
-    // ---- output stage: projection check of O / l (src/ft_flash_attention_a0.cu:613-662), normalise, store
-    if (alive && attn_wait_all(&sh.p_empty, (num_tiles - 1) & 1, abort_flag, poller)) {
-      tcgen05_fence_after();
-      const float inv_l = 1.0f / l_run;
-      const int query = q0 + row_in_cta;
-      const bool my_fault = output_fault && fault_row == row_in_cta;
-      float actual_sum = 0.0f, actual_weighted = 0.0f;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        float o[32];
-        tmem_ld_32x32b_x32(lane_addr + kTmemO + cc * 32, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = o[i] * inv_l;
-          if (my_fault && p.fault_index == cc * 32 + i) x += p.fault_value;
-          actual_sum += x;
-          actual_weighted = __fmaf_rn(static_cast<float>(2 * (cc * 32 + i) - (kAttnTile - 1)), x, actual_weighted);
-        }
-      }
-      const float expected_sum = exp_sum * inv_l;
-      const float expected_weighted = exp_weighted * inv_l;
-      const float delta_sum = actual_sum - expected_sum;
-      const float delta_weighted = actual_weighted - expected_weighted;
-      const float thr_sum = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_sum)), p.pv_abs_tol);
-      const float thr_weighted = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_weighted)), p.pv_abs_tol);
-      int recover_dim = -1;
-      if (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted) {
-        atomicAdd(&p.report->pv_detected, 1);
-        if (fabsf(delta_sum) > thr_sum) {
-          const float observed_weight = delta_weighted / delta_sum;
-          const int dim = __float2int_rn(0.5f * (observed_weight + static_cast<float>(kAttnTile - 1)));
-          if (dim >= 0 && dim < kAttnTile && fabsf(observed_weight - static_cast<float>(2 * dim - (kAttnTile - 1))) <= 0.25f) {
-            recover_dim = dim;
-            atomicAdd(&p.report->pv_corrected, 1);
-          }
-        }
-        if (recover_dim < 0) atomicAdd(&p.report->failed_rows, 1);
-      }
-      float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kAttnTile;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        float o[32];
-        tmem_ld_32x32b_x32(lane_addr + kTmemO + cc * 32, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = o[i] * inv_l;
-          if (my_fault && p.fault_index == cc * 32 + i) x += p.fault_value;
-          if (recover_dim == cc * 32 + i) x -= delta_sum;
-          o[i] = x;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
-        }
-      }
-    }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) max_ratio = fmaxf(max_ratio, __shfl_xor_sync(0xffffffffU, max_ratio, off));
-    if (lane == 0) atomicMax(&p.report->max_noise_bits, __float_as_int(max_ratio));
-  }
-
-  // ------------------------------------------------------------------- teardown
-  tcgen05_fence_before();
-  __syncthreads();
-  if (sh.abort_flag != 0) {
-    if (threadIdx.x == 0) atomicExch(&p.report->status, 1);
-    for (int i = 0; i < 64; ++i) __nanosleep(20000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tcgen05_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
 }
 
 // Seeded FP16 inputs.  dist 0: the reference attention generator's grid
@@ -518,13 +132,422 @@ cudaError_t launch_generate_f16(void* out, size_t count, uint32_t seed, int dist
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// forward kernel helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// OR of `flag` over the 128 threads of one softmax warpgroup (named barrier `id`).
+__device__ __forceinline__ bool attn_any(bool flag, int id) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, %2, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(flag)), "r"(id)
+      : "memory");
+  return out != 0;
+}
+
+// One thread of the warpgroup polls; the others sleep in the hardware barrier.
+// Returns false (for all 128) when the wait was abandoned.
+__device__ __forceinline__ bool attn_wait_all(uint64_t* bar, uint32_t parity, volatile int* abort_flag, bool poller, int id) {
+  bool ok = true;
+  if (poller) ok = mbar_wait_bounded(bar, parity, abort_flag, kAttnTimeoutNs);
+  return !attn_any(!ok, id);
+}
+
+// Adds `value` to one element of a TMEM column in place; executed by the whole
+// warp that owns the row's lane quarter.
+__device__ __forceinline__ void tmem_add_to_element(uint32_t taddr_column, int lane, int target_lane, float value) {
+  float x;
+  tmem_ld_32x32b_x1(taddr_column, x);
+  tmem_wait_ld();
+  if (lane == target_lane) x += value;
+  tmem_st_32x32b_x1(taddr_column, x);
+  tmem_wait_st();
+}
+
+template <int Regs>
+__device__ __forceinline__ void reg_release() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Regs));
+}
+template <int Regs>
+__device__ __forceinline__ void reg_acquire() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Regs));
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smem_q = smem;                       // 2 query tiles
+  uint8_t* smem_k = smem + 2 * kAttnTileBytes;  // 1 stage
+  uint8_t* smem_v = smem + 3 * kAttnTileBytes;  // 1 stage
+  uint8_t* smem_p = smem + 4 * kAttnTileBytes;  // 2 query tiles
+  AttnShared& sh = *reinterpret_cast<AttnShared*>(smem + 6 * kAttnTileBytes);
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int group = warp >> 2;  // 0: producer + MMA, 1 and 2: softmax of query tile A and B
+  const int bh = blockIdx.y;
+  const int q0 = blockIdx.x * kAttnQTiles * kAttnTile;
+  const int seq = p.seq;
+  const int num_tiles = seq / kAttnTile;
+  const int row_base = bh * seq;  // first row of this head in the [B*H*N, D] matrices
+  const int qtiles = q0 + kAttnQTiles * kAttnTile <= seq ? kAttnQTiles : 1;  // the last CTA of a head may own one tile
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh.q_full, 1);
+    mbar_init(&sh.k_full, 1);
+    mbar_init(&sh.k_empty, 1);
+    mbar_init(&sh.v_full, 1);
+    mbar_init(&sh.v_empty, 1);
+    for (int t = 0; t < kAttnQTiles; ++t) {
+      mbar_init(&sh.s_full[t], 1);
+      mbar_init(&sh.s_empty[t], 128);
+      mbar_init(&sh.p_full[t], 128);
+      mbar_init(&sh.p_empty[t], 1);
+    }
+    sh.abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_vt);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (group == 0) {
+    reg_release<40>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------- producer
+      mbar_arrive_expect_tx(&sh.q_full, qtiles * kAttnTileBytes);
+      for (int t = 0; t < qtiles; ++t) {
+        tma_load_2d(smem_q + t * kAttnTileBytes, &tmap_q, &sh.q_full, 0, row_base + q0 + t * kAttnTile);
+        tma_load_2d(smem_q + t * kAttnTileBytes + kAttnSlabBytes, &tmap_q, &sh.q_full, 64, row_base + q0 + t * kAttnTile);
+      }
+      for (int j = 0; j < num_tiles; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait_bounded(&sh.k_empty, ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
+        mbar_arrive_expect_tx(&sh.k_full, kAttnTileBytes);
+        tma_load_2d(smem_k, &tmap_k, &sh.k_full, 0, row_base + j * kAttnTile);
+        tma_load_2d(smem_k + kAttnSlabBytes, &tmap_k, &sh.k_full, 64, row_base + j * kAttnTile);
+        if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
+        mbar_arrive_expect_tx(&sh.v_full, kAttnTileBytes);
+        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kAttnTile, bh * kAttnTile);
+        tma_load_2d(smem_v + kAttnSlabBytes, &tmap_vt, &sh.v_full, j * kAttnTile + 64, bh * kAttnTile);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc_f16_f32(kAttnTile, kAttnTile);
+      bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kAttnTimeoutNs);
+      for (int j = 0; j <= num_tiles && alive; ++j) {
+        if (j < num_tiles) {  // S_A, S_B = Q_{A,B} K_j^T
+          if (!mbar_wait_bounded(&sh.k_full, j & 1, abort_flag, kAttnTimeoutNs)) break;
+          for (int t = 0; t < qtiles && alive; ++t) {
+            // the score buffer of tile t is free once its softmax group has read S_{j-1} twice
+            if (!mbar_wait_bounded(&sh.s_empty[t], (j & 1) ^ 1, abort_flag, kAttnTimeoutNs)) {
+              alive = false;
+              break;
+            }
+            tcgen05_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              uint64_t da = make_smem_desc_sw128(smem_u32(smem_q + t * kAttnTileBytes + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
+              uint64_t db = make_smem_desc_sw128(smem_u32(smem_k + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
+              umma_f16(tmem_base + kTmemS + t * kAttnTile, da, db, idesc, kk != 0 ? 1u : 0u);
+            }
+            umma_commit(&sh.s_full[t]);
+          }
+          if (!alive) break;
+          umma_commit(&sh.k_empty);
+        }
+        if (j > 0) {  // O_{A,B} += P_i V_i for the previous key tile
+          const int i = j - 1;
+          if (!mbar_wait_bounded(&sh.v_full, i & 1, abort_flag, kAttnTimeoutNs)) break;
+          for (int t = 0; t < qtiles && alive; ++t) {
+            if (!mbar_wait_bounded(&sh.p_full[t], i & 1, abort_flag, kAttnTimeoutNs)) {
+              alive = false;
+              break;
+            }
+            tcgen05_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              uint64_t da = make_smem_desc_sw128(smem_u32(smem_p + t * kAttnTileBytes + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
+              uint64_t db = make_smem_desc_sw128(smem_u32(smem_v + (kk >> 2) * kAttnSlabBytes)) + 2 * (kk & 3);
+              umma_f16(tmem_base + kTmemO + t * kAttnTile, da, db, idesc, (i | kk) != 0 ? 1u : 0u);
+            }
+            umma_commit(&sh.p_empty[t]);
+          }
+          if (!alive) break;
+          umma_commit(&sh.v_empty);
+        }
+      }
+    }
+  } else {
+    reg_acquire<224>();
+    // ------------------------------------------------------------- softmax / verifier: one thread per query row
+    const int t = group - 1;  // query tile of this warpgroup
+    if (t < qtiles) {
+      const int quarter = warp & 3;
+      const int pair = quarter >> 1;
+      const int half = quarter & 1;
+      const int r_local = half * 32 + lane;
+      const int row_in_tile = quarter * 32 + lane;
+      const int tg = threadIdx.x & 127;
+      const bool poller = tg == 0;
+      const int bar_all = 3 + 3 * t;          // 128-thread barrier of this warpgroup
+      const int bar_pair = 1 + 3 * t + pair;  // 64-thread barrier of this 64-row band
+      const int tile_cols = seq / 64;
+      const size_t head_cache = static_cast<size_t>(bh) * tile_cols * tile_cols * 64;
+      const int q_tile0 = q0 + t * kAttnTile;
+      const int q_band = q_tile0 / 64 + pair;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t s_addr = lane_addr + kTmemS + t * kAttnTile;
+      const uint32_t o_addr = lane_addr + kTmemO + t * kAttnTile;
+      uint8_t* p_tile = smem_p + t * kAttnTileBytes;
+      const bool fault_here = p.fault_bh == bh && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kAttnTile;
+      const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE;
+      const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT;
+      const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
+
+      float m_run = -INFINITY, l_run = 0.0f, exp_sum = 0.0f, exp_weighted = 0.0f, max_ratio = 0.0f;
+      bool alive = true;
+
+      for (int j = 0; j < num_tiles; ++j) {
+        const int buf = j & 1;
+        // per-key sums of V for this tile (read in pass 2; published by the barrier inside the wait below)
+        sh.v_meta[t][buf][tg] = make_float2(__ldg(p.v_sum + static_cast<size_t>(bh) * seq + j * kAttnTile + tg),
+                                            __ldg(p.v_weighted + static_cast<size_t>(bh) * seq + j * kAttnTile + tg));
+        // cached expected checksums of the four 64x64 tiles this thread takes part in: fetched before the wait
+        float exp_row[2], scale_row[2], exp_col0[2], exp_col1[2], scale_col0[2], scale_col1[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
+          exp_row[c] = __ldg(p.expected_rows + cache + r_local);
+          scale_row[c] = __ldg(p.row_scales + cache + r_local);
+          exp_col0[c] = __ldg(p.expected_cols + cache + lane);
+          exp_col1[c] = __ldg(p.expected_cols + cache + 32 + lane);
+          scale_col0[c] = __ldg(p.col_scales + cache + lane);
+          scale_col1[c] = __ldg(p.col_scales + cache + 32 + lane);
+        }
+        if (!attn_wait_all(&sh.s_full[t], j & 1, abort_flag, poller, bar_all)) {
+          alive = false;
+          break;
+        }
+        tcgen05_fence_after();
+
+        // test hook: the fault enters the accumulator itself, before any checksum
+        if (score_fault && p.fault_index / kAttnTile == j && fault_row / 32 == quarter) {
+          tmem_add_to_element(s_addr + p.fault_index % kAttnTile, lane, fault_row % 32, p.fault_value);
+        }
+
+        // ---- pass 1: verify both 64x64 score tiles of this thread's band, track the row maximum
+        float row_max = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int key_band = j * 2 + c;
+          float v[64];
+          tmem_ld_32x32b_x32(s_addr + c * 64, v);
+          tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
+          tmem_wait_ld();
+          TileDecision d = abft_check_tile(v, lane, half, bar_pair, sh.scratch[t][pair][c], exp_row[c], scale_row[c], exp_col0[c],
+                                           exp_col1[c], scale_col0[c], scale_col1[c], p.score_abs_tol, p.score_rel_tol, max_ratio);
+          if ((d.bad_rows | d.bad_cols) != 0) {
+            if (d.corrected && d.bad_row / 32 == half) {
+              // the corrected score must also be what pass 2 reads back
+              tmem_add_to_element(s_addr + c * 64 + d.bad_col, lane, d.bad_row % 32, 0.5f * (d.row_delta + d.col_delta));
+            }
+            if (half == 0 && lane == 0) {
+              atomicAdd(&p.report->score_detected, 1);
+              atomicAdd(d.corrected ? &p.report->score_corrected : &p.report->score_uncorrected, 1);
+              int slot = atomicAdd(&p.report->record_count, 1);
+              if (slot < 16) {
+                ft_tile_record rec;
+                rec.tile = (bh * tile_cols + q_band) * tile_cols + key_band;
+                rec.bad_row_count = d.bad_rows;
+                rec.bad_col_count = d.bad_cols;
+                rec.bad_row = d.bad_row;
+                rec.bad_col = d.bad_col;
+                rec.row_delta = d.row_delta;
+                rec.col_delta = d.col_delta;
+                rec.corrected = d.corrected ? 1 : 0;
+                p.report->records[slot] = rec;
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, v[i]);
+        }
+
+        // ---- online softmax state (log2 domain)
+        const float m_new = fmaxf(m_run, row_max * p.scale_log2);
+        const float alpha = fast_exp2(m_run - m_new);  // 0 for the first tile (m_run = -inf)
+
+        if (j > 0) {
+          // PV of the previous tile must have finished: the P buffer is free and O is quiescent
+          if (!attn_wait_all(&sh.p_empty[t], (j - 1) & 1, abort_flag, poller, bar_all)) {
+            alive = false;
+            break;
+          }
+          tcgen05_fence_after();
+          if (__any_sync(0xffffffffU, alpha != 1.0f)) {
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+              float o[32];
+              tmem_ld_32x32b_x32(o_addr + cc * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tmem_st_32x32b_x32(o_addr + cc * 32, o);
+            }
+            tmem_wait_st();
+          }
+        }
+        // ---- pass 2: probabilities, FP16 P tile for the MMA, expected output projections
+        float l_tile = 0.0f, es_tile = 0.0f, ew_tile = 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          float v[64];
+          tmem_ld_32x32b_x32(s_addr + c * 64, v);
+          tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
+          tmem_wait_ld();
+          if (c == 1) {  // both halves are in registers: the score buffer can take S of the next key tile
+            tcgen05_fence_before();
+            mbar_arrive(&sh.s_empty[t]);
+          }
+          uint8_t* p_row = p_tile + c * kAttnSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i0 = ch * 8 + 2 * e;
+              const float p0 = fast_exp2(__fmaf_rn(v[i0], p.scale_log2, -m_new));
+              const float p1 = fast_exp2(__fmaf_rn(v[i0 + 1], p.scale_log2, -m_new));
+              l_tile += p0;
+              l_tile += p1;
+              const __half2 h = __floats2half2_rn(p0, p1);
+              const float2 r = __half22float2(h);  // what the MMA will multiply by V
+              const float4 meta = *reinterpret_cast<const float4*>(&sh.v_meta[t][buf][c * 64 + i0]);  // two keys
+              es_tile = __fmaf_rn(r.x, meta.x, es_tile);
+              es_tile = __fmaf_rn(r.y, meta.z, es_tile);
+              ew_tile = __fmaf_rn(r.x, meta.y, ew_tile);
+              ew_tile = __fmaf_rn(r.y, meta.w, ew_tile);
+              packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+            *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+        l_run = __fmaf_rn(alpha, l_run, l_tile);
+        exp_sum = __fmaf_rn(alpha, exp_sum, es_tile);
+        exp_weighted = __fmaf_rn(alpha, exp_weighted, ew_tile);
+        m_run = m_new;
+        fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
+        tcgen05_fence_before();
+        mbar_arrive(&sh.p_full[t]);
+      }
+      // ---- output stage: projection check of O / l (src/ft_flash_attention_a0.cu:613-662), normalise, store
+      if (alive && attn_wait_all(&sh.p_empty[t], (num_tiles - 1) & 1, abort_flag, poller, bar_all)) {
+        tcgen05_fence_after();
+        const float inv_l = 1.0f / l_run;
+        const int query = q_tile0 + row_in_tile;
+        const bool my_fault = output_fault && fault_row == row_in_tile;
+        float actual_sum = 0.0f, actual_weighted = 0.0f;
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          float o[32];
+          tmem_ld_32x32b_x32(o_addr + cc * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = o[i] * inv_l;
+            if (my_fault && p.fault_index == cc * 32 + i) x += p.fault_value;
+            actual_sum += x;
+            actual_weighted = __fmaf_rn(static_cast<float>(2 * (cc * 32 + i) - (kAttnTile - 1)), x, actual_weighted);
+          }
+        }
+        const float expected_sum = exp_sum * inv_l;
+        const float expected_weighted = exp_weighted * inv_l;
+        const float delta_sum = actual_sum - expected_sum;
+        const float delta_weighted = actual_weighted - expected_weighted;
+        const float thr_sum = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_sum)), p.pv_abs_tol);
+        const float thr_weighted = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_weighted)), p.pv_abs_tol);
+        int recover_dim = -1;
+        if (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted) {
+          atomicAdd(&p.report->pv_detected, 1);
+          if (fabsf(delta_sum) > thr_sum) {
+            const float observed_weight = delta_weighted / delta_sum;
+            const int dim = __float2int_rn(0.5f * (observed_weight + static_cast<float>(kAttnTile - 1)));
+            if (dim >= 0 && dim < kAttnTile && fabsf(observed_weight - static_cast<float>(2 * dim - (kAttnTile - 1))) <= 0.25f) {
+              recover_dim = dim;
+              atomicAdd(&p.report->pv_corrected, 1);
+            }
+          }
+          if (recover_dim < 0) atomicAdd(&p.report->failed_rows, 1);
+        }
+        float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kAttnTile;
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          float o[32];
+          tmem_ld_32x32b_x32(o_addr + cc * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = o[i] * inv_l;
+            if (my_fault && p.fault_index == cc * 32 + i) x += p.fault_value;
+            if (recover_dim == cc * 32 + i) x -= delta_sum;
+            o[i] = x;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+          }
+        }
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) max_ratio = fmaxf(max_ratio, __shfl_xor_sync(0xffffffffU, max_ratio, off));
+      if (lane == 0) atomicMax(&p.report->max_noise_bits, __float_as_int(max_ratio));
+    }
+  }
+
+  // ------------------------------------------------------------------- teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if (sh.abort_flag != 0) {
+    if (threadIdx.x == 0) atomicExch(&p.report->status, 1);
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 cudaError_t configure_attention() {
   return cudaFuncSetAttribute(ft_attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
 }
 
 cudaError_t launch_attention(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                              int batch_heads, cudaStream_t stream) {
-  dim3 grid(params.seq / kAttnTile, batch_heads);
+  dim3 grid((params.seq + kAttnQTiles * kAttnTile - 1) / (kAttnQTiles * kAttnTile), batch_heads);
   ft_attention_fwd_kernel<<<grid, kAttnThreads, kAttnSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
   return cudaGetLastError();
 }
