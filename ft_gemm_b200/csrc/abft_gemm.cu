@@ -111,7 +111,9 @@ __device__ __forceinline__ bool any_over_epilogue(bool flag) {
   return out != 0;
 }
 
-template <bool kPair>
+// kProfile adds the per-role cycle counters of GemmParams::profile; the production
+// instantiation carries none of that code.
+template <bool kPair, bool kProfile>
 __global__ void __launch_bounds__(kThreads, 1)
 abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ GemmParams p) {
@@ -133,7 +135,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int num_tiles = num_m * num_n;
   const int num_kb = p.k / kBlockK;
   constexpr int kGroupM = kTileGroupRows / Cfg::kTileM;
-  const bool profiling = p.profile != nullptr;
+  constexpr bool profiling = kProfile;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -497,17 +499,24 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
 int abft_gemm_smem_bytes(bool pair) { return pair ? smem_bytes<true>() : smem_bytes<false>(); }
 
-cudaError_t configure_abft_gemm() {
-  cudaError_t err =
-      cudaFuncSetAttribute(abft_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<false>());
-  if (err != cudaSuccess) return err;
-  return cudaFuncSetAttribute(abft_gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<true>());
+template <bool kPair, bool kProfile>
+static cudaError_t configure_one() {
+  return cudaFuncSetAttribute(abft_gemm_fp8_kernel<kPair, kProfile>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<kPair>());
 }
 
-cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid, bool pair,
-                             cudaStream_t stream) {
+cudaError_t configure_abft_gemm() {
+  cudaError_t err = configure_one<false, false>();
+  if (err == cudaSuccess) err = configure_one<true, false>();
+  if (err == cudaSuccess) err = configure_one<false, true>();
+  if (err == cudaSuccess) err = configure_one<true, true>();
+  return err;
+}
+
+template <bool kProfile>
+static cudaError_t launch_with(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid, bool pair,
+                               cudaStream_t stream) {
   if (!pair) {
-    abft_gemm_fp8_kernel<false><<<grid, kThreads, smem_bytes<false>(), stream>>>(tmap_a, tmap_b, params);
+    abft_gemm_fp8_kernel<false, kProfile><<<grid, kThreads, smem_bytes<false>(), stream>>>(tmap_a, tmap_b, params);
     return cudaGetLastError();
   }
   cudaLaunchAttribute attribute{};
@@ -522,7 +531,13 @@ cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_
   config.stream = stream;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, abft_gemm_fp8_kernel<true>, tmap_a, tmap_b, params);
+  return cudaLaunchKernelEx(&config, abft_gemm_fp8_kernel<true, kProfile>, tmap_a, tmap_b, params);
+}
+
+cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid, bool pair,
+                             cudaStream_t stream) {
+  return params.profile != nullptr ? launch_with<true>(tmap_a, tmap_b, params, grid, pair, stream)
+                                   : launch_with<false>(tmap_a, tmap_b, params, grid, pair, stream);
 }
 
 }  // namespace ftg
