@@ -47,14 +47,14 @@ constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
 constexpr int kGroups = kBlockN / kGroupCols;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
 constexpr int kTileGroupRows = 2048;  // rows walked together so that concurrent tiles share A and B in L2
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 7;
 
 template <bool kPair>
 struct Config {
   static constexpr int kBRows = kPair ? kBlockN / 2 : kBlockN;  // rows of B staged by one CTA
   static constexpr int kBBytes = kBRows * kBlockK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = kPair ? 6 : 4;
+  static constexpr int kStages = kPair ? 7 : 4;
   static constexpr int kTileM = kPair ? 2 * kBlockM : kBlockM;  // rows of C per scheduled tile
   static constexpr uint32_t kExpectTx = kPair ? 2 * kStageBytes : kStageBytes;
   static constexpr uint32_t kEmptyArrivals = kPair ? 2 * kEpilogueThreads : kEpilogueThreads;
@@ -84,7 +84,7 @@ struct SharedTail {
 
 template <bool kPair>
 constexpr int smem_bytes() {
-  return Config<kPair>::kStages * Config<kPair>::kStageBytes + static_cast<int>(sizeof(SharedTail)) + 1024;
+  return Config<kPair>::kStages * Config<kPair>::kStageBytes + static_cast<int>(sizeof(SharedTail));
 }
 
 // tile index -> (row block of kTileM rows, column block of 256 columns)
@@ -118,8 +118,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ GemmParams p) {
   using Cfg = Config<kPair>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // The swizzled operand tiles need a 1024-byte aligned base.  The declaration asks for it; should a toolchain not
+  // honour that, the kernel reports an error instead of running with misplaced tiles.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(&p.report->status, 2);
+    return;
+  }
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + Cfg::kStages * kABytes;
   SharedTail& tail = *reinterpret_cast<SharedTail*>(smem + Cfg::kStages * Cfg::kStageBytes);
