@@ -31,6 +31,14 @@ M_PER_RANK, N_DIM, K_DIM = 8192, 8192, 8192
 SEED_A, SEED_B = 0x12345678, 0x9ABCDEF0
 
 
+def _ncu_traffic(m, n, k):
+    """DRAM bytes per launch of the fused kernel.  Measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
+    capture-sized case 8192x4096x4096: 146.2 MB against 184 MiB algorithmic (profiles/abft_gemm_fp8_kernel_8192x4096x4096.md);
+    traffic grows with the algorithmic bytes M*K + N*K + 4*M*N + 16*M*N/64, so a larger launch is scaled by that ratio."""
+    algorithmic = lambda mm, nn, kk: mm * kk + nn * kk + 4.0 * mm * nn + 16.0 * mm * nn / 64.0
+    return 146.2e6 * algorithmic(m, n, k) / algorithmic(8192, 4096, 4096)
+
+
 def _peaks(timed_seconds):
     """FP8 tensor peak for the roofline.  MEASURED_PEAKS.json holds cuBLAS bf16 figures only; dense FP8 runs at twice
     the bf16 rate on this part.  A timed region shorter than 0.1 s never reaches the power cap, so it is compared
@@ -276,7 +284,8 @@ def main():
                 "gpu_launches": args.steps * world,
                 "clocks": clocks,
                 "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
-                             "traffic": None, "peak_note": peak_note, "kernel": "abft_gemm_fp8_kernel",
+                             "traffic": _ncu_traffic(m_rank, n, k), "traffic_note": "ncu capture at 8192x4096x4096 scaled by algorithmic bytes",
+                             "peak_note": peak_note, "kernel": "abft_gemm_fp8_kernel",
                              "kernel_ms": kernel_ms, "flops_per_launch": 2.0 * m_rank * n * k},
                 "prepare_ms": prep.prepare_ms,
                 "first_call_tflops": 2.0 * m_rank * n * k / ((prep.prepare_ms + kernel_ms) * 1e-3) / 1e12,
