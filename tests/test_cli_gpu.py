@@ -1,0 +1,85 @@
+"""The per-stage command-line programs on a GPU: same flags, `key: value` report and
+exit-code rule as the reference's programs (which are their own tests: each one
+verifies itself and returns 0 or 1, src/s4_cluster_multicast_abft_fp8_gemm.cu:723-726, 784)."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BUILD = os.path.join(ROOT, "build")
+
+
+def run(program, *args):
+    exe = os.path.join(BUILD, program)
+    if not os.path.exists(exe):
+        subprocess.run(["make", "-C", ROOT, "cli"], check=True, stdout=subprocess.DEVNULL)
+    out = subprocess.run([exe, *map(str, args)], capture_output=True, text=True, timeout=600)
+    report = {}
+    for line in out.stdout.splitlines():
+        key, sep, value = line.partition(": ")
+        if sep:
+            report.setdefault(key, value)
+    return out.returncode, report, out.stderr
+
+
+def test_stage_program_clean_and_injected():
+    rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 1024, "--n", 1024, "--k", 1024, "--warmup", 1, "--repeat", 3)
+    assert rc == 0 and rep["verification"] == "PASS"
+    assert rep["shape"].startswith("M=1024 N=1024 K=1024, abft_tiles=256")
+    assert (rep["bad_tiles"], rep["corrected_tiles"]) == ("0", "0")
+    for key in ("metadata_cache_bytes", "input_metadata_time_ms", "expected_metadata_time_ms", "metadata_prepare_time_ms",
+                "first_fused_gemm_abft_time_ms", "first_call_total_ms", "first_call_tflops", "avg_fused_gemm_abft_time_ms",
+                "amortized_time_ms", "amortized_tflops", "fused_gemm_tflops", "abft_tolerance", "verification_samples",
+                "sampled_max_absolute_error", "sampled_max_tolerance_ratio", "layout"):
+        assert key in rep, key
+    assert rep["layout"] == "A=[M,K] row-major, B=[N,K] column-major, C=[N,M] column-major"
+    assert float(rep["sampled_max_tolerance_ratio"]) <= 1.0 and rep["verification_samples"] == "64"
+    # `--name=value` grammar and the deterministic fault of the reference (s4:449-453)
+    rc, rep, _ = run("stage_abft_fp8_gemm", "--m=512", "--n=512", "--k=256", "--repeat=2", "--inject-fault", "--fault-value", 2.5)
+    assert rc == 0 and (rep["bad_tiles"], rep["corrected_tiles"], rep["verification"]) == ("1", "1", "PASS")
+    # one-CTA form (M not a multiple of 256) and a fault below the threshold: the run fails like the reference's would
+    rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 384, "--n", 256, "--k", 128, "--repeat", 1, "--inject-fault", "--fault-value", 1e-4)
+    assert rc == 1 and rep["bad_tiles"] == "0" and rep["verification"] == "FAIL"
+
+
+def test_stage_program_rejects_bad_shapes():
+    for args in (["--m", 100], ["--n", 128], ["--k", 64], ["--repeat", 0]):
+        rc, rep, err = run("stage_abft_fp8_gemm", *args)
+        assert rc == 1 and not rep and "Invalid options" in err
+
+
+def test_campaign_program():
+    rc, rep, _ = run("fault_campaign", "--m", 1024, "--n", 1024, "--k", 1024, "--warmup", 1, "--repeat", 1, "--fault-trials", 60,
+                     "--fault-seed", 12345, "--double-trials", 10)
+    assert rc == 0 and rep["verification"] == "PASS"
+    assert rep["fault_campaign_trials"] == "60" and rep["fault_campaign_seed"] == "12345"
+    # uniform(-1,1) inputs at K=1024: threshold ~0.34, every fault of magnitude >= 1 is caught
+    assert rep["fault_campaign_detected"] == "60" and rep["fault_campaign_corrected"] == "60"
+    assert rep["fault_campaign_missed"] == "0" and rep["fault_campaign_miscorrected"] == "0"
+    assert rep["fault_campaign_correction_rate_percent"] == "100.000"
+    assert rep["double_fault_reported_uncorrected"] == "10" and rep["double_fault_silently_corrected"] == "0"
+    assert sum(int(rep[f"fault_campaign_bin_{i}"].split("trials=")[1].split()[0]) for i in range(4)) == 60
+
+
+def test_attention_program():
+    rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--repeat", 2)
+    assert rc == 0 and rep["verification"] == "PASS" and rep["mismatches"] == "0"
+    assert (rep["score_detected"], rep["pv_detected"], rep["failed_rows"]) == ("0", "0", "0")
+    rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--repeat", 1, "--fault-stage", "score",
+                     "--fault-value", 4.0)
+    assert rc == 0 and (rep["score_detected"], rep["score_corrected"]) == ("1", "1")
+    assert rep["fault_target"].startswith("batch=0 head=0 query=256 index=256")  # defaults of a0:193-199
+    rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--repeat", 1, "--fault-stage=output",
+                     "--fault-value", 0.5, "--dist", "grid")
+    assert rc == 0 and (rep["pv_detected"], rep["pv_corrected"], rep["failed_rows"]) == ("1", "1", "0")
+    rc, _, err = run("ft_flash_attention", "--head-dim", 64)
+    assert rc == 1 and "Invalid options" in err
+
+
+def test_cublaslt_program():
+    rc, rep, _ = run("cublaslt_fp8_bench", "--m", 1024, "--n", 1024, "--k", 1024, "--warmup", 2, "--repeat", 5)
+    assert rc == 0 and rep["verification"] == "PASS" and rep["benchmark"] == "cuBLASLt FP8 E4M3 GEMM"
+    assert float(rep["throughput_tflops"]) > 0 and int(rep["heuristic_algorithms"]) >= 1
