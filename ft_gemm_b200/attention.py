@@ -15,12 +15,13 @@ import torch
 from . import _abi
 from .operator import TileRecord, _stream_ptr
 
-FAULT_NONE, FAULT_SCORE, FAULT_OUTPUT = 0, 1, 4
+FAULT_NONE, FAULT_SCORE, FAULT_SOFTMAX, FAULT_SOFTMAX_STATE, FAULT_OUTPUT = 0, 1, 2, 3, 4
 
 
 class FtAttnOptions(ctypes.Structure):
     _fields_ = [("score_abs_tol", ctypes.c_float), ("score_rel_tol", ctypes.c_float), ("pv_abs_tol", ctypes.c_float),
-                ("pv_rel_tol", ctypes.c_float), ("reserved", ctypes.c_int * 4)]
+                ("pv_rel_tol", ctypes.c_float), ("softmax_abs_tol", ctypes.c_float), ("softmax_rel_tol", ctypes.c_float),
+                ("protect_softmax", ctypes.c_int), ("reserved", ctypes.c_int * 1)]
 
 
 class FtAttnFault(ctypes.Structure):
@@ -31,7 +32,8 @@ class FtAttnFault(ctypes.Structure):
 class FtAttnReport(ctypes.Structure):
     _fields_ = [("status", ctypes.c_int), ("score_detected", ctypes.c_int), ("score_corrected", ctypes.c_int),
                 ("score_uncorrected", ctypes.c_int), ("pv_detected", ctypes.c_int), ("pv_corrected", ctypes.c_int),
-                ("failed_rows", ctypes.c_int), ("n_records", ctypes.c_int), ("max_score_noise", ctypes.c_float),
+                ("failed_rows", ctypes.c_int), ("softmax_detected", ctypes.c_int), ("softmax_corrected", ctypes.c_int),
+                ("softmax_replayed", ctypes.c_int), ("n_records", ctypes.c_int), ("max_score_noise", ctypes.c_float),
                 ("prepare_ms", ctypes.c_float), ("records", _abi.FtTileRecord * 16)]
 
 
@@ -44,6 +46,9 @@ class AttnReport:
     pv_detected: int
     pv_corrected: int
     failed_rows: int
+    softmax_detected: int
+    softmax_corrected: int
+    softmax_replayed: int
     max_score_noise: float
     prepare_ms: float
     records: List[TileRecord] = field(default_factory=list)
@@ -84,7 +89,7 @@ class FtAttention:
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, score_abs_tol: float = 1.0e-2,
                  score_rel_tol: float = 2.0e-5, pv_abs_tol: float = 2.0e-3, pv_rel_tol: float = 2.0e-3,
-                 stream: Optional[torch.cuda.Stream] = None):
+                 protect_softmax: bool = False, stream: Optional[torch.cuda.Stream] = None):
         for t, name in ((q, "Q"), (k, "K"), (v, "V")):
             if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 4 or not t.is_contiguous() or t.shape != q.shape:
                 raise ValueError(f"{name} must be a contiguous [B, H, N, D] float16 CUDA tensor of the same shape as Q")
@@ -95,6 +100,7 @@ class FtAttention:
         self.lib.ft_attn_options_default(ctypes.byref(options))
         options.score_abs_tol, options.score_rel_tol = score_abs_tol, score_rel_tol
         options.pv_abs_tol, options.pv_rel_tol = pv_abs_tol, pv_rel_tol
+        options.protect_softmax = int(protect_softmax)
         self.handle = ctypes.c_void_p()
         with torch.cuda.device(q.device):
             _abi.check(self.lib.ft_attention_fp16_abft_prepare(
@@ -124,7 +130,8 @@ class FtAttention:
         records = [TileRecord(r.tile, r.bad_row_count, r.bad_col_count, r.bad_row, r.bad_col, r.row_delta, r.col_delta,
                               r.corrected) for r in rep.records[:rep.n_records]]
         return AttnReport(rep.status, rep.score_detected, rep.score_corrected, rep.score_uncorrected, rep.pv_detected,
-                          rep.pv_corrected, rep.failed_rows, rep.max_score_noise, rep.prepare_ms, records)
+                          rep.pv_corrected, rep.failed_rows, rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed,
+                          rep.max_score_noise, rep.prepare_ms, records)
 
     def close(self):
         if getattr(self, "handle", None) is not None and self.handle.value:

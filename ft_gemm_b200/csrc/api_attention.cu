@@ -78,6 +78,9 @@ void ft_attn_options_default(ft_attn_options* o) {
   o->score_rel_tol = 2.0e-5f;
   o->pv_abs_tol = 2.0e-3f;
   o->pv_rel_tol = 2.0e-3f;
+  o->softmax_abs_tol = 2.0e-5f;
+  o->softmax_rel_tol = 2.0e-5f;
+  o->protect_softmax = 0;
 }
 
 int ft_attention_fp16_abft_destroy(ft_attn_handle* h) {
@@ -208,14 +211,21 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   params.score_rel_tol = h->options.score_rel_tol;
   params.pv_abs_tol = h->options.pv_abs_tol;
   params.pv_rel_tol = h->options.pv_rel_tol;
+  params.softmax_abs_tol = h->options.softmax_abs_tol;
+  params.softmax_rel_tol = h->options.softmax_rel_tol;
+  params.protect_softmax = h->options.protect_softmax;
   params.scale_log2 = 1.44269504088896340736f / std::sqrt(static_cast<float>(h->dim));
   params.fault_stage = FT_ATTN_FAULT_NONE;
   params.fault_bh = -1;
   if (fault != nullptr && fault->stage != FT_ATTN_FAULT_NONE) {
-    if (fault->stage != FT_ATTN_FAULT_SCORE && fault->stage != FT_ATTN_FAULT_OUTPUT) {
-      return noalloc_fail(FT_ERR_INVALID, "only the score (1) and output (4) stages can be targeted");
+    const bool softmax_stage = fault->stage == FT_ATTN_FAULT_SOFTMAX || fault->stage == FT_ATTN_FAULT_SOFTMAX_STATE;
+    if (fault->stage != FT_ATTN_FAULT_SCORE && fault->stage != FT_ATTN_FAULT_OUTPUT && !softmax_stage) {
+      return noalloc_fail(FT_ERR_INVALID, "fault stage must be 1 (score), 2 (softmax), 3 (softmax-state) or 4 (output)");
     }
-    int limit = fault->stage == FT_ATTN_FAULT_SCORE ? h->seq : h->dim;
+    if (softmax_stage && h->options.protect_softmax == 0) {
+      return noalloc_fail(FT_ERR_INVALID, "the softmax stages can be targeted only by a handle prepared with protect_softmax");
+    }
+    int limit = fault->stage == FT_ATTN_FAULT_OUTPUT ? h->dim : h->seq;
     if (fault->batch < 0 || fault->batch >= h->batch || fault->head < 0 || fault->head >= h->heads || fault->query < 0 ||
         fault->query >= h->seq || fault->index < 0 || fault->index >= limit) {
       return noalloc_fail(FT_ERR_INVALID, "fault target is outside the tensor");
@@ -246,6 +256,9 @@ int ft_attention_fp16_abft_report(ft_attn_handle* h, ft_attn_report* out) {
   out->pv_detected = dev.pv_detected;
   out->pv_corrected = dev.pv_corrected;
   out->failed_rows = dev.failed_rows;
+  out->softmax_detected = dev.softmax_detected;
+  out->softmax_corrected = dev.softmax_corrected;
+  out->softmax_replayed = dev.softmax_replayed;
   out->n_records = std::min(dev.record_count, 16);
   std::memcpy(&out->max_score_noise, &dev.max_noise_bits, sizeof(float));
   std::copy(dev.records, dev.records + out->n_records, out->records);

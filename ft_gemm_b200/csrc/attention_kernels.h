@@ -17,7 +17,9 @@ struct AttnDeviceReport {
   int failed_rows;
   int record_count;
   int max_noise_bits;
-  int pad[3];
+  int softmax_detected;
+  int softmax_corrected;
+  int softmax_replayed;
   ft_tile_record records[16];
 };
 
@@ -31,7 +33,8 @@ struct AttnParams {
   float* out;               // [B*H][N][D]
   AttnDeviceReport* report;
   int seq;
-  float score_abs_tol, score_rel_tol, pv_abs_tol, pv_rel_tol;
+  float score_abs_tol, score_rel_tol, pv_abs_tol, pv_rel_tol, softmax_abs_tol, softmax_rel_tol;
+  int protect_softmax;
   float scale_log2;  // log2(e) / sqrt(D)
   int fault_stage, fault_bh, fault_query, fault_index;
   float fault_value;

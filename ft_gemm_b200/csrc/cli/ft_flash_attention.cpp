@@ -37,23 +37,33 @@ int main(int argc, char** argv) {
   std::string stage_name = args.get_string("--fault-stage", "none");
   std::string dist = args.get_string("--dist", "normal");
   bool causal = args.has_flag("--causal");
+  opt.softmax_abs_tol = args.get_float("--softmax-abs-tol", opt.softmax_abs_tol);
+  opt.softmax_rel_tol = args.get_float("--softmax-rel-tol", opt.softmax_rel_tol);
+  opt.protect_softmax = args.has_flag("--protect-softmax") ? 1 : 0;
   if (args.has_flag("--help")) {
     std::printf(
         "Usage: %s [--batch N --heads N --sequence N --head-dim 128 --warmup N --repeat N]\n"
-        "       [--fault-stage none|score|output --fault-batch N --fault-head N --fault-query N --fault-index N --fault-value X]\n"
+        "       [--protect-softmax --softmax-abs-tol X --softmax-rel-tol X]\n"
+        "       [--fault-stage none|score|softmax|softmax-state|output --fault-batch N --fault-head N --fault-query N --fault-index N --fault-value X]\n"
         "       [--score-abs-tol X --score-rel-tol X --pv-abs-tol X --pv-rel-tol X]\n"
         "       [--verify-abs-tol X --verify-rel-tol X --verify-rows N --dist normal|grid]\n",
         argv[0]);
     return EXIT_SUCCESS;
   }
-  int stage = stage_name == "none" ? FT_ATTN_FAULT_NONE : stage_name == "score" ? FT_ATTN_FAULT_SCORE : stage_name == "output" ? FT_ATTN_FAULT_OUTPUT : -1;
+  int stage = stage_name == "none"            ? FT_ATTN_FAULT_NONE
+              : stage_name == "score"         ? FT_ATTN_FAULT_SCORE
+              : stage_name == "softmax"       ? FT_ATTN_FAULT_SOFTMAX
+              : stage_name == "softmax-state" ? FT_ATTN_FAULT_SOFTMAX_STATE
+              : stage_name == "output"        ? FT_ATTN_FAULT_OUTPUT
+                                              : -1;
+  if (stage == FT_ATTN_FAULT_SOFTMAX || stage == FT_ATTN_FAULT_SOFTMAX_STATE) opt.protect_softmax = 1;  // the reference always protects it
   if (fault_query < 0) fault_query = sequence / 2;
   if (fault_index < 0) fault_index = stage == FT_ATTN_FAULT_OUTPUT ? head_dim / 2 : sequence / 2;  // a0:193-199
   if (batch <= 0 || heads <= 0 || sequence <= 0 || sequence % 128 != 0 || head_dim != 128 || warmup < 0 || repeat <= 0 || stage < 0 ||
       causal || (dist != "normal" && dist != "grid") || verify_rows <= 0) {
     std::fprintf(stderr,
-                 "Invalid options. Require head_dim == 128, sequence %% 128 == 0, non-causal, --fault-stage none|score|output "
-                 "(the softmax stages of the reference are not protected by this build).\n");
+                 "Invalid options. Require head_dim == 128, sequence %% 128 == 0, non-causal, "
+                 "--fault-stage none|score|softmax|softmax-state|output.\n");
     return EXIT_FAILURE;
   }
   CLI_CUDA(cudaSetDevice(0));
@@ -139,10 +149,14 @@ int main(int argc, char** argv) {
   bool fault_pass;
   if (stage == FT_ATTN_FAULT_SCORE) {
     fault_pass = report.score_detected > 0 && report.score_corrected > 0 && report.failed_rows == 0;
+  } else if (stage == FT_ATTN_FAULT_SOFTMAX) {  // pass rules of src/ft_flash_attention_a0.cu:735-750
+    fault_pass = report.softmax_detected > 0 && (report.softmax_corrected > 0 || report.softmax_replayed > 0) && report.failed_rows == 0;
+  } else if (stage == FT_ATTN_FAULT_SOFTMAX_STATE) {
+    fault_pass = report.softmax_detected > 0 && report.softmax_replayed > 0 && report.failed_rows == 0;
   } else if (stage == FT_ATTN_FAULT_OUTPUT) {
     fault_pass = report.pv_detected > 0 && report.pv_corrected > 0 && report.failed_rows == 0;
   } else {
-    fault_pass = report.score_detected == 0 && report.pv_detected == 0 && report.failed_rows == 0;
+    fault_pass = report.score_detected == 0 && report.softmax_detected == 0 && report.pv_detected == 0 && report.failed_rows == 0;
   }
   bool passed = mismatches == 0 && fault_pass;
   double attention_flops = 4.0 * batch * heads * static_cast<double>(sequence) * sequence * head_dim;
@@ -162,6 +176,10 @@ int main(int argc, char** argv) {
   std::printf("score_corrected: %d\n", report.score_corrected);
   std::printf("score_uncorrected: %d\n", report.score_uncorrected);
   std::printf("score_checksum_noise_ratio: %.6e\n", report.max_score_noise);
+  std::printf("softmax_protection: %s\n", opt.protect_softmax ? "on" : "off");
+  std::printf("softmax_detected: %d\n", report.softmax_detected);
+  std::printf("softmax_corrected: %d\n", report.softmax_corrected);
+  std::printf("softmax_replayed: %d\n", report.softmax_replayed);
   std::printf("pv_detected: %d\n", report.pv_detected);
   std::printf("pv_corrected: %d\n", report.pv_corrected);
   std::printf("failed_rows: %d\n", report.failed_rows);

@@ -174,6 +174,12 @@ __device__ __forceinline__ void tmem_add_to_element(uint32_t taddr_column, int l
   tmem_wait_st();
 }
 
+// Hides a value from the optimiser so that a verifier copy is really recomputed.
+__device__ __forceinline__ float opaque(float x) {
+  asm volatile("" : "+f"(x));
+  return x;
+}
+
 template <int Regs>
 __device__ __forceinline__ void reg_release() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Regs));
@@ -183,6 +189,8 @@ __device__ __forceinline__ void reg_acquire() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Regs));
 }
 
+// kProtect adds the reference's softmax-stage protection (verifier copies, moment check, state duplicate).
+template <bool kProtect>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
@@ -327,6 +335,8 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
 
       float m_run = -INFINITY, l_run = 0.0f, exp_sum = 0.0f, exp_weighted = 0.0f, max_ratio = 0.0f;
+      float u1_run = 0.0f, u2_run = 0.0f;                                             // running moments (kProtect)
+      float m_verify = -INFINITY, l_verify = 0.0f, u1_verify = 0.0f, u2_verify = 0.0f;  // verifier copy of the state
       bool alive = true;
 
       for (int j = 0; j < num_tiles; ++j) {
@@ -420,45 +430,151 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           }
         }
         // ---- pass 2: probabilities, FP16 P tile for the MMA, expected output projections
-        float l_tile = 0.0f, es_tile = 0.0f, ew_tile = 0.0f;
+        // With kProtect the reference's softmax-stage protection runs alongside (src/ft_flash_attention_a14.cu:
+        // 964-1099): a verifier copy of the maximum, of every probability and of the moments sum p, sum w p,
+        // sum w^2 p (w = 2*key - (N-1)) of the FP16-rounded probabilities; on a mismatch one probability is
+        // located by the ratio of the moment deltas and replaced by the verifier's, otherwise the whole row of
+        // the tile is replayed from the verifier; a duplicate of the running state (m, l, u1, u2) follows.
+        float l_tile = 0.0f, es_tile = 0.0f, ew_tile = 0.0f, u1_tile = 0.0f, u2_tile = 0.0f;
+        float check_u0 = 0.0f, check_u1 = 0.0f, check_u2 = 0.0f;
+        float m_check = m_new, alpha_check = alpha;
+        if (kProtect) {
+          // verifier maximum: recomputed from its own copy of the running maximum
+          float verifier_max = opaque(row_max);
+          if (fabsf(row_max - verifier_max) > p.softmax_abs_tol) {
+            atomicAdd(&p.report->softmax_detected, 1);
+            atomicAdd(&p.report->softmax_replayed, 1);
+          }
+          m_check = fmaxf(m_verify, verifier_max * p.scale_log2);
+          alpha_check = fast_exp2(opaque(m_verify - m_check));
+        }
+        const bool softmax_fault = kProtect && fault_here && p.fault_stage == FT_ATTN_FAULT_SOFTMAX && fault_row == row_in_tile &&
+                                   p.fault_index / kAttnTile == j;
+        int recovery_action = 0, recovery_key = -1;  // 1: take the verifier's value at recovery_key, 2: replay the row
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          float v[64];
-          tmem_ld_32x32b_x32(s_addr + c * 64, v);
-          tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
-          tmem_wait_ld();
-          if (c == 1) {  // both halves are in registers: the score buffer can take S of the next key tile
-            tcgen05_fence_before();
-            mbar_arrive(&sh.s_empty[t]);
-          }
-          uint8_t* p_row = p_tile + c * kAttnSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
-#pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            uint32_t packed[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i0 = ch * 8 + 2 * e;
-              const float p0 = fast_exp2(__fmaf_rn(v[i0], p.scale_log2, -m_new));
-              const float p1 = fast_exp2(__fmaf_rn(v[i0 + 1], p.scale_log2, -m_new));
-              l_tile += p0;
-              l_tile += p1;
-              const __half2 h = __floats2half2_rn(p0, p1);
-              const float2 r = __half22float2(h);  // what the MMA will multiply by V
-              const float4 meta = *reinterpret_cast<const float4*>(&sh.v_meta[t][buf][c * 64 + i0]);  // two keys
-              es_tile = __fmaf_rn(r.x, meta.x, es_tile);
-              es_tile = __fmaf_rn(r.y, meta.z, es_tile);
-              ew_tile = __fmaf_rn(r.x, meta.y, ew_tile);
-              ew_tile = __fmaf_rn(r.y, meta.w, ew_tile);
-              packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+        for (int attempt = 0; attempt < (kProtect ? 2 : 1); ++attempt) {
+          l_tile = es_tile = ew_tile = u1_tile = u2_tile = 0.0f;
+          check_u0 = check_u1 = check_u2 = 0.0f;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            float v[64];
+            tmem_ld_32x32b_x32(s_addr + c * 64, v);
+            tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
+            tmem_wait_ld();
+            if (!kProtect && c == 1) {  // both halves are in registers: the score buffer can take S of the next key tile
+              tcgen05_fence_before();
+              mbar_arrive(&sh.s_empty[t]);
             }
-            // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-            *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            uint8_t* p_row = p_tile + c * kAttnSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+            const int key0 = c * 64;  // key of v[0] within the tile
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              uint32_t packed[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i0 = ch * 8 + 2 * e;
+                float p0 = fast_exp2(__fmaf_rn(v[i0], p.scale_log2, -m_new));
+                float p1 = fast_exp2(__fmaf_rn(v[i0 + 1], p.scale_log2, -m_new));
+                __half2 h;
+                if (kProtect) {
+                  if (softmax_fault && p.fault_index % kAttnTile == key0 + i0) p0 += p.fault_value;
+                  if (softmax_fault && p.fault_index % kAttnTile == key0 + i0 + 1) p1 += p.fault_value;
+                  const float q0 = fast_exp2(opaque(__fmaf_rn(v[i0], p.scale_log2, -m_check)));
+                  const float q1 = fast_exp2(opaque(__fmaf_rn(v[i0 + 1], p.scale_log2, -m_check)));
+                  const __half2 hv = __floats2half2_rn(q0, q1);
+                  const float2 rv = __half22float2(hv);
+                  const float w0 = static_cast<float>(2 * (j * kAttnTile + key0 + i0) - (seq - 1));
+                  const float w1 = w0 + 2.0f;
+                  check_u0 += rv.x;
+                  check_u0 += rv.y;
+                  check_u1 = __fmaf_rn(w0, rv.x, check_u1);
+                  check_u1 = __fmaf_rn(w1, rv.y, check_u1);
+                  check_u2 = __fmaf_rn(w0, w0 * rv.x, check_u2);
+                  check_u2 = __fmaf_rn(w1, w1 * rv.y, check_u2);
+                  h = __floats2half2_rn(p0, p1);
+                  if (recovery_action == 2 || (recovery_action == 1 && recovery_key == key0 + i0)) h = __halves2half2(__low2half(hv), __high2half(h));
+                  if (recovery_action == 2 || (recovery_action == 1 && recovery_key == key0 + i0 + 1)) h = __halves2half2(__low2half(h), __high2half(hv));
+                  const float2 ra = __half22float2(h);
+                  u1_tile = __fmaf_rn(w0, ra.x, u1_tile);
+                  u1_tile = __fmaf_rn(w1, ra.y, u1_tile);
+                  u2_tile = __fmaf_rn(w0, w0 * ra.x, u2_tile);
+                  u2_tile = __fmaf_rn(w1, w1 * ra.y, u2_tile);
+                } else {
+                  h = __floats2half2_rn(p0, p1);
+                }
+                const float2 r = __half22float2(h);  // what the MMA will multiply by V
+                l_tile += r.x;
+                l_tile += r.y;
+                const float4 meta = *reinterpret_cast<const float4*>(&sh.v_meta[t][buf][key0 + i0]);  // two keys
+                es_tile = __fmaf_rn(r.x, meta.x, es_tile);
+                es_tile = __fmaf_rn(r.y, meta.z, es_tile);
+                ew_tile = __fmaf_rn(r.x, meta.y, ew_tile);
+                ew_tile = __fmaf_rn(r.y, meta.w, ew_tile);
+                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+              *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
           }
+          if (!kProtect || attempt == 1) break;
+          // moment check of the probabilities just written (a14:1014-1046)
+          const float delta0 = l_tile - check_u0, delta1 = u1_tile - check_u1, delta2 = u2_tile - check_u2;
+          const float thr0 = __fmaf_rn(p.softmax_rel_tol, fmaxf(1.0f, fabsf(check_u0)), p.softmax_abs_tol);
+          const float thr1 = __fmaf_rn(p.softmax_rel_tol, fmaxf(1.0f, fabsf(check_u1)), p.softmax_abs_tol);
+          const float thr2 = __fmaf_rn(p.softmax_rel_tol, fmaxf(1.0f, fabsf(check_u2)), p.softmax_abs_tol);
+          const bool bad = fabsf(delta0) > thr0 || fabsf(delta1) > thr1 || fabsf(delta2) > thr2;
+          if (bad) {
+            atomicAdd(&p.report->softmax_detected, 1);
+            recovery_action = 2;
+            if (fabsf(delta0) > thr0) {
+              const float observed_weight = delta1 / delta0;
+              const int key_index = __float2int_rn(0.5f * (observed_weight + static_cast<float>(seq - 1)));
+              const float second_residual = fabsf(delta2 / delta0 - observed_weight * observed_weight);
+              if (key_index >= j * kAttnTile && key_index < (j + 1) * kAttnTile &&
+                  fabsf(observed_weight - static_cast<float>(2 * key_index - (seq - 1))) <= 0.25f &&
+                  second_residual <= fmaxf(1.0f, fabsf(observed_weight)) * 0.5f) {
+                recovery_action = 1;
+                recovery_key = key_index - j * kAttnTile;
+              }
+            }
+            atomicAdd(recovery_action == 1 ? &p.report->softmax_corrected : &p.report->softmax_replayed, 1);
+          }
+          // The repair pass reads the scores again with warp-wide TMEM loads, so the whole warp takes it together;
+          // rows without a finding recompute what they already have.
+          if (!__any_sync(0xffffffffU, bad)) break;
+        }
+        if (kProtect) {  // the score buffer is released only now: a repair pass reads it again
+          tcgen05_fence_before();
+          mbar_arrive(&sh.s_empty[t]);
+          // duplicate of the running state (a14:1075-1098)
+          l_verify = __fmaf_rn(alpha_check, l_verify, check_u0);
+          u1_verify = __fmaf_rn(alpha_check, u1_verify, check_u1);
+          u2_verify = __fmaf_rn(alpha_check, u2_verify, check_u2);
+          m_verify = m_check;
+          u1_run = __fmaf_rn(alpha, u1_run, u1_tile);
+          u2_run = __fmaf_rn(alpha, u2_run, u2_tile);
         }
         l_run = __fmaf_rn(alpha, l_run, l_tile);
         exp_sum = __fmaf_rn(alpha, exp_sum, es_tile);
         exp_weighted = __fmaf_rn(alpha, exp_weighted, ew_tile);
         m_run = m_new;
+        if (kProtect) {
+          if (fault_here && p.fault_stage == FT_ATTN_FAULT_SOFTMAX_STATE && fault_row == row_in_tile && p.fault_index / kAttnTile == j) {
+            l_run += p.fault_value;
+          }
+          auto exceeds = [&](float actual, float expected) {
+            return fabsf(actual - expected) > __fmaf_rn(p.softmax_rel_tol, fmaxf(1.0f, fabsf(expected)), p.softmax_abs_tol);
+          };
+          const bool m_bad = m_run != m_verify && exceeds(m_run, m_verify);  // both are -inf only before the first tile
+          if (m_bad || exceeds(l_run, l_verify) || exceeds(u1_run, u1_verify) || exceeds(u2_run, u2_verify)) {
+            atomicAdd(&p.report->softmax_detected, 1);
+            atomicAdd(&p.report->softmax_replayed, 1);
+            m_run = m_verify;
+            l_run = l_verify;
+            u1_run = u1_verify;
+            u2_run = u2_verify;
+          }
+        }
         fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
         tcgen05_fence_before();
         mbar_arrive(&sh.p_full[t]);
@@ -542,13 +658,19 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 }
 
 cudaError_t configure_attention() {
-  return cudaFuncSetAttribute(ft_attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
+  cudaError_t err = cudaFuncSetAttribute(ft_attention_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
+  if (err != cudaSuccess) return err;
+  return cudaFuncSetAttribute(ft_attention_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
 }
 
 cudaError_t launch_attention(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                              int batch_heads, cudaStream_t stream) {
   dim3 grid((params.seq + kAttnQTiles * kAttnTile - 1) / (kAttnQTiles * kAttnTile), batch_heads);
-  ft_attention_fwd_kernel<<<grid, kAttnThreads, kAttnSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  if (params.protect_softmax != 0) {
+    ft_attention_fwd_kernel<true><<<grid, kAttnThreads, kAttnSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  } else {
+    ft_attention_fwd_kernel<false><<<grid, kAttnThreads, kAttnSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  }
   return cudaGetLastError();
 }
 

@@ -44,13 +44,19 @@ typedef struct {
   float score_rel_tol; /* default 2e-5 */
   float pv_abs_tol;    /* default 2e-3 (src/ft_flash_attention_a0.cu:63-64) */
   float pv_rel_tol;    /* default 2e-3 */
-  int reserved[4];
+  float softmax_abs_tol; /* default 2e-5 (src/ft_flash_attention_a0.cu:61-62) */
+  float softmax_rel_tol; /* default 2e-5 */
+  int protect_softmax;   /* 0 (default): score and output stages only; 1: also the reference's softmax-stage
+                            protection (verifier copies, moment check, state duplicate; about 1.4x the time) */
+  int reserved[1];
 } ft_attn_options;
 
 /* Fault stages use the reference's numbering (src/ft_flash_attention_a0.cu:27-33);
- * only the two stages this build protects can be targeted. */
+ * the softmax stages can be targeted only when protect_softmax is set. */
 #define FT_ATTN_FAULT_NONE 0
 #define FT_ATTN_FAULT_SCORE 1  /* value added to S[query, index=key] after Q K^T */
+#define FT_ATTN_FAULT_SOFTMAX 2       /* value added to the probability of key `index` (needs protect_softmax) */
+#define FT_ATTN_FAULT_SOFTMAX_STATE 3 /* value added to the running sum l in the tile holding key `index` (needs protect_softmax) */
 #define FT_ATTN_FAULT_OUTPUT 4 /* value added to the normalised O[query, index=dim] */
 
 typedef struct {
@@ -70,6 +76,9 @@ typedef struct {
   int pv_detected;       /* output rows whose projection check fired */
   int pv_corrected;
   int failed_rows;       /* output rows detected but not locatable */
+  int softmax_detected;  /* (row, key tile) pairs whose moment or state check fired (protect_softmax) */
+  int softmax_corrected; /* of which: one probability located and replaced by the verifier's */
+  int softmax_replayed;  /* of which: the row of the tile, or the running state, taken from the verifier */
   int n_records;
   float max_score_noise; /* max |delta|/threshold over score checksums that passed */
   float prepare_ms;

@@ -32,6 +32,7 @@
 typedef struct {
   int score_detected, score_corrected, score_uncorrected;
   int pv_detected, pv_corrected, failed_rows;
+  int softmax_detected, softmax_corrected, softmax_replayed;
   int n_records;
   float max_score_noise;
   float min_margin; /* nearest score-stage decision to its threshold, relative */
@@ -121,23 +122,32 @@ static void band_sums_f32(const float* x, int rows, int d, float* sums, float* m
 
 /*
  * Forward for all heads.  Q, K, V: [B*H, N, D] FP16 bit patterns; out: [B*H, N, D].
- * fault_stage 0 none, 1 score (value added to S[query, index]), 4 output (value
- * added to the normalised O[query, index]); numbering of src/ft_flash_attention_a0.cu:27-33.
+ * fault_stage 0 none, 1 score (value added to S[query, index]), 2 softmax (value
+ * added to the probability of key index), 3 softmax-state (value added to the running
+ * sum l in the tile holding key index), 4 output (value added to the normalised
+ * O[query, index]); numbering of src/ft_flash_attention_a0.cu:27-33.  Stages 2 and 3
+ * act only with protect_softmax, which adds the reference's softmax-stage protection
+ * (src/ft_flash_attention_a14.cu:964-1099): verifier probabilities, the moments
+ * sum p, sum w p, sum w^2 p of the FP16-rounded probabilities, single-point
+ * replacement or replay of the row, and a duplicate of the running state.
  * records (may be NULL): score tiles whose checker fired, tile id =
  * ((bh * N/64) + q_band) * N/64 + key_band, sorted by tile id.
  */
 void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint16_t* v16, int batch_heads, int seq, int dim,
-                           float score_abs, float score_rel, float pv_abs, float pv_rel, int fault_stage, int fault_bh,
+                           float score_abs, float score_rel, float pv_abs, float pv_rel, float softmax_abs, float softmax_rel,
+                           int protect_softmax, int fault_stage, int fault_bh,
                            int fault_query, int fault_index, float fault_value, float* out, ftq_attn_stats* stats,
                            ftq_tile_record* records, int max_records) {
   const int bands = seq / 64;
   const float scale_log2 = 1.44269504088896340736f / sqrtf((float)dim);
   int score_detected = 0, score_corrected = 0, score_uncorrected = 0, pv_detected = 0, pv_corrected = 0, failed_rows = 0;
+  int softmax_detected = 0, softmax_corrected = 0, softmax_replayed = 0;
   int n_records = 0;
   float max_noise = 0.0f, min_margin = INFINITY;
 
 #pragma omp parallel for schedule(dynamic, 1) reduction(+ : score_detected, score_corrected, score_uncorrected, pv_detected, \
-                                                            pv_corrected, failed_rows) reduction(max : max_noise)          \
+                                                            pv_corrected, failed_rows, softmax_detected, softmax_corrected, \
+                                                            softmax_replayed) reduction(max : max_noise)                  \
     reduction(min : min_margin)
   for (int bh = 0; bh < batch_heads; ++bh) {
     const size_t head = (size_t)bh * seq * dim;
@@ -171,11 +181,14 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
     float* s = (float*)malloc((size_t)64 * 128 * sizeof(float));    /* one 64-query band x 128 keys */
     float* acc = (float*)malloc((size_t)64 * dim * sizeof(float));  /* unnormalised output of the band */
     float m_run[64], l_run[64], e_sum[64], e_weighted[64];
+    float u1_run[64], u2_run[64], m_ver[64], l_ver[64], u1_ver[64], u2_ver[64];
+    float ph[128], qh[128];
 
     for (int qb = 0; qb < bands; ++qb) { /* the two 64-row bands of a 128-query CTA are independent */
       for (int r = 0; r < 64; ++r) {
-        m_run[r] = -INFINITY;
+        m_run[r] = m_ver[r] = -INFINITY;
         l_run[r] = e_sum[r] = e_weighted[r] = 0.0f;
+        u1_run[r] = u2_run[r] = l_ver[r] = u1_ver[r] = u2_ver[r] = 0.0f;
       }
       memset(acc, 0, (size_t)64 * dim * sizeof(float));
       for (int j = 0; j < seq / 128; ++j) {
@@ -250,21 +263,88 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
           for (int c = 0; c < 128; ++c) row_max = fmaxf(row_max, s[r * 128 + c]);
           float m_new = fmaxf(m_run[r], row_max * scale_log2);
           float alpha = exp2f(m_run[r] - m_new);
-          float l_tile = 0.0f, es = 0.0f, ew = 0.0f;
           float* o = acc + (size_t)r * dim;
           for (int d = 0; d < dim; ++d) o[d] *= alpha;
+          int query = qb * 64 + r;
+          int target = fault_bh == bh && fault_query == query && fault_index / 128 == j;
+          float m_check = m_new, alpha_check = alpha;
+          if (protect_softmax) {
+            m_check = fmaxf(m_ver[r], row_max * scale_log2);
+            alpha_check = exp2f(m_ver[r] - m_check);
+          }
+          /* FP16-rounded primary (ph) and verifier (qh) probabilities */
           for (int c = 0; c < 128; ++c) {
             float pr = exp2f(fmaf(s[r * 128 + c], scale_log2, -m_new));
-            l_tile += pr;
-            float ph = ftq_half_to_float(ftq_float_to_half(pr));
-            es = fmaf(ph, v_sum[j * 128 + c], es);
-            ew = fmaf(ph, v_weighted[j * 128 + c], ew);
+            if (protect_softmax && fault_stage == 2 && target && fault_index % 128 == c) pr += fault_value;
+            ph[c] = ftq_half_to_float(ftq_float_to_half(pr));
+            qh[c] = protect_softmax ? ftq_half_to_float(ftq_float_to_half(exp2f(fmaf(s[r * 128 + c], scale_log2, -m_check)))) : ph[c];
+          }
+          float l_tile = 0.0f, u1 = 0.0f, u2 = 0.0f, c0 = 0.0f, c1 = 0.0f, c2 = 0.0f;
+          for (int attempt = 0; attempt < 2; ++attempt) {
+            l_tile = u1 = u2 = c0 = c1 = c2 = 0.0f;
+            for (int c = 0; c < 128; ++c) {
+              float w = (float)(2 * (j * 128 + c) - (seq - 1));
+              l_tile += ph[c];
+              u1 = fmaf(w, ph[c], u1);
+              u2 = fmaf(w, w * ph[c], u2);
+              c0 += qh[c];
+              c1 = fmaf(w, qh[c], c1);
+              c2 = fmaf(w, w * qh[c], c2);
+            }
+            if (!protect_softmax || attempt == 1) break;
+            float d0 = l_tile - c0, d1 = u1 - c1, d2 = u2 - c2;
+            if (!(fabsf(d0) > threshold(softmax_abs, softmax_rel, fabsf(c0)) || fabsf(d1) > threshold(softmax_abs, softmax_rel, fabsf(c1)) ||
+                  fabsf(d2) > threshold(softmax_abs, softmax_rel, fabsf(c2))))
+              break;
+            ++softmax_detected;
+            int action = 2, key = -1;
+            if (fabsf(d0) > threshold(softmax_abs, softmax_rel, fabsf(c0))) {
+              float observed = d1 / d0;
+              int key_index = (int)nearbyintf(0.5f * (observed + (float)(seq - 1)));
+              float second = fabsf(d2 / d0 - observed * observed);
+              if (key_index >= j * 128 && key_index < (j + 1) * 128 && fabsf(observed - (float)(2 * key_index - (seq - 1))) <= 0.25f &&
+                  second <= fmaxf(1.0f, fabsf(observed)) * 0.5f) {
+                action = 1;
+                key = key_index - j * 128;
+              }
+            }
+            if (action == 1) {
+              ++softmax_corrected;
+              ph[key] = qh[key];
+            } else {
+              ++softmax_replayed;
+              memcpy(ph, qh, sizeof(ph));
+            }
+          }
+          float es = 0.0f, ew = 0.0f;
+          for (int c = 0; c < 128; ++c) {
+            es = fmaf(ph[c], v_sum[j * 128 + c], es);
+            ew = fmaf(ph[c], v_weighted[j * 128 + c], ew);
             const float* vr = vf + (size_t)(j * 128 + c) * dim;
-            for (int d = 0; d < dim; ++d) o[d] = fmaf(ph, vr[d], o[d]);
+            for (int d = 0; d < dim; ++d) o[d] = fmaf(ph[c], vr[d], o[d]);
           }
           l_run[r] = fmaf(alpha, l_run[r], l_tile);
           e_sum[r] = fmaf(alpha, e_sum[r], es);
           e_weighted[r] = fmaf(alpha, e_weighted[r], ew);
+          if (protect_softmax) {
+            u1_run[r] = fmaf(alpha, u1_run[r], u1);
+            u2_run[r] = fmaf(alpha, u2_run[r], u2);
+            l_ver[r] = fmaf(alpha_check, l_ver[r], c0);
+            u1_ver[r] = fmaf(alpha_check, u1_ver[r], c1);
+            u2_ver[r] = fmaf(alpha_check, u2_ver[r], c2);
+            m_ver[r] = m_check;
+            if (fault_stage == 3 && target) l_run[r] += fault_value;
+            if ((m_new != m_ver[r] && fabsf(m_new - m_ver[r]) > threshold(softmax_abs, softmax_rel, fabsf(m_ver[r]))) ||
+                fabsf(l_run[r] - l_ver[r]) > threshold(softmax_abs, softmax_rel, fabsf(l_ver[r])) ||
+                fabsf(u1_run[r] - u1_ver[r]) > threshold(softmax_abs, softmax_rel, fabsf(u1_ver[r])) ||
+                fabsf(u2_run[r] - u2_ver[r]) > threshold(softmax_abs, softmax_rel, fabsf(u2_ver[r]))) {
+              ++softmax_detected;
+              ++softmax_replayed;
+              l_run[r] = l_ver[r];
+              u1_run[r] = u1_ver[r];
+              u2_run[r] = u2_ver[r];
+            }
+          }
           m_run[r] = m_new;
         }
       }
@@ -332,6 +412,9 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
   stats->pv_detected = pv_detected;
   stats->pv_corrected = pv_corrected;
   stats->failed_rows = failed_rows;
+  stats->softmax_detected = softmax_detected;
+  stats->softmax_corrected = softmax_corrected;
+  stats->softmax_replayed = softmax_replayed;
   stats->n_records = n_records;
   stats->max_score_noise = max_noise;
   stats->min_margin = min_margin;

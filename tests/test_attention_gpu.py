@@ -152,3 +152,48 @@ def test_config5_shape_properties(ftg):
     assert (rep.score_detected, rep.score_corrected, rep.pv_detected) == (1, 1, 0)
     assert float((faulty - out).abs().max()) < 5e-4
     op.close()
+
+
+def test_softmax_stage_protection(ftg):
+    """protect_softmax adds the reference's third protected stage (a14:964-1099)."""
+    b, h, n = 1, 2, 384
+    q, k, v = _qkv(b, h, n, seed=19)
+    plain_op = ftg.FtAttention(q, k, v)
+    plain = plain_op.new_output()
+    plain_op.run(plain)
+    with pytest.raises(ftg.FtGemmError):
+        plain_op.run(plain, (ftg.FAULT_SOFTMAX, 0, 0, 1, 1, 0.5))  # needs a handle prepared with the protection
+    plain_op.close()
+    op = ftg.FtAttention(q, k, v, protect_softmax=True)
+    clean = op.new_output()
+    op.run(clean)
+    rep = op.report()
+    assert (rep.softmax_detected, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    assert torch.equal(clean, plain)  # the protection changes nothing when nothing is wrong
+    want, _, _ = oa.forward(_np(q), _np(k), _np(v), protect_softmax=True)
+    np.testing.assert_allclose(_np(clean), want, atol=2e-3, rtol=0)
+    out = op.new_output()
+    for head, query, key, value in [(1, 5, 9, 0.25), (0, 200, 383, 0.5), (1, 383, 130, 0.01), (0, 130, 64, 1.0)]:
+        fault = (ftg.FAULT_SOFTMAX, 0, head, query, key, value)
+        op.run(out, fault)
+        rep = op.report()
+        _, stats, _ = oa.forward(_np(q), _np(k), _np(v), protect_softmax=True, fault=fault)
+        assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 1, 0) == \
+               (stats.softmax_detected, stats.softmax_corrected, stats.softmax_replayed)
+        assert (rep.pv_detected, rep.failed_rows, rep.score_detected) == (0, 0, 0)
+        assert torch.equal(out, clean)  # the verifier's probability replaces the faulty one exactly
+    fault = (ftg.FAULT_SOFTMAX_STATE, 0, 0, 100, 300, 0.75)
+    op.run(out, fault)
+    rep = op.report()
+    _, stats, _ = oa.forward(_np(q), _np(k), _np(v), protect_softmax=True, fault=fault)
+    assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 0, 1) == \
+           (stats.softmax_detected, stats.softmax_corrected, stats.softmax_replayed)
+    assert torch.equal(out, clean)
+    # the other two stages still work under the protection
+    op.run(out, (ftg.FAULT_SCORE, 0, 1, 77, 200, 6.0))
+    rep = op.report()
+    assert (rep.score_corrected, rep.softmax_detected, rep.pv_detected) == (1, 0, 0)
+    op.run(out, (ftg.FAULT_OUTPUT, 0, 0, 10, 100, 0.5))
+    rep = op.report()
+    assert (rep.pv_corrected, rep.softmax_detected, rep.failed_rows) == (1, 0, 0)
+    op.close()

@@ -68,3 +68,25 @@ def test_output_fault_is_located_and_corrected():
     # below the projection tolerance (2e-3 + 2e-3 * max(1, |expected|)): invisible, as in the reference
     out, stats, _ = oa.forward(q, k, v, fault=(4, 0, 0, 10, 10, 1e-3))
     assert stats.pv_detected == 0
+
+
+def test_softmax_stage_protection():
+    """The reference's softmax-stage protection (a14:964-1099): a faulty probability is located by the moment
+    deltas and replaced, a corrupted running sum is replaced by the verifier's copy."""
+    q, k, v = _qkv(1, 2, 384, 128, seed=6)
+    clean, stats, _ = oa.forward(q, k, v, protect_softmax=True)
+    assert (stats.softmax_detected, stats.score_detected, stats.pv_detected) == (0, 0, 0)
+    plain, _, _ = oa.forward(q, k, v)
+    np.testing.assert_array_equal(clean, plain)  # protection changes nothing when nothing is wrong
+    for query, key, value in [(5, 9, 0.25), (200, 383, 0.5), (383, 130, 0.01)]:
+        out, stats, _ = oa.forward(q, k, v, protect_softmax=True, fault=(2, 0, 1, query, key, value))
+        assert (stats.softmax_detected, stats.softmax_corrected, stats.softmax_replayed) == (1, 1, 0)
+        assert (stats.pv_detected, stats.failed_rows) == (0, 0)
+        np.testing.assert_array_equal(out, clean)  # the verifier's probability replaces the faulty one exactly
+    out, stats, _ = oa.forward(q, k, v, protect_softmax=True, fault=(3, 0, 0, 100, 300, 0.75))
+    assert (stats.softmax_detected, stats.softmax_corrected, stats.softmax_replayed) == (1, 0, 1)
+    np.testing.assert_array_equal(out, clean)
+    # without the protection a softmax fault cannot even be requested through the operator; in the oracle it is inert
+    out, stats, _ = oa.forward(q, k, v, protect_softmax=False, fault=(2, 0, 1, 5, 9, 0.25))
+    assert stats.softmax_detected == 0
+    np.testing.assert_array_equal(out, plain)
