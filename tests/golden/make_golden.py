@@ -63,7 +63,7 @@ def run_s0(m, n, k, keep_inputs, outdir):
 
 
 def main():
-    outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(outdir, exist_ok=True)
     for case in S4_CASES:
         run_s4(*case, outdir)

@@ -246,7 +246,7 @@ def test_invalid_arguments_are_rejected(ftg):
 
 
 def test_campaign_config1_normal_1024(ftg, oracle):
-    """BASELINE config 1: 1024^3, N(0,1) inputs, one fault U[1,256] per trial from the campaign chain."""
+    """The 1024^3 configuration: N(0,1) inputs, one fault U[1,256] per trial from the campaign chain."""
     m = n = k = 1024
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k, "normal")
     op = ftg.AbftGemm(a, b)
