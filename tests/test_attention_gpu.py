@@ -125,7 +125,7 @@ def test_repeat_runs_are_bit_identical_and_arguments_checked(ftg):
     with pytest.raises(ftg.FtGemmError):
         op.run(first, (ftg.FAULT_SCORE, 0, 5, 0, 0, 1.0))  # head out of range
     with pytest.raises(ftg.FtGemmError):
-        op.run(first, (2, 0, 0, 0, 0, 1.0))  # the softmax stage is not a target of this build
+        op.run(first, (2, 0, 0, 0, 0, 1.0))  # a softmax-stage fault needs a handle prepared with protect_softmax
     op.close()
     with pytest.raises(ftg.FtGemmError):
         ftg.FtAttention(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous())  # D must be 128
