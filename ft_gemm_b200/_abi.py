@@ -67,6 +67,7 @@ def load():
     lib.ft_gemm_fp8_abft_prepare.argtypes = [ctypes.POINTER(vp), vp, vp, ci, ci, ci, ctypes.POINTER(FtOptions), vp]
     lib.ft_gemm_fp8_abft_refresh.argtypes = [vp, ci, vp]
     lib.ft_gemm_fp8_abft_run.argtypes = [vp, vp, ctypes.POINTER(FtFault), ci, vp]
+    lib.ft_gemm_fp8_abft_run_window.argtypes = [vp, vp, ctypes.POINTER(FtFault), ci, ci, ci, ci, ci, ci, vp]
     lib.ft_gemm_fp8_abft_run_profiled.argtypes = [vp, vp, vp, ci, ctypes.POINTER(ci), vp]
     lib.ft_gemm_fp8_abft_run_profiled.restype = ci
     lib.ft_gemm_fp8_abft_report.argtypes = [vp, ctypes.POINTER(FtReport)]
@@ -82,7 +83,7 @@ def load():
     lib.ft_gemm_last_error.argtypes = []
     lib.ft_gemm_last_error.restype = ctypes.c_char_p
     lib.ft_gemm_abi_version.argtypes = []
-    for name in ("ft_gemm_fp8_abft_prepare", "ft_gemm_fp8_abft_refresh", "ft_gemm_fp8_abft_run", "ft_gemm_fp8_abft_report",
+    for name in ("ft_gemm_fp8_abft_prepare", "ft_gemm_fp8_abft_refresh", "ft_gemm_fp8_abft_run", "ft_gemm_fp8_abft_run_window", "ft_gemm_fp8_abft_report",
                  "ft_gemm_fp8_abft_destroy", "ft_gemm_fp8_abft_cache", "ft_gemm_fp8_abft_cache_read",
                  "ft_gemm_fp8_abft_set_tolerance",
                  "ft_gemm_fp8_abft_host", "ft_gemm_generate_fp8", "ft_gemm_abi_version"):

@@ -136,8 +136,11 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t rank = kPair ? cluster_ctarank() : 0u;  // 0 = leader of the pair
   const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  const int num_m = p.m / Cfg::kTileM;
-  const int num_n = p.n / kBlockN;
+  // the launch covers the window [row0, row0+rows) x [col0, col0+cols) of C; checksum indices stay global
+  const int num_m = p.rows / Cfg::kTileM;
+  const int num_n = p.cols / kBlockN;
+  const int first_mb = p.row0 / Cfg::kTileM;
+  const int first_nb = p.col0 / kBlockN;
   const int num_tiles = num_m * num_n;
   const int num_kb = p.k / kBlockK;
   constexpr int kGroupM = kTileGroupRows / Cfg::kTileM;
@@ -185,6 +188,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       for (int t = worker; t < num_tiles && alive; t += workers) {
         int mb, nb;
         tile_coords(t, num_m, num_n, kGroupM, mb, nb);
+        mb += first_mb;
+        nb += first_nb;
         const int a_row = mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM;
         const int b_row = nb * kBlockN + static_cast<int>(rank) * Cfg::kBRows;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -292,6 +297,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     for (int t = worker; t < num_tiles; t += workers) {
       int mb, nb;
       tile_coords(t, num_m, num_n, kGroupM, mb, nb);
+      mb += first_mb;
+      nb += first_nb;
       const long long t0 = profiling ? clock64() : 0;
       // one thread polls the barrier; the other 127 sleep in the hardware barrier below until it has seen the phase
       bool ok = true;

@@ -81,6 +81,8 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int k, int bo
 
 }  // namespace
 
+constexpr int kMaxPipeChunks = 8;
+
 struct ft_gemm_handle {
   int device = 0;
   int m = 0, n = 0, k = 0;
@@ -105,6 +107,9 @@ struct ft_gemm_handle {
   void* own_b = nullptr;
   float* own_c = nullptr;
   cudaStream_t own_stream = nullptr;
+  // copy streams and events of the pipelined form of the host-buffer entry point
+  cudaStream_t in_stream = nullptr, out_stream = nullptr;
+  cudaEvent_t pipe_events[3 * kMaxPipeChunks + 1] = {};
 };
 
 namespace {
@@ -132,6 +137,91 @@ int fill_cache(ft_gemm_handle* h, int which, cudaStream_t stream) {
   FT_CUDA(cudaEventRecord(h->ev1, stream));
   h->prepare_timed = true;
   h->last_stream = stream;
+  return FT_OK;
+}
+
+void fill_params(const ft_gemm_handle* h, float* c, GemmParams* params) {
+  params->expected_rows = h->expected_rows;
+  params->expected_cols = h->expected_cols;
+  params->row_scales = h->row_scales;
+  params->col_scales = h->col_scales;
+  params->c = c;
+  params->report = h->report;
+  params->m = h->m;
+  params->n = h->n;
+  params->k = h->k;
+  params->row0 = 0;
+  params->rows = h->m;
+  params->col0 = 0;
+  params->cols = h->n;
+  params->abs_tol = h->options.abs_tol;
+  params->rel_tol = h->options.rel_tol;
+}
+
+// Largest chunk count g <= kMaxPipeChunks for which M/g and N/g are whole tiles; 1 = no pipelining.
+int pipe_chunks(const ft_gemm_handle* h) {
+  const int tile_m = h->pair ? 256 : 128;
+  for (int g = kMaxPipeChunks; g > 1; g >>= 1) {
+    if (h->m % (g * tile_m) == 0 && h->n % (g * 256) == 0) return g;
+  }
+  return 1;
+}
+
+int ensure_pipe(ft_gemm_handle* h) {
+  if (h->in_stream != nullptr) return FT_OK;
+  FT_CUDA(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+  FT_CUDA(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+  for (cudaEvent_t& e : h->pipe_events) FT_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  return FT_OK;
+}
+
+// Steady-state form of the host-buffer call (cache valid): A and B arrive in g row chunks each, alternating; as soon as
+// chunk i of both is on the device the L-shaped part of C that needs only chunks 0..i is computed by two window launches
+// and copied back while later chunks are still on their way.  Three streams: copies in, compute, copies out.
+int host_pipelined(ft_gemm_handle* h, const void* a_host, const void* b_host, float* c_host, const ft_fault* faults, int n_faults,
+                   int g) {
+  int rc = ensure_pipe(h);
+  if (rc != FT_OK) return rc;
+  const size_t k = static_cast<size_t>(h->k), m = static_cast<size_t>(h->m);
+  const int mc = h->m / g, nc = h->n / g;
+  const size_t pitch = m * sizeof(float);
+  cudaStream_t compute = h->own_stream;
+  cudaEvent_t* in_done = h->pipe_events;
+  cudaEvent_t* c_done = h->pipe_events + g;
+  cudaEvent_t out_done = h->pipe_events[3 * g];
+  const char* a_src = static_cast<const char*>(a_host);
+  const char* b_src = static_cast<const char*>(b_host);
+  FT_CUDA(cudaMemsetAsync(h->report, 0, 32, compute));
+  for (int i = 0; i < g; ++i) {
+    const size_t a_off = static_cast<size_t>(i) * mc * k, b_off = static_cast<size_t>(i) * nc * k;
+    FT_CUDA(cudaMemcpyAsync(static_cast<char*>(h->own_a) + a_off, a_src + a_off, static_cast<size_t>(mc) * k, cudaMemcpyHostToDevice,
+                            h->in_stream));
+    FT_CUDA(cudaMemcpyAsync(static_cast<char*>(h->own_b) + b_off, b_src + b_off, static_cast<size_t>(nc) * k, cudaMemcpyHostToDevice,
+                            h->in_stream));
+    FT_CUDA(cudaEventRecord(in_done[i], h->in_stream));
+    FT_CUDA(cudaStreamWaitEvent(compute, in_done[i], 0));
+    // rows of chunk i against every column that has arrived (the corner included)
+    rc = ft_gemm_fp8_abft_run_window(h, h->own_c, faults, n_faults, i * mc, mc, 0, (i + 1) * nc, 0, compute);
+    if (rc != FT_OK) return rc;
+    FT_CUDA(cudaEventRecord(c_done[2 * i], compute));
+    FT_CUDA(cudaStreamWaitEvent(h->out_stream, c_done[2 * i], 0));
+    FT_CUDA(cudaMemcpy2DAsync(c_host + static_cast<size_t>(i) * mc, pitch, h->own_c + static_cast<size_t>(i) * mc, pitch,
+                              static_cast<size_t>(mc) * sizeof(float), static_cast<size_t>(i + 1) * nc, cudaMemcpyDeviceToHost,
+                              h->out_stream));
+    if (i > 0) {
+      // columns of chunk i against the rows of the earlier chunks
+      rc = ft_gemm_fp8_abft_run_window(h, h->own_c, faults, n_faults, 0, i * mc, i * nc, nc, 0, compute);
+      if (rc != FT_OK) return rc;
+      FT_CUDA(cudaEventRecord(c_done[2 * i + 1], compute));
+      FT_CUDA(cudaStreamWaitEvent(h->out_stream, c_done[2 * i + 1], 0));
+      const size_t off = static_cast<size_t>(i) * nc * m;
+      FT_CUDA(cudaMemcpy2DAsync(c_host + off, pitch, h->own_c + off, pitch, static_cast<size_t>(i) * mc * sizeof(float),
+                                static_cast<size_t>(nc), cudaMemcpyDeviceToHost, h->out_stream));
+    }
+  }
+  FT_CUDA(cudaEventRecord(out_done, h->out_stream));
+  FT_CUDA(cudaStreamWaitEvent(compute, out_done, 0));
+  h->last_stream = compute;
   return FT_OK;
 }
 
@@ -247,23 +337,29 @@ int ft_gemm_fp8_abft_set_tolerance(ft_gemm_handle* h, float abs_tol, float rel_t
 }
 
 int ft_gemm_fp8_abft_run(ft_gemm_handle* h, float* c, const ft_fault* faults, int n_faults, void* stream_ptr) {
+  if (h == nullptr) return fail(FT_ERR_INVALID, "null handle or output pointer");
+  return ft_gemm_fp8_abft_run_window(h, c, faults, n_faults, 0, h->m, 0, h->n, 1, stream_ptr);
+}
+
+int ft_gemm_fp8_abft_run_window(ft_gemm_handle* h, float* c, const ft_fault* faults, int n_faults, int row0, int rows, int col0,
+                                int cols, int zero_report, void* stream_ptr) {
   if (h == nullptr || c == nullptr) return fail(FT_ERR_INVALID, "null handle or output pointer");
   if (n_faults < 0 || n_faults > FT_MAX_FAULTS || (n_faults > 0 && faults == nullptr)) {
     return fail(FT_ERR_INVALID, "n_faults must be in [0, %d]", FT_MAX_FAULTS);
   }
+  const int tile_m = h->pair ? 256 : 128;
+  if (row0 < 0 || rows <= 0 || col0 < 0 || cols <= 0 || row0 % tile_m != 0 || rows % tile_m != 0 || col0 % 256 != 0 ||
+      cols % 256 != 0 || row0 + rows > h->m || col0 + cols > h->n) {
+    return fail(FT_ERR_INVALID, "window rows [%d,+%d) cols [%d,+%d) must lie inside %dx%d on multiples of %d rows and 256 columns",
+                row0, rows, col0, cols, h->m, h->n, tile_m);
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   GemmParams params{};
-  params.expected_rows = h->expected_rows;
-  params.expected_cols = h->expected_cols;
-  params.row_scales = h->row_scales;
-  params.col_scales = h->col_scales;
-  params.c = c;
-  params.report = h->report;
-  params.m = h->m;
-  params.n = h->n;
-  params.k = h->k;
-  params.abs_tol = h->options.abs_tol;
-  params.rel_tol = h->options.rel_tol;
+  fill_params(h, c, &params);
+  params.row0 = row0;
+  params.rows = rows;
+  params.col0 = col0;
+  params.cols = cols;
   params.faults.count = n_faults;
   int tile_count = (h->m / 64) * (h->n / 64);
   for (int i = 0; i < n_faults; ++i) {
@@ -276,8 +372,10 @@ int ft_gemm_fp8_abft_run(ft_gemm_handle* h, float* c, const ft_fault* faults, in
     params.faults.value[i] = faults[i].value;
   }
   // one small memset in place of the reference's two counter memsets
-  FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
-  FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, h->pair, stream));
+  if (zero_report) FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
+  int tiles = (rows / tile_m) * (cols / 256);
+  int grid = h->pair ? std::min(h->grid, 2 * tiles) : std::min(h->grid, tiles);
+  FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, grid, h->pair, stream));
   h->last_stream = stream;
   return FT_OK;
 }
@@ -291,17 +389,7 @@ int ft_gemm_fp8_abft_run_profiled(ft_gemm_handle* h, float* c, unsigned long lon
   FT_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), bytes));
   FT_CUDA(cudaMemsetAsync(dev, 0, bytes, stream));
   GemmParams params{};
-  params.expected_rows = h->expected_rows;
-  params.expected_cols = h->expected_cols;
-  params.row_scales = h->row_scales;
-  params.col_scales = h->col_scales;
-  params.c = c;
-  params.report = h->report;
-  params.m = h->m;
-  params.n = h->n;
-  params.k = h->k;
-  params.abs_tol = h->options.abs_tol;
-  params.rel_tol = h->options.rel_tol;
+  fill_params(h, c, &params);
   params.profile = dev;
   cudaError_t err = cudaMemsetAsync(h->report, 0, 32, stream);
   if (err == cudaSuccess) err = launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, h->pair, stream);
@@ -379,6 +467,11 @@ int ft_gemm_fp8_abft_destroy(ft_gemm_handle* h) {
   cudaFree(h->own_b);
   cudaFree(h->own_c);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  if (h->in_stream) cudaStreamDestroy(h->in_stream);
+  if (h->out_stream) cudaStreamDestroy(h->out_stream);
+  for (cudaEvent_t e : h->pipe_events) {
+    if (e) cudaEventDestroy(e);
+  }
   delete h;
   return FT_OK;
 }
@@ -424,30 +517,39 @@ int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void
     dc = h->own_c;
     stream = h->own_stream;
   }
-  cudaError_t err = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream);
-  if (err == cudaSuccess) err = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream);
-  if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "host-to-device copy failed: %s", cudaGetErrorString(err));
-  if (rc == FT_OK && fresh) {
-    rc = ft_gemm_fp8_abft_prepare(&h, da, db, m, n, k, options, stream);
-    if (rc == FT_OK) {
-      h->own_a = da;
-      h->own_b = db;
-      h->own_c = dc;
-      h->own_stream = stream;
-    } else {
-      cudaFree(da);
-      cudaFree(db);
-      cudaFree(dc);
-      cudaStreamDestroy(stream);
-      return rc;
+  const int chunks = (!fresh && !prepare) ? pipe_chunks(h) : 1;
+  if (chunks > 1) {
+    rc = host_pipelined(h, a_host, b_host, c_host, faults, n_faults, chunks);
+    if (rc != FT_OK) {  // nothing may still be writing into the caller's memory when the error is returned
+      cudaStreamSynchronize(h->in_stream);
+      cudaStreamSynchronize(h->out_stream);
     }
-  } else if (rc == FT_OK && prepare) {
-    rc = ft_gemm_fp8_abft_refresh(h, 3, stream);
-  }
-  if (rc == FT_OK) rc = ft_gemm_fp8_abft_run(h, dc, faults, n_faults, stream);
-  if (rc == FT_OK) {
-    err = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream);
-    if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "device-to-host copy failed: %s", cudaGetErrorString(err));
+  } else {
+    cudaError_t err = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "host-to-device copy failed: %s", cudaGetErrorString(err));
+    if (rc == FT_OK && fresh) {
+      rc = ft_gemm_fp8_abft_prepare(&h, da, db, m, n, k, options, stream);
+      if (rc == FT_OK) {
+        h->own_a = da;
+        h->own_b = db;
+        h->own_c = dc;
+        h->own_stream = stream;
+      } else {
+        cudaFree(da);
+        cudaFree(db);
+        cudaFree(dc);
+        cudaStreamDestroy(stream);
+        return rc;
+      }
+    } else if (rc == FT_OK && prepare) {
+      rc = ft_gemm_fp8_abft_refresh(h, 3, stream);
+    }
+    if (rc == FT_OK) rc = ft_gemm_fp8_abft_run(h, dc, faults, n_faults, stream);
+    if (rc == FT_OK) {
+      err = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream);
+      if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "device-to-host copy failed: %s", cudaGetErrorString(err));
+    }
   }
   int report_rc = ft_gemm_fp8_abft_report(h, report);
   if (rc == FT_OK) rc = report_rc;

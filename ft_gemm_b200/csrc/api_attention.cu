@@ -81,6 +81,7 @@ void ft_attn_options_default(ft_attn_options* o) {
   o->softmax_abs_tol = 2.0e-5f;
   o->softmax_rel_tol = 2.0e-5f;
   o->protect_softmax = 0;
+  o->causal = 0;
 }
 
 int ft_attention_fp16_abft_destroy(ft_attn_handle* h) {
@@ -214,6 +215,7 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   params.softmax_abs_tol = h->options.softmax_abs_tol;
   params.softmax_rel_tol = h->options.softmax_rel_tol;
   params.protect_softmax = h->options.protect_softmax;
+  params.causal = h->options.causal != 0 ? 1 : 0;
   params.scale_log2 = 1.44269504088896340736f / std::sqrt(static_cast<float>(h->dim));
   params.fault_stage = FT_ATTN_FAULT_NONE;
   params.fault_bh = -1;
@@ -229,6 +231,9 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
     if (fault->batch < 0 || fault->batch >= h->batch || fault->head < 0 || fault->head >= h->heads || fault->query < 0 ||
         fault->query >= h->seq || fault->index < 0 || fault->index >= limit) {
       return noalloc_fail(FT_ERR_INVALID, "fault target is outside the tensor");
+    }
+    if (h->options.causal != 0 && fault->stage != FT_ATTN_FAULT_OUTPUT && fault->index > fault->query) {
+      return noalloc_fail(FT_ERR_INVALID, "For causal attention, the fault key must not exceed the fault query.");
     }
     params.fault_stage = fault->stage;
     params.fault_bh = fault->batch * h->heads + fault->head;

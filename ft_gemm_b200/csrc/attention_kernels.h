@@ -35,6 +35,7 @@ struct AttnParams {
   int seq;
   float score_abs_tol, score_rel_tol, pv_abs_tol, pv_rel_tol, softmax_abs_tol, softmax_rel_tol;
   int protect_softmax;
+  int causal;
   float scale_log2;  // log2(e) / sqrt(D)
   int fault_stage, fault_bh, fault_query, fault_index;
   float fault_value;

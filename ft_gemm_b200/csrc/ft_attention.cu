@@ -212,6 +212,12 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   const int num_tiles = seq / kAttnTile;
   const int row_base = bh * seq;  // first row of this head in the [B*H*N, D] matrices
   const int qtiles = q0 + kAttnQTiles * kAttnTile <= seq ? kAttnQTiles : 1;  // the last CTA of a head may own one tile
+  // Causal attention (src/ft_flash_attention_a14.cu:708): query tile t stops after the key tile on its diagonal, so tile B
+  // of a CTA runs one key tile longer than tile A; inside the diagonal tile keys beyond the query are masked.
+  const bool causal = p.causal != 0;
+  const int first_qtile = q0 / kAttnTile;
+  auto tiles_of = [&](int t) { return causal ? min(num_tiles, first_qtile + t + 1) : num_tiles; };
+  const int cta_tiles = tiles_of(qtiles - 1);
 
   if (threadIdx.x == 0) {
     mbar_init(&sh.q_full, 1);
@@ -249,7 +255,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         tma_load_2d(smem_q + t * kAttnTileBytes, &tmap_q, &sh.q_full, 0, row_base + q0 + t * kAttnTile);
         tma_load_2d(smem_q + t * kAttnTileBytes + kAttnSlabBytes, &tmap_q, &sh.q_full, 64, row_base + q0 + t * kAttnTile);
       }
-      for (int j = 0; j < num_tiles; ++j) {
+      for (int j = 0; j < cta_tiles; ++j) {
         const uint32_t ph = j & 1;
         if (!mbar_wait_bounded(&sh.k_empty, ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
         mbar_arrive_expect_tx(&sh.k_full, kAttnTileBytes);
@@ -264,10 +270,11 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       // ------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc = make_idesc_f16_f32(kAttnTile, kAttnTile);
       bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kAttnTimeoutNs);
-      for (int j = 0; j <= num_tiles && alive; ++j) {
-        if (j < num_tiles) {  // S_A, S_B = Q_{A,B} K_j^T
+      for (int j = 0; j <= cta_tiles && alive; ++j) {
+        if (j < cta_tiles) {  // S_A, S_B = Q_{A,B} K_j^T
           if (!mbar_wait_bounded(&sh.k_full, j & 1, abort_flag, kAttnTimeoutNs)) break;
           for (int t = 0; t < qtiles && alive; ++t) {
+            if (j >= tiles_of(t)) continue;
             // the score buffer of tile t is free once its softmax group has read S_{j-1} twice
             if (!mbar_wait_bounded(&sh.s_empty[t], (j & 1) ^ 1, abort_flag, kAttnTimeoutNs)) {
               alive = false;
@@ -289,6 +296,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           const int i = j - 1;
           if (!mbar_wait_bounded(&sh.v_full, i & 1, abort_flag, kAttnTimeoutNs)) break;
           for (int t = 0; t < qtiles && alive; ++t) {
+            if (i >= tiles_of(t)) continue;
             if (!mbar_wait_bounded(&sh.p_full[t], i & 1, abort_flag, kAttnTimeoutNs)) {
               alive = false;
               break;
@@ -339,8 +347,10 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       float m_verify = -INFINITY, l_verify = 0.0f, u1_verify = 0.0f, u2_verify = 0.0f;  // verifier copy of the state
       bool alive = true;
 
-      for (int j = 0; j < num_tiles; ++j) {
+      const int my_tiles = tiles_of(t);
+      for (int j = 0; j < my_tiles; ++j) {
         const int buf = j & 1;
+        const bool diagonal = causal && j == first_qtile + t;  // keys beyond the query are masked in this tile
         // per-key sums of V for this tile (read in pass 2; published by the barrier inside the wait below)
         sh.v_meta[t][buf][tg] = make_float2(__ldg(p.v_sum + static_cast<size_t>(bh) * seq + j * kAttnTile + tg),
                                             __ldg(p.v_weighted + static_cast<size_t>(bh) * seq + j * kAttnTile + tg));
@@ -399,6 +409,12 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                 rec.corrected = d.corrected ? 1 : 0;
                 p.report->records[slot] = rec;
               }
+            }
+          }
+          if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
             }
           }
 #pragma unroll
@@ -461,6 +477,12 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             tmem_ld_32x32b_x32(s_addr + c * 64, v);
             tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
             tmem_wait_ld();
+            if (diagonal) {  // exp2(-inf) = 0: a masked key gets probability zero in every copy below
+#pragma unroll
+              for (int i = 0; i < 64; ++i) {
+                if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+              }
+            }
             if (!kProtect && c == 1) {  // both halves are in registers: the score buffer can take S of the next key tile
               tcgen05_fence_before();
               mbar_arrive(&sh.s_empty[t]);
@@ -580,7 +602,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         mbar_arrive(&sh.p_full[t]);
       }
       // ---- output stage: projection check of O / l (src/ft_flash_attention_a0.cu:613-662), normalise, store
-      if (alive && attn_wait_all(&sh.p_empty[t], (num_tiles - 1) & 1, abort_flag, poller, bar_all)) {
+      if (alive && attn_wait_all(&sh.p_empty[t], (my_tiles - 1) & 1, abort_flag, poller, bar_all)) {
         tcgen05_fence_after();
         const float inv_l = 1.0f / l_run;
         const int query = q_tile0 + row_in_tile;

@@ -36,6 +36,8 @@ struct GemmParams {
   float* c;
   DeviceReport* report;
   int m, n, k;
+  // window of C this launch computes (rows a multiple of the tile height, cols of 256); the whole product by default
+  int row0, rows, col0, cols;
   float abs_tol, rel_tol;
   FaultParams faults;
   // optional per-CTA cycle counters (8 x uint64 per CTA), nullptr in normal runs:

@@ -125,6 +125,17 @@ class AbftGemm:
             _abi.check(self.lib.ft_gemm_fp8_abft_run(self.handle, ctypes.c_void_p(c.data_ptr()), arr, count,
                                                      _stream_ptr(stream)))
 
+    def run_window(self, c: torch.Tensor, row0: int, rows: int, col0: int, cols: int, faults: Optional[Sequence[Fault]] = None,
+                   zero_report: bool = True, stream: Optional[torch.cuda.Stream] = None):
+        """The launch restricted to rows [row0, row0+rows) x columns [col0, col0+cols) of the product; `c` is the full [N, M]
+        output.  zero_report=False keeps the counters of earlier windows."""
+        if not c.is_cuda or c.dtype != torch.float32 or not c.is_contiguous() or tuple(c.shape) != (self.n, self.m):
+            raise ValueError("C must be a contiguous float32 CUDA tensor of shape [N, M]")
+        arr, count = _fault_array(faults)
+        with torch.cuda.device(self.a.device):
+            _abi.check(self.lib.ft_gemm_fp8_abft_run_window(self.handle, ctypes.c_void_p(c.data_ptr()), arr, count, row0, rows,
+                                                            col0, cols, int(zero_report), _stream_ptr(stream)))
+
     def run_profiled(self, c: torch.Tensor):
         """Runs once and returns a [ctas, 8] int64 tensor of per-role wait/total cycle counters (see ft_gemm.h)."""
         out = torch.zeros((512, 8), dtype=torch.int64)

@@ -129,6 +129,17 @@ int ft_gemm_fp8_abft_refresh(ft_gemm_handle* handle, int which, void* stream);
  * corrector on `stream`.  Asynchronous.  `faults` may be NULL (n_faults = 0). */
 int ft_gemm_fp8_abft_run(ft_gemm_handle* handle, float* c, const ft_fault* faults, int n_faults, void* stream);
 
+/* The same launch restricted to the window rows [row0, row0+rows) x columns
+ * [col0, col0+cols) of the product (the reference always launches the whole grid,
+ * src/s4_cluster_multicast_abft_fp8_gemm.cu:657-672).  `c` is still the base of
+ * the full [N,M] output, tile ids in faults and records stay global.  rows and
+ * row0 must be multiples of 256 (128 for a handle in the one-CTA form), cols and
+ * col0 of 256.  With zero_report = 0 the counters of earlier windows are kept, so
+ * a caller whose operands arrive in pieces can cover the product with several
+ * windows and read one report. */
+int ft_gemm_fp8_abft_run_window(ft_gemm_handle* handle, float* c, const ft_fault* faults, int n_faults, int row0, int rows,
+                                int col0, int cols, int zero_report, void* stream);
+
 /* Diagnostic variant of _run without faults: additionally records, per CTA, how
  * many clock cycles each role spent waiting (8 counters per CTA: producer waiting
  * for a free stage, MMA waiting for a full stage, MMA waiting for a drained
@@ -162,7 +173,11 @@ int ft_gemm_fp8_abft_set_tolerance(ft_gemm_handle* handle, float abs_tol, float 
 
 /* The same operator with HOST buffers: copies A and B to the device, prepares
  * (when `reuse` is NULL) or reuses the cache of *reuse, runs, copies C back and
- * fills `report`.  a, b, c should be pinned for full copy bandwidth.  When
+ * fills `report`.  a, b, c should be pinned for full copy bandwidth.  With a
+ * reused handle and prepare = 0 the call is pipelined: A and B travel in up to 8
+ * row chunks each, every part of C is computed by a window launch as soon as its
+ * operands are on the device and copied back while later chunks are still on
+ * their way (three streams).  When
  * `reuse` is non-NULL and *reuse is NULL a new handle with its own device
  * buffers is created and returned there for later calls; destroy it with
  * ft_gemm_fp8_abft_destroy. */

@@ -135,7 +135,7 @@ static void band_sums_f32(const float* x, int rows, int d, float* sums, float* m
  */
 void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint16_t* v16, int batch_heads, int seq, int dim,
                            float score_abs, float score_rel, float pv_abs, float pv_rel, float softmax_abs, float softmax_rel,
-                           int protect_softmax, int fault_stage, int fault_bh,
+                           int protect_softmax, int causal, int fault_stage, int fault_bh,
                            int fault_query, int fault_index, float fault_value, float* out, ftq_attn_stats* stats,
                            ftq_tile_record* records, int max_records) {
   const int bands = seq / 64;
@@ -191,7 +191,9 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
         u1_run[r] = u2_run[r] = l_ver[r] = u1_ver[r] = u2_ver[r] = 0.0f;
       }
       memset(acc, 0, (size_t)64 * dim * sizeof(float));
-      for (int j = 0; j < seq / 128; ++j) {
+      /* causal (a14:708): the band's 128-query tile stops after the key tile on its diagonal */
+      const int key_tiles = causal ? (qb * 64) / 128 + 1 : seq / 128;
+      for (int j = 0; j < key_tiles; ++j) {
         /* S tile: FP32 accumulate, ascending d */
         for (int r = 0; r < 64; ++r)
           for (int c = 0; c < 128; ++c) {
@@ -257,6 +259,11 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
             }
           }
         }
+        /* causal mask (a14:893), applied after the verifier has seen the raw tile: exp2(-inf) = 0 below */
+        if (causal)
+          for (int r = 0; r < 64; ++r)
+            for (int c = 0; c < 128; ++c)
+              if (j * 128 + c > qb * 64 + r) s[r * 128 + c] = -INFINITY;
         /* online softmax, FP16 probabilities, P V and the expected projections */
         for (int r = 0; r < 64; ++r) {
           float row_max = -INFINITY;

@@ -232,6 +232,62 @@ def test_host_buffer_entry_point(ftg, oracle):
     host.close()
 
 
+def test_windows_cover_the_product(ftg, oracle):
+    """Four window launches into one report give the same C, bit for bit, and the same decisions as one full launch."""
+    for m, n, k, single in [(1024, 1024, 256, 0), (384, 512, 128, 1)]:
+        a = ftg.generate_fp8((m, k), SEED_A)
+        b = ftg.generate_fp8((n, k), SEED_B)
+        op = ftg.AbftGemm(a, b, single_cta=bool(single))
+        whole = op.new_output()
+        fault = [((5 * (n // 64)) + 7, 9, 11, 6.0)]  # rows 320.., columns 448..
+        op.run(whole, fault)
+        want = op.report()
+        assert (want.bad_tiles, want.corrected_tiles) == (1, 1)
+        parts = torch.full_like(whole, float("nan"))
+        rm = 512 if not single else 128
+        windows = [(0, rm, 0, 256), (rm, m - rm, 0, 256), (0, rm, 256, n - 256), (rm, m - rm, 256, n - 256)]
+        for i, (r0, rows, c0, cols) in enumerate(windows):
+            op.run_window(parts, r0, rows, c0, cols, fault, zero_report=(i == 0))
+            got = op.report()
+            filled = ~torch.isnan(parts)
+            assert int(filled.sum()) == sum(w[1] * w[3] for w in windows[:i + 1])  # nothing outside the windows is written
+        assert torch.equal(parts, whole)
+        assert (got.bad_tiles, got.corrected_tiles, got.multi_fault_tiles) == (1, 1, 0)
+        assert (got.records[0].tile, got.records[0].bad_row, got.records[0].bad_col) == (fault[0][0], 9, 11)
+        with pytest.raises(ftg.FtGemmError):
+            op.run_window(parts, 64, 128, 0, 256)  # not on a tile boundary
+        with pytest.raises(ftg.FtGemmError):
+            op.run_window(parts, 0, m, 256, n)  # reaches past N
+        op.close()
+
+
+def test_host_entry_point_pipelined(ftg, oracle):
+    """Second and later calls on a reused handle take the chunked three-stream form: same C as the device-buffer path."""
+    for m, n, k in [(2048, 2048, 256), (1024, 512, 128), (768, 768, 128)]:  # 8, 2 and 1 chunk(s)
+        ah = oracle.generate_uniform(m * k, SEED_A)
+        bh = oracle.generate_uniform(n * k, SEED_B)
+        a_pin = torch.from_numpy(ah.reshape(m, k)).pin_memory()
+        b_pin = torch.from_numpy(bh.reshape(n, k)).pin_memory()
+        c_first = torch.empty((n, m), dtype=torch.float32).pin_memory()
+        c_pipe = torch.full((n, m), float("nan"), dtype=torch.float32).pin_memory()
+        host = ftg.HostAbftGemm(m, n, k)
+        assert host(a_pin, b_pin, c_first).bad_tiles == 0  # creates the handle: plain form
+        rep = host(a_pin, b_pin, c_pipe)  # pipelined form
+        assert rep.bad_tiles == 0
+        assert torch.equal(c_pipe, c_first)
+        tile = (m // 64 - 1) * (n // 64) + 1
+        rep = host(a_pin, b_pin, c_pipe, faults=[(tile, 63, 0, -12.0), (0, 0, 0, 5.0)])
+        assert (rep.bad_tiles, rep.corrected_tiles, len(rep.records)) == (2, 2, 2)
+        assert [r.tile for r in rep.records] == [0, tile]
+        np.testing.assert_allclose(c_pipe.numpy(), c_first.numpy(), atol=1e-3)
+        dev = ftg.AbftGemm(a_pin.cuda(), b_pin.cuda())
+        c_dev = dev.new_output()
+        dev.run(c_dev)
+        assert torch.equal(c_dev.cpu(), c_first)
+        dev.close()
+        host.close()
+
+
 def test_invalid_arguments_are_rejected(ftg):
     a = torch.zeros((128, 128), dtype=torch.uint8, device="cuda")
     b = torch.zeros((256, 128), dtype=torch.uint8, device="cuda")
