@@ -42,7 +42,7 @@ int main(int argc, char** argv) {
   opt.protect_softmax = args.has_flag("--protect-softmax") ? 1 : 0;
   if (args.has_flag("--help")) {
     std::printf(
-        "Usage: %s [--batch N --heads N --sequence N --head-dim 128 --warmup N --repeat N]\n"
+        "Usage: %s [--batch N --heads N --sequence N --head-dim 128 --warmup N --repeat N --causal]\n"
         "       [--protect-softmax --softmax-abs-tol X --softmax-rel-tol X]\n"
         "       [--fault-stage none|score|softmax|softmax-state|output --fault-batch N --fault-head N --fault-query N --fault-index N --fault-value X]\n"
         "       [--score-abs-tol X --score-rel-tol X --pv-abs-tol X --pv-rel-tol X]\n"
@@ -58,12 +58,18 @@ int main(int argc, char** argv) {
                                               : -1;
   if (stage == FT_ATTN_FAULT_SOFTMAX || stage == FT_ATTN_FAULT_SOFTMAX_STATE) opt.protect_softmax = 1;  // the reference always protects it
   if (fault_query < 0) fault_query = sequence / 2;
-  if (fault_index < 0) fault_index = stage == FT_ATTN_FAULT_OUTPUT ? head_dim / 2 : sequence / 2;  // a0:193-199
+  // defaults of a0:193-199; the causal default of a14:261 keeps the key under the query
+  if (fault_index < 0) fault_index = stage == FT_ATTN_FAULT_OUTPUT ? head_dim / 2 : (causal ? fault_query / 2 : sequence / 2);
+  opt.causal = causal ? 1 : 0;
   if (batch <= 0 || heads <= 0 || sequence <= 0 || sequence % 128 != 0 || head_dim != 128 || warmup < 0 || repeat <= 0 || stage < 0 ||
-      causal || (dist != "normal" && dist != "grid") || verify_rows <= 0) {
+      (dist != "normal" && dist != "grid") || verify_rows <= 0) {
     std::fprintf(stderr,
-                 "Invalid options. Require head_dim == 128, sequence %% 128 == 0, non-causal, "
+                 "Invalid options. Require head_dim == 128, sequence %% 128 == 0, "
                  "--fault-stage none|score|softmax|softmax-state|output.\n");
+    return EXIT_FAILURE;
+  }
+  if (causal && stage != FT_ATTN_FAULT_OUTPUT && stage != FT_ATTN_FAULT_NONE && fault_index > fault_query) {  // a14:278-281
+    std::fprintf(stderr, "For causal attention, the fault key must not exceed the fault query.\n");
     return EXIT_FAILURE;
   }
   CLI_CUDA(cudaSetDevice(0));
@@ -123,21 +129,22 @@ int main(int argc, char** argv) {
     }
     CLI_CUDA(cudaMemcpy(q_row.data(), static_cast<uint16_t*>(d_q) + row * head_dim, head_dim * 2, cudaMemcpyDeviceToHost));
     CLI_CUDA(cudaMemcpy(o_row.data(), d_out + row * head_dim, head_dim * sizeof(float), cudaMemcpyDeviceToHost));
+    const int key_count = causal ? static_cast<int>(row % sequence) + 1 : sequence;  // a14:1214
     double maximum = -1e300;
-    for (int key = 0; key < sequence; ++key) {
+    for (int key = 0; key < key_count; ++key) {
       double dot = 0.0;
       for (int d = 0; d < head_dim; ++d) dot += static_cast<double>(half_bits_to_float(q_row[d])) * half_bits_to_float(k_head[static_cast<size_t>(key) * head_dim + d]);
       scores[key] = dot / std::sqrt(static_cast<double>(head_dim));
       maximum = std::max(maximum, scores[key]);
     }
     double denominator = 0.0;
-    for (int key = 0; key < sequence; ++key) {
+    for (int key = 0; key < key_count; ++key) {
       scores[key] = std::exp(scores[key] - maximum);
       denominator += scores[key];
     }
     for (int d = 0; d < head_dim; ++d) {
       double reference = 0.0;
-      for (int key = 0; key < sequence; ++key) reference += scores[key] * half_bits_to_float(v_head[static_cast<size_t>(key) * head_dim + d]);
+      for (int key = 0; key < key_count; ++key) reference += scores[key] * half_bits_to_float(v_head[static_cast<size_t>(key) * head_dim + d]);
       reference /= denominator;
       float absolute_error = static_cast<float>(std::fabs(o_row[d] - reference));
       float tolerance = verify_abs + verify_rel * std::max(1.0f, static_cast<float>(std::fabs(reference)));
@@ -159,11 +166,13 @@ int main(int argc, char** argv) {
     fault_pass = report.score_detected == 0 && report.softmax_detected == 0 && report.pv_detected == 0 && report.failed_rows == 0;
   }
   bool passed = mismatches == 0 && fault_pass;
-  double attention_flops = 4.0 * batch * heads * static_cast<double>(sequence) * sequence * head_dim;
+  // attended (query, key) pairs as the reference counts them (a14:1464-1469)
+  double attended_pairs = causal ? 0.5 * static_cast<double>(sequence) * (sequence + 1.0) : static_cast<double>(sequence) * sequence;
+  double attention_flops = 4.0 * batch * heads * attended_pairs * head_dim;
 
   std::printf("version: FT-FlashAttention B200 tcgen05 TMEM softmax with ABFT score tiles and output projections\n");
   std::printf("layout: Q/K/V=[B,H,N,D], FP16; O=FP32\n");
-  std::printf("shape: B=%d H=%d N=%d D=%d causal=0\n", batch, heads, sequence, head_dim);
+  std::printf("shape: B=%d H=%d N=%d D=%d causal=%d\n", batch, heads, sequence, head_dim, causal ? 1 : 0);
   std::printf("query_tile: 128, key_tile: 128\n");
   std::printf("input_distribution: %s\n", dist.c_str());
   std::printf("avg_no_fault_time_ms: %.6f\n", average_ms);

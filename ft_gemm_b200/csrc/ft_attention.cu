@@ -207,7 +207,9 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   const int lane = threadIdx.x & 31;
   const int group = warp >> 2;  // 0: producer + MMA, 1 and 2: softmax of query tile A and B
   const int bh = blockIdx.y;
-  const int q0 = blockIdx.x * kAttnQTiles * kAttnTile;
+  // causal CTAs get longer towards the end of the sequence: the longest are scheduled first
+  const int q_block = p.causal != 0 ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int q0 = q_block * kAttnQTiles * kAttnTile;
   const int seq = p.seq;
   const int num_tiles = seq / kAttnTile;
   const int row_base = bh * seq;  // first row of this head in the [B*H*N, D] matrices

@@ -15,7 +15,7 @@ class AttnStats(ctypes.Structure):
 
 
 def forward(q, k, v, score_abs=1e-2, score_rel=2e-5, pv_abs=2e-3, pv_rel=2e-3, fault=None, max_records=64, protect_softmax=False,
-            softmax_abs=2e-5, softmax_rel=2e-5):
+            softmax_abs=2e-5, softmax_rel=2e-5, causal=False):
     """q, k, v: numpy float16 arrays [B, H, N, D].  fault = (stage, batch, head, query, index, value).
     Returns (out float32 [B,H,N,D], stats, records)."""
     lib = oracle_lib.load().lib
@@ -30,15 +30,18 @@ def forward(q, k, v, score_abs=1e-2, score_rel=2e-5, pv_abs=2e-3, pv_rel=2e-3, f
     ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
     lib.ftq_attention_forward(ptr(q16), ptr(k16), ptr(v16), b * h, n, d, ctypes.c_float(score_abs), ctypes.c_float(score_rel),
                               ctypes.c_float(pv_abs), ctypes.c_float(pv_rel), ctypes.c_float(softmax_abs), ctypes.c_float(softmax_rel),
-                              int(bool(protect_softmax)), int(stage), int(fb * h + fh), int(fq), int(fi),
+                              int(bool(protect_softmax)), int(bool(causal)), int(stage), int(fb * h + fh), int(fq), int(fi),
                               ctypes.c_float(fv), ptr(out), ctypes.byref(stats), records, max_records)
     return out, stats, list(records[:stats.n_records])
 
 
-def truth_fp64(q, k, v):
-    """softmax(Q K^T / sqrt(D)) V in float64."""
+def truth_fp64(q, k, v, causal=False):
+    """softmax(Q K^T / sqrt(D)) V in float64; causal keeps key <= query."""
     qd, kd, vd = (np.asarray(x, dtype=np.float64) for x in (q, k, v))
     s = qd @ np.swapaxes(kd, -1, -2) / np.sqrt(q.shape[-1])
+    if causal:
+        n = q.shape[-2]
+        s = np.where(np.arange(n)[None, :] > np.arange(n)[:, None], -np.inf, s)
     s -= s.max(axis=-1, keepdims=True)
     p = np.exp(s)
     p /= p.sum(axis=-1, keepdims=True)

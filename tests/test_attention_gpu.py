@@ -197,3 +197,46 @@ def test_softmax_stage_protection(ftg):
     rep = op.report()
     assert (rep.pv_corrected, rep.softmax_detected, rep.failed_rows) == (1, 0, 0)
     op.close()
+
+
+@pytest.mark.parametrize("n", [128, 384, 512])
+def test_causal_forward_and_faults(ftg, n):
+    """causal = key <= query (src/ft_flash_attention_a14.cu:708, 893): key tiles beyond the diagonal are skipped, the
+    diagonal tile is verified raw and masked afterwards."""
+    b, h = 1, 2
+    q, k, v = _qkv(b, h, n, seed=23 + n)
+    op = ftg.FtAttention(q, k, v, causal=True)
+    clean = op.new_output()
+    op.run(clean)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    want, stats, _ = oa.forward(_np(q), _np(k), _np(v), causal=True)
+    assert stats.score_detected == 0
+    np.testing.assert_allclose(_np(clean), want, atol=2e-3, rtol=0)
+    np.testing.assert_allclose(_np(clean), oa.truth_fp64(_np(q), _np(k), _np(v), causal=True), atol=4e-3, rtol=0)
+    assert torch.equal(clean[:, :, 0, :], v[:, :, 0, :].float())  # the first query sees key 0 only
+    out = op.new_output()
+    for head, query, key, value in [(0, n - 1, 0, 3.0), (1, n // 2, n // 2, -4.0), (0, 100, 64, 6.0), (1, n - 1, n - 2, 2.0)]:
+        fault = (ftg.FAULT_SCORE, 0, head, query, key, value)
+        op.run(out, fault)
+        rep = op.report()
+        _, stats, records = oa.forward(_np(q), _np(k), _np(v), causal=True, fault=fault)
+        assert (rep.score_detected, rep.score_corrected) == (1, 1) == (stats.score_detected, stats.score_corrected)
+        assert (rep.records[0].tile, rep.records[0].bad_row, rep.records[0].bad_col) == (records[0].tile, query % 64, key % 64)
+        np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
+    op.run(out, (ftg.FAULT_OUTPUT, 0, 1, n - 1, 77, 0.5))
+    rep = op.report()
+    assert (rep.pv_detected, rep.pv_corrected, rep.failed_rows) == (1, 1, 0)
+    with pytest.raises(ftg.FtGemmError):
+        op.run(out, (ftg.FAULT_SCORE, 0, 0, 10, 11, 1.0))  # a masked score is never computed (a14:278)
+    op.close()
+    # with the softmax-stage protection
+    op = ftg.FtAttention(q, k, v, causal=True, protect_softmax=True)
+    op.run(out)
+    assert torch.equal(out, clean) and op.report().softmax_detected == 0
+    fault = (ftg.FAULT_SOFTMAX, 0, 1, n - 1, n - 3, 0.25)
+    op.run(out, fault)
+    rep = op.report()
+    assert (rep.softmax_detected, rep.softmax_corrected) == (1, 1)
+    assert torch.equal(out, clean)
+    op.close()

@@ -90,3 +90,25 @@ def test_softmax_stage_protection():
     out, stats, _ = oa.forward(q, k, v, protect_softmax=False, fault=(2, 0, 1, 5, 9, 0.25))
     assert stats.softmax_detected == 0
     np.testing.assert_array_equal(out, plain)
+
+
+def test_causal_forward():
+    """Causal attention (src/ft_flash_attention_a14.cu:708, 893): key <= query only; the checker still sees raw score tiles."""
+    q, k, v = _qkv(1, 2, 384, 128, seed=21)
+    out, stats, records = oa.forward(q, k, v, causal=True)
+    assert (stats.score_detected, stats.pv_detected, stats.failed_rows) == (0, 0, 0) and not records
+    np.testing.assert_allclose(out, oa.truth_fp64(q, k, v, causal=True), atol=3e-3, rtol=0)
+    # the first query attends to key 0 only
+    np.testing.assert_allclose(out[0, :, 0, :], v[0, :, 0, :].astype(np.float32), atol=1e-6, rtol=0)
+    # score fault under the diagonal: located, corrected
+    for query, key, value in [(300, 5, 4.0), (200, 200, -3.0), (130, 128, 2.0)]:
+        got, stats, records = oa.forward(q, k, v, causal=True, fault=(1, 0, 1, query, key, value))
+        assert (stats.score_detected, stats.score_corrected) == (1, 1)
+        assert (records[0].bad_row, records[0].bad_col) == (query % 64, key % 64)
+        np.testing.assert_allclose(got, out, atol=5e-4, rtol=0)
+    # softmax and output stages keep working under the mask
+    got, stats, _ = oa.forward(q, k, v, causal=True, protect_softmax=True, fault=(2, 0, 0, 260, 257, 0.5))
+    assert (stats.softmax_detected, stats.softmax_corrected) == (1, 1)
+    np.testing.assert_allclose(got, out, atol=1e-6, rtol=0)
+    got, stats, _ = oa.forward(q, k, v, causal=True, fault=(4, 0, 1, 50, 99, 0.75))
+    assert (stats.pv_detected, stats.pv_corrected, stats.failed_rows) == (1, 1, 0)

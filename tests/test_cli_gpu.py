@@ -75,6 +75,12 @@ def test_attention_program():
     rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--repeat", 1, "--fault-stage=output",
                      "--fault-value", 0.5, "--dist", "grid")
     assert rc == 0 and (rep["pv_detected"], rep["pv_corrected"], rep["failed_rows"]) == ("1", "1", "0")
+    rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--repeat", 1, "--causal", "--fault-stage",
+                     "score", "--fault-value", 4.0)
+    assert rc == 0 and rep["shape"].endswith("causal=1") and (rep["score_detected"], rep["score_corrected"]) == ("1", "1")
+    assert rep["fault_target"].startswith("batch=0 head=0 query=256 index=128")  # causal default of a14:261
+    rc, _, err = run("ft_flash_attention", "--sequence", 256, "--causal", "--fault-stage", "score", "--fault-query", 10, "--fault-index", 20)
+    assert rc == 1 and "must not exceed" in err
     rc, _, err = run("ft_flash_attention", "--head-dim", 64)
     assert rc == 1 and "Invalid options" in err
 
