@@ -138,11 +138,11 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   // the launch covers the window [row0, row0+rows) x [col0, col0+cols) of C; checksum indices stay global
   const int num_m = p.rows / Cfg::kTileM;
-  const int num_n = p.cols / kBlockN;
+  const int num_n = (p.cols + kBlockN - 1) / kBlockN;  // the last column block may reach past N: the copies fill zeros there
   const int first_mb = p.row0 / Cfg::kTileM;
   const int first_nb = p.col0 / kBlockN;
   const int num_tiles = num_m * num_n;
-  const int num_kb = p.k / kBlockK;
+  const int num_kb = (p.k + kBlockK - 1) / kBlockK;    // a short last K block is zero-filled by the copy engine
   constexpr int kGroupM = kTileGroupRows / Cfg::kTileM;
   constexpr bool profiling = kProfile;
 
@@ -288,7 +288,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int pair = quarter >> 1;  // which 64-row ABFT band of this CTA's 128 rows
     const int half = quarter & 1;   // which 32 rows of that band
     const int r_local = half * 32 + lane;
-    const int tile_cols = p.n / kGroupCols;
+    const int tile_cols = (p.n + kGroupCols - 1) / kGroupCols;
+    uint32_t groups_done = 0;  // selects the scratch buffer; counts across tiles because a ragged tile may hold an odd number of groups
     int acc = 0;
     uint32_t acc_phase = 0;
     float max_ratio = 0.0f;
@@ -312,8 +313,11 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int row0 = mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM;  // first row of this CTA's part
       const int grow = row0 + quarter * 32 + lane;
       const int tile_row = row0 / kGroupCols + pair;
+      // 64-column groups of this tile that hold at least one column of C (src/s3:418-419)
+      const int groups_here = min(kGroups, (p.n - nb * kBlockN + kGroupCols - 1) / kGroupCols);
 #pragma unroll 1
-      for (int g = 0; g < kGroups; ++g) {
+      for (int g = 0; g < groups_here; ++g) {
+        const int valid_cols = min(kGroupCols, p.n - nb * kBlockN - g * kGroupCols);
         const int tile_id = tile_row * tile_cols + nb * kGroups + g;
         const size_t cache = static_cast<size_t>(tile_id) * kGroupCols;
         const float exp_row = __ldg(p.expected_rows + cache + r_local);
@@ -328,7 +332,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         tmem_ld_32x32b_x32(taddr, v);
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
-        if (g == kGroups - 1) {
+        if (g == groups_here - 1) {
           // the accumulator is now entirely in registers: hand it back to the MMA warp (of the leader)
           tcgen05_fence_before();
           if (kPair) {
@@ -344,7 +348,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int f = 0; f < FT_MAX_FAULTS; ++f) {
             if (f < p.faults.count && p.faults.tile[f] == tile_id) {
               int fr = min(p.faults.row[f], kGroupCols - 1);
-              int fc = min(p.faults.col[f], kGroupCols - 1);
+              int fc = min(p.faults.col[f], valid_cols - 1);
               if (fr == r_local) {
 #pragma unroll
                 for (int c = 0; c < kGroupCols; ++c) {
@@ -388,7 +392,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
         // w[0], w[1] = sums of columns 2*lane, 2*lane+1 over 32 rows
-        EpilogueScratch& sc = tail.scratch[pair][g & 1];
+        EpilogueScratch& sc = tail.scratch[pair][groups_done & 1];
+        ++groups_done;
         *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(w[0], w[1]);
         const uint32_t row_mask = __ballot_sync(0xffffffffU, row_bad);
         const int first_lane = row_mask != 0 ? __ffs(row_mask) - 1 : 0;
@@ -470,8 +475,15 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
         // C is column-major [N,M]: for a fixed column the 32 lanes write 32 consecutive floats
         float* cptr = p.c + static_cast<size_t>(nb * kBlockN + g * kGroupCols) * p.m + grow;
+        if (valid_cols == kGroupCols) {
 #pragma unroll
-        for (int c = 0; c < kGroupCols; ++c) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);
+          for (int c = 0; c < kGroupCols; ++c) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < kGroupCols; ++c) {
+            if (c < valid_cols) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);
+          }
+        }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;

@@ -93,7 +93,7 @@ inline void read_common(const ArgReader& args, CommonOptions& o) {
 }
 
 inline bool common_valid(const CommonOptions& o) {
-  return o.m > 0 && o.n > 0 && o.k > 0 && o.m % 128 == 0 && o.n % 256 == 0 && o.k % 128 == 0 && o.warmup >= 0 && o.repeat > 0 &&
+  return o.m > 0 && o.n > 0 && o.k > 0 && o.m % 128 == 0 && o.k % 32 == 0 && o.warmup >= 0 && o.repeat > 0 &&
          o.verify_samples >= 0 && o.verify_abs_tolerance >= 0.0f && o.verify_rel_tolerance >= 0.0f && o.abft_abs_tolerance >= 0.0f &&
          o.abft_rel_tolerance >= 0.0f && (o.dist == "uniform" || o.dist == "normal" || o.dist == "llm");
 }
@@ -209,12 +209,12 @@ inline StageTimings time_stage(ft_gemm_handle* handle, float* d_c, const CommonO
 }
 
 inline void print_common_header(const CommonOptions& o, const char* version_key, const char* version) {
-  int tile_count = (o.m / 64) * (o.n / 64);
-  int cta_tiles = (o.m / 128) * (o.n / 256);
+  int tile_count = (o.m / 64) * ((o.n + 63) / 64);
+  int cta_tiles = (o.m / 128) * ((o.n + 255) / 256);
   std::printf("%s: %s\n", version_key, version);
   bool pair = o.m % 256 == 0;
   std::printf("instruction_tile: %s, cta_tile: 128x256x128, tma_stage_k: 128, stages: %d\n", pair ? "256x256x32 (2 CTAs)" : "128x256x32",
-              pair ? 6 : 4);
+              pair ? 7 : 4);
   std::printf("threads_per_cta: 192, producer_warps: 1, mma_warps: 1, epilogue_warps: 4, tmem_accumulators: 2\n");
   std::printf("pipeline: TMA producer || tcgen05.mma issuer || TMEM epilogue with fused ABFT verifier (persistent)\n");
   std::printf("layout: A=[M,K] row-major, B=[N,K] column-major, C=[N,M] column-major\n");

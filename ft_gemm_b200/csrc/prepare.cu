@@ -68,16 +68,17 @@ __global__ void generate_fp8_kernel(uint8_t* out, size_t count, uint32_t seed, i
 constexpr int kBandThreads = 128;
 
 __global__ void __launch_bounds__(kBandThreads) band_sums_kernel(const uint8_t* __restrict__ x, float* __restrict__ sums,
-                                                                 float* __restrict__ mags, int k) {
+                                                                 float* __restrict__ mags, int rows, int k) {
   int band = blockIdx.y;
   int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 16;
   if (k0 >= k) return;
   const uint8_t* base = x + static_cast<size_t>(band) * 64 * k + k0;
+  const int valid = min(64, rows - band * 64);  // the last band of B may be short (src/s3:203)
   float s[16], m[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) s[i] = m[i] = 0.0f;
 #pragma unroll 8
-  for (int row = 0; row < 64; ++row) {
+  for (int row = 0; row < valid; ++row) {
     uint4 packed = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(row) * k));
     uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
@@ -170,9 +171,10 @@ constexpr int kExpChunk = 128;  // k per staged slice
 __device__ __forceinline__ float element_to_float(uint8_t v) { return fp8_to_float(v); }
 __device__ __forceinline__ float element_to_float(__half v) { return __half2float(v); }
 
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* global_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-               "l"(global_src)
+// copies `bytes` (0..16) from global memory and fills the rest of the 16 bytes with zeros
+__device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* global_src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(global_src), "r"(bytes)
                : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(256) expected_checksums_kernel(const T* __rest
                                                                  float* __restrict__ scales, int rows, int nbands, int k, int mode) {
   {
     const size_t z = blockIdx.z;
-    const size_t tiles64 = static_cast<size_t>(rows >> 6) * nbands * 64;
+    const size_t tiles64 = static_cast<size_t>((rows + 63) >> 6) * nbands * 64;
     x += z * rows * k;
     band_sums += z * nbands * k;
     band_mags += z * nbands * k;
@@ -206,18 +208,24 @@ __global__ void __launch_bounds__(256) expected_checksums_kernel(const T* __rest
   const int row0 = blockIdx.x * 64 + warp * kExpRows;
   const int band0 = blockIdx.y * kExpBands;
   constexpr int kXChunksPerRow = kExpChunk * static_cast<int>(sizeof(T)) / 16;
+  // Rows past the end of x repeat the last row (their results are stored as zeros below); k past the end is filled
+  // with zeros, which leaves every partial sum unchanged.  k must be a multiple of 16 elements of T's 16-byte chunks.
+  constexpr int kElemsPerChunk = 16 / static_cast<int>(sizeof(T));
   auto stage_copy = [&](int stage, int k0) {
 #pragma unroll
     for (int i = threadIdx.x; i < 64 * kXChunksPerRow; i += 256) {
       const int r = i / kXChunksPerRow, ch = i % kXChunksPerRow;
-      cp_async_16(reinterpret_cast<uint8_t*>(&sx[stage][r][0]) + ch * 16,
-                  reinterpret_cast<const uint8_t*>(x + static_cast<size_t>(blockIdx.x * 64 + r) * k + k0) + ch * 16);
+      const int kk = k0 + ch * kElemsPerChunk;
+      const int row = min(blockIdx.x * 64 + r, rows - 1);
+      cp_async_16_zfill(reinterpret_cast<uint8_t*>(&sx[stage][r][0]) + ch * 16, x + static_cast<size_t>(row) * k + min(kk, k - kElemsPerChunk),
+                        kk < k ? 16 : 0);
     }
     {
       const int j = threadIdx.x >> 5, ch = threadIdx.x & 31;  // 8 bands x 32 chunks of 4 floats
-      const size_t src = static_cast<size_t>(min(band0 + j, nbands - 1)) * k + k0 + ch * 4;
-      cp_async_16(&sbs[stage][j][ch * 4], band_sums + src);
-      cp_async_16(&sbm[stage][j][ch * 4], band_mags + src);
+      const int kk = k0 + ch * 4;
+      const size_t src = static_cast<size_t>(min(band0 + j, nbands - 1)) * k + min(kk, k - 4);
+      cp_async_16_zfill(&sbs[stage][j][ch * 4], band_sums + src, kk < k ? 16 : 0);
+      cp_async_16_zfill(&sbm[stage][j][ch * 4], band_mags + src, kk < k ? 16 : 0);
     }
     cp_async_commit();
   };
@@ -226,7 +234,7 @@ __global__ void __launch_bounds__(256) expected_checksums_kernel(const T* __rest
 #pragma unroll
   for (int i = 0; i < 2 * kExpRows * kExpBands; ++i) v[i] = 0.0f;
 
-  const int chunks = k / kExpChunk;
+  const int chunks = (k + kExpChunk - 1) / kExpChunk;
   stage_copy(0, 0);
   for (int c = 0; c < chunks; ++c) {
     const int stage = c & 1;
@@ -271,12 +279,14 @@ __global__ void __launch_bounds__(256) expected_checksums_kernel(const T* __rest
     int band = band0 + j;
     if (band < nbands) {
       int row = row0 + r;
-      size_t tile = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band : static_cast<size_t>(band) * (rows >> 6) + (row >> 6);
+      size_t tile = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band
+                              : static_cast<size_t>(band) * ((rows + 63) >> 6) + (row >> 6);
       size_t out = tile * 64 + (row & 63);
+      const float value = row < rows ? v[i] : 0.0f;  // entries past the last valid column are stored as zeros (src/s4:284-293)
       if (which == 0) {
-        expected[out] = v[i];
+        expected[out] = value;
       } else {
-        scales[out] = v[i];
+        scales[out] = value;
       }
     }
   }
@@ -295,14 +305,14 @@ cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, fl
 }
 
 cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, int k, cudaStream_t stream) {
-  dim3 grid((k / 16 + kBandThreads - 1) / kBandThreads, rows / 64);
-  band_sums_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const uint8_t*>(x), sums, mags, k);
+  dim3 grid((k / 16 + kBandThreads - 1) / kBandThreads, (rows + 63) / 64);
+  band_sums_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const uint8_t*>(x), sums, mags, rows, k);
   return cudaGetLastError();
 }
 
 cudaError_t launch_expected(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
                             int nbands, int k, int mode, cudaStream_t stream) {
-  dim3 grid(rows / 64, (nbands + kExpBands - 1) / kExpBands);
+  dim3 grid((rows + 63) / 64, (nbands + kExpBands - 1) / kExpBands);
   expected_checksums_kernel<uint8_t><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), band_sums, band_mags, expected, scales,
                                                                rows, nbands, k, mode);
   return cudaGetLastError();

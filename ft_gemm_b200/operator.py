@@ -107,7 +107,7 @@ class AbftGemm:
 
     @property
     def tile_cols(self) -> int:
-        return self.n // _abi.FT_ABFT_TILE
+        return -(-self.n // _abi.FT_ABFT_TILE)  # the last tile column may be short
 
     @property
     def tile_count(self) -> int:
@@ -168,7 +168,7 @@ class AbftGemm:
         _abi.check(self.lib.ft_gemm_fp8_abft_cache(self.handle, ctypes.byref(view)))
         tiles = self.tile_count
         shapes = {"a_sums": (self.m // 64, self.k), "a_magnitudes": (self.m // 64, self.k),
-                  "b_sums": (self.n // 64, self.k), "b_magnitudes": (self.n // 64, self.k),
+                  "b_sums": (-(-self.n // 64), self.k), "b_magnitudes": (-(-self.n // 64), self.k),
                   "expected_rows": (tiles, 64), "expected_cols": (tiles, 64), "row_scales": (tiles, 64),
                   "col_scales": (tiles, 64)}
         out = {}

@@ -33,7 +33,7 @@ class RowShard:
     def global_tile(self, local_tile: int) -> int:
         """ABFT tile id of the whole product for a tile id of this shard
         (tile ids are tile_row * (N/64) + tile_col; only tile_row shifts)."""
-        return local_tile + self.tile_row_offset * (self.n // FT_ABFT_TILE)
+        return local_tile + self.tile_row_offset * (-(-self.n // FT_ABFT_TILE))
 
 
 def shard_rows(m: int, n: int, rank: int, world: int) -> RowShard:

@@ -15,9 +15,13 @@
  *   A  [M,K]  FP8 E4M3, K contiguous
  *   B  [N,K]  FP8 E4M3, K contiguous
  *   C  [N,M]  FP32 column-major: element (row r, column c) at C[c*M + r]
- *   ABFT tiles are 64x64; tile_id = (r/64) * (N/64) + (c/64)
- *   M % 128 == 0, N % 256 == 0, K % 128 == 0 (the reference's own constraint,
- *   src/s4_cluster_multicast_abft_fp8_gemm.cu:163-169)
+ *   ABFT tiles are 64x64; tile_id = (r/64) * ceil(N/64) + (c/64)
+ *   M % 128 == 0 and K % 32 == 0, N any positive value: the shape rule of the
+ *   reference's stages with boundary tiles (src/s3_warpspecialized_abft_fp8_gemm.cu:
+ *   144-154, 418-419); the last tile column then holds N % 64 valid columns and its
+ *   cached checksums past them are zeros (src/s4_cluster_multicast_abft_fp8_gemm.cu:
+ *   284-293).  The final stage's stricter N % 256 == 0, K % 128 == 0 (src/s4:163-169)
+ *   is a special case.
  *
  * Every function returns FT_OK (0) or a negative FT_ERR_* code; the text of the
  * last error of the calling thread is available from ft_gemm_last_error().

@@ -42,7 +42,8 @@ def test_generator_bit_exact(ftg, oracle):
     assert same.mean() > 0.999
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 384), (384, 256, 2048), (1024, 1024, 1024)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 384), (384, 256, 2048), (1024, 1024, 1024),
+                                   (128, 200, 96), (256, 320, 160), (384, 1000, 416), (128, 7, 32)])  # the last four: boundary tiles
 def test_expected_cache_bit_exact(ftg, oracle, m, n, k):
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k)
     op = ftg.AbftGemm(a, b)
@@ -55,7 +56,10 @@ def test_expected_cache_bit_exact(ftg, oracle, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k,dist", [(128, 256, 128, "uniform"), (256, 512, 384, "uniform"), (512, 768, 1024, "normal"),
-                                        (1024, 1024, 1024, "normal"), (2048, 256, 4096, "uniform")])
+                                        (1024, 1024, 1024, "normal"), (2048, 256, 4096, "uniform"),
+                                        # boundary tiles in N, K not a multiple of the 128-wide K block (src/s3:144-154)
+                                        (128, 200, 96, "uniform"), (256, 1000, 416, "normal"), (512, 64, 32, "uniform"),
+                                        (384, 320, 2080, "uniform"), (256, 129, 224, "normal")])
 def test_gemm_and_clean_check(ftg, oracle, m, n, k, dist):
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k, dist)
     op = ftg.AbftGemm(a, b)
@@ -91,7 +95,7 @@ def _compare_decisions(ftg, oracle, op, c_clean, cache, m, n, faults, abs_tol=1e
         if w.bad_col_count == 1:
             assert g.bad_col == w.bad_col and g.col_delta == pytest.approx(w.col_delta, abs=2e-3)
         if w.corrected:
-            tile_cols = n // 64
+            tile_cols = -(-n // 64)
             corrected_idx.append(((w.tile % tile_cols) * 64 + w.bad_col, (w.tile // tile_cols) * 64 + w.bad_row))
     mask = np.ones_like(got_c, dtype=bool)
     for col, row in corrected_idx:
@@ -230,6 +234,36 @@ def test_host_buffer_entry_point(ftg, oracle):
     assert (rep.bad_tiles, rep.corrected_tiles) == (1, 1)
     np.testing.assert_allclose(c_pin.numpy(), oracle.gemm_f32(ah, bh, m, n, k), atol=1e-3)
     host.close()
+
+
+def test_fault_decisions_in_boundary_tiles(ftg, oracle):
+    """N = 200: the last tile column holds 8 valid columns; a fault column past them is clamped (campaign:464-466)."""
+    for m, n, k in [(256, 200, 160), (128, 449, 96)]:
+        a, b, ah, bh = _inputs(ftg, oracle, m, n, k)
+        op = ftg.AbftGemm(a, b)
+        c = op.new_output()
+        op.run(c)
+        assert op.report().bad_tiles == 0
+        c_clean = c.cpu().numpy()
+        cache = oracle.expected(ah, bh, m, n, k)
+        tile_cols = -(-n // 64)
+        valid_last = n - (tile_cols - 1) * 64
+        last = tile_cols - 1
+        for fault in [(last, 5, 0, 7.0), (tile_cols + last, 40, valid_last - 1, -9.0), (last, 63, 63, 12.0), (1, 2, 3, 4.0)]:
+            rep = _compare_decisions(ftg, oracle, op, c_clean, cache, m, n, [fault])
+            assert (rep.bad_tiles, rep.corrected_tiles) == (1, 1)
+            want_col = min(fault[2], valid_last - 1) if fault[0] % tile_cols == last else fault[2]
+            assert (rep.records[0].bad_row, rep.records[0].bad_col) == (fault[1], want_col)
+        rep = _compare_decisions(ftg, oracle, op, c_clean, cache, m, n, [(last, 1, 0, 5.0), (last, 9, 0, 5.0)])
+        assert (rep.bad_tiles, rep.corrected_tiles, rep.multi_fault_tiles) == (1, 0, 1)
+        # the window form accepts a short last column block
+        parts = torch.full_like(c, float("nan"))
+        tile_m = 256 if m % 256 == 0 else 128
+        op.run_window(parts, 0, tile_m, 0, n)
+        if m > tile_m:
+            op.run_window(parts, tile_m, m - tile_m, 0, n, zero_report=False)
+        assert torch.equal(parts, c)
+        op.close()
 
 
 def test_windows_cover_the_product(ftg, oracle):
