@@ -66,6 +66,8 @@ def load():
     lib.ft_options_default.restype = None
     lib.ft_gemm_fp8_abft_prepare.argtypes = [ctypes.POINTER(vp), vp, vp, ci, ci, ci, ctypes.POINTER(FtOptions), vp]
     lib.ft_gemm_fp8_abft_refresh.argtypes = [vp, ci, vp]
+    lib.ft_gemm_fp8_abft_quantize_a.argtypes = [vp, vp, ci, cf, vp]
+    lib.ft_gemm_fp8_abft_quantize_a.restype = ci
     lib.ft_gemm_fp8_abft_run.argtypes = [vp, vp, ctypes.POINTER(FtFault), ci, vp]
     lib.ft_gemm_fp8_abft_run_window.argtypes = [vp, vp, ctypes.POINTER(FtFault), ci, ci, ci, ci, ci, ci, vp]
     lib.ft_gemm_fp8_abft_run_profiled.argtypes = [vp, vp, vp, ci, ctypes.POINTER(ci), vp]

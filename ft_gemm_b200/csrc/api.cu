@@ -329,6 +329,25 @@ int ft_gemm_fp8_abft_refresh(ft_gemm_handle* h, int which, void* stream_ptr) {
   return fill_cache(h, which & 3, static_cast<cudaStream_t>(stream_ptr));
 }
 
+int ft_gemm_fp8_abft_quantize_a(ft_gemm_handle* h, const void* src, int src_dtype, float scale, void* stream_ptr) {
+  if (h == nullptr || src == nullptr) return fail(FT_ERR_INVALID, "null handle or source pointer");
+  if (src_dtype < FT_SRC_F32 || src_dtype > FT_SRC_F16) return fail(FT_ERR_INVALID, "src_dtype must be 0 (FP32), 1 (BF16) or 2 (FP16)");
+  if ((reinterpret_cast<uintptr_t>(src) & 15) != 0) return fail(FT_ERR_INVALID, "the source must be 16-byte aligned");
+  if (!(scale == scale) || scale == 0.0f) return fail(FT_ERR_INVALID, "scale must be a non-zero number");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const int band_rows_a = h->m / 64, band_rows_b = (h->n + 63) / 64;
+  FT_CUDA(cudaEventRecord(h->ev0, stream));
+  // A and its band sums in one pass over the source; the caller's A buffer is written here
+  FT_CUDA(launch_quantize_band_sums(src, src_dtype, const_cast<void*>(h->a), h->a_sums, h->a_mags, h->m, h->k, scale, stream));
+  FT_CUDA(cudaEventRecord(h->ev_mid, stream));
+  FT_CUDA(launch_expected(h->a, h->b_sums, h->b_mags, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0, stream));
+  FT_CUDA(launch_expected(h->b, h->a_sums, h->a_mags, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1, stream));
+  FT_CUDA(cudaEventRecord(h->ev1, stream));
+  h->prepare_timed = true;
+  h->last_stream = stream;
+  return FT_OK;
+}
+
 int ft_gemm_fp8_abft_set_tolerance(ft_gemm_handle* h, float abs_tol, float rel_tol) {
   if (h == nullptr || abs_tol < 0.0f || rel_tol < 0.0f) return fail(FT_ERR_INVALID, "null handle or negative tolerance");
   h->options.abs_tol = abs_tol;

@@ -50,6 +50,9 @@ cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, fl
 cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, int k, cudaStream_t stream);
 cudaError_t launch_expected(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
                             int nbands, int k, int mode, cudaStream_t stream);
+// src [rows, k] (dtype 0 FP32, 1 BF16, 2 FP16) * scale -> E4M3 dst, with the band sums of dst in the same pass; rows % 64 == 0, k % 8 == 0.
+cudaError_t launch_quantize_band_sums(const void* src, int src_dtype, void* dst, float* sums, float* mags, int rows, int k, float scale,
+                                      cudaStream_t stream);
 
 // FP16 variants for the attention path: `rows` may span many heads for the band sums; the expected
 // kernel treats `batch` problems of [rows, k] x [nbands, k] laid out back to back.

@@ -13,6 +13,7 @@
 //   expected:  32 partial sums per checksum, partial l taking k = l, l+32, ...
 //              in ascending order with one fma per step, then the pairwise tree
 //              (l, l+16), (l, l+8), ..., (l, l+1) of a shuffle-down reduction.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -101,6 +102,75 @@ __global__ void __launch_bounds__(kBandThreads) band_sums_kernel(const uint8_t* 
     so[q] = make_float4(s[4 * q], s[4 * q + 1], s[4 * q + 2], s[4 * q + 3]);
     mo[q] = make_float4(m[4 * q], m[4 * q + 1], m[4 * q + 2], m[4 * q + 3]);
   }
+}
+
+// ---------------------------------------------------------------------------
+// Producer of an FP8 operand fused with its band sums: src [rows, k] in FP32, BF16
+// or FP16 is scaled, rounded to E4M3 (round to nearest even, saturating) and
+// written to dst while the 64-row band sums and magnitudes of the ROUNDED values
+// are accumulated in the order of band_sums_kernel (rows ascending, one
+// accumulator per k), so the result equals a separate band-sum pass over dst bit
+// for bit.  The reference reads A again for this (src/s4:194-235, 634-640).
+// One thread owns 8 consecutive k; grid (ceil(k / 1024), rows / 64), 128 threads.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 lo = __ldg(reinterpret_cast<const float4*>(p)), hi = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {  // a BF16 is the upper half of an FP32
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <class S>
+__global__ void __launch_bounds__(kBandThreads) quantize_band_sums_kernel(const S* __restrict__ src, uint8_t* __restrict__ dst,
+                                                                          float* __restrict__ sums, float* __restrict__ mags,
+                                                                          int k, float scale) {
+  const int band = blockIdx.y;
+  const int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 8;
+  if (k0 >= k) return;
+  const size_t base = static_cast<size_t>(band) * 64 * k + k0;
+  float s[8], m[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = m[i] = 0.0f;
+#pragma unroll 8
+  for (int row = 0; row < 64; ++row) {
+    float v[8];
+    load8(src + base + static_cast<size_t>(row) * k, v);
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const __nv_fp8x2_storage_t two = __nv_cvt_float2_to_fp8x2(make_float2(v[i] * scale, v[i + 1] * scale), __NV_SATFINITE, __NV_E4M3);
+      packed[i >> 2] |= static_cast<uint32_t>(two) << (8 * (i & 3));
+      const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(two, __NV_E4M3)));
+      s[i] += f.x;
+      m[i] += fabsf(f.x);
+      s[i + 1] += f.y;
+      m[i + 1] += fabsf(f.y);
+    }
+    *reinterpret_cast<uint2*>(dst + base + static_cast<size_t>(row) * k) = make_uint2(packed[0], packed[1]);
+  }
+  float4* so = reinterpret_cast<float4*>(sums + static_cast<size_t>(band) * k + k0);
+  float4* mo = reinterpret_cast<float4*>(mags + static_cast<size_t>(band) * k + k0);
+  so[0] = make_float4(s[0], s[1], s[2], s[3]);
+  so[1] = make_float4(s[4], s[5], s[6], s[7]);
+  mo[0] = make_float4(m[0], m[1], m[2], m[3]);
+  mo[1] = make_float4(m[4], m[5], m[6], m[7]);
 }
 
 // FP16 operands (attention): one thread owns 8 consecutive k.
@@ -307,6 +377,20 @@ cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, fl
 cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, int k, cudaStream_t stream) {
   dim3 grid((k / 16 + kBandThreads - 1) / kBandThreads, (rows + 63) / 64);
   band_sums_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const uint8_t*>(x), sums, mags, rows, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_band_sums(const void* src, int src_dtype, void* dst, float* sums, float* mags, int rows, int k, float scale,
+                                      cudaStream_t stream) {
+  dim3 grid((k / 8 + kBandThreads - 1) / kBandThreads, rows / 64);
+  uint8_t* out = static_cast<uint8_t*>(dst);
+  if (src_dtype == 0) {
+    quantize_band_sums_kernel<float><<<grid, kBandThreads, 0, stream>>>(static_cast<const float*>(src), out, sums, mags, k, scale);
+  } else if (src_dtype == 1) {
+    quantize_band_sums_kernel<__nv_bfloat16><<<grid, kBandThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), out, sums, mags, k, scale);
+  } else {
+    quantize_band_sums_kernel<__half><<<grid, kBandThreads, 0, stream>>>(static_cast<const __half*>(src), out, sums, mags, k, scale);
+  }
   return cudaGetLastError();
 }
 

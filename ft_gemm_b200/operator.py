@@ -151,6 +151,16 @@ class AbftGemm:
             _abi.check(self.lib.ft_gemm_fp8_abft_refresh(self.handle, int(a_changed) | (int(b_changed) << 1),
                                                          _stream_ptr(stream)))
 
+    def quantize_a(self, src: torch.Tensor, scale: float = 1.0, stream: Optional[torch.cuda.Stream] = None):
+        """Overwrites A with E4M3(src * scale) (src: [M, K] float32, bfloat16 or float16 on the device) and refreshes the
+        cache, with the band sums of A taken in the same pass over src."""
+        dtypes = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+        if not src.is_cuda or src.dtype not in dtypes or not src.is_contiguous() or tuple(src.shape) != (self.m, self.k):
+            raise ValueError("src must be a contiguous [M, K] float32, bfloat16 or float16 CUDA tensor")
+        with torch.cuda.device(self.a.device):
+            _abi.check(self.lib.ft_gemm_fp8_abft_quantize_a(self.handle, ctypes.c_void_p(src.data_ptr()), dtypes[src.dtype],
+                                                            float(scale), _stream_ptr(stream)))
+
     def set_tolerance(self, abs_tol: float, rel_tol: float):
         _abi.check(self.lib.ft_gemm_fp8_abft_set_tolerance(self.handle, abs_tol, rel_tol))
 

@@ -127,6 +127,21 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a_e4m3, const 
  * (same pointers, same shape).  which: bit 0 = A changed, bit 1 = B changed. */
 int ft_gemm_fp8_abft_refresh(ft_gemm_handle* handle, int which, void* stream);
 
+/* Producer of A fused with its band sums, for callers whose A is produced on the
+ * device in a wider type (activations of an FP8 projection).  The reference makes
+ * a separate pass over the finished FP8 A for a_sums / a_magnitudes
+ * (src/s4_cluster_multicast_abft_fp8_gemm.cu:194-235, 634-640).  Here one pass
+ * over src [M,K] (row-major, src_dtype FT_SRC_*) writes E4M3(src * scale), rounded
+ * to nearest even and saturated, into the A buffer the handle was prepared with
+ * (which must be writable), accumulates the band sums of the rounded values in the
+ * reference's order, and is followed by the two expected-checksum launches; B's
+ * band sums are reused.  The resulting A and cache are bit-identical to quantising
+ * first and calling _refresh(handle, 1, ...). */
+#define FT_SRC_F32 0
+#define FT_SRC_BF16 1
+#define FT_SRC_F16 2
+int ft_gemm_fp8_abft_quantize_a(ft_gemm_handle* handle, const void* src, int src_dtype, float scale, void* stream);
+
 /* Replaces one enqueue_gemm() of the reference together with the two counter
  * memsets in front of it (src/s4_cluster_multicast_abft_fp8_gemm.cu:657-672,
  * 693-694): zeroes the handle's report and launches the fused GEMM + checker +

@@ -84,6 +84,12 @@ uint8_t ftq_e4m3_from_float(float x) {
 }
 
 /* src/s0_tiled_abft_fp8_gemm.cu:102-110 */
+/* The producer of an FP8 operand: out = E4M3(src * scale), one FP32 multiply and one rounding per element
+ * (what a fused quantise kernel in front of src/s4:194-235 has to produce). */
+void ftq_quantize_f32(const float* src, size_t count, float scale, uint8_t* out) {
+  for (size_t index = 0; index < count; ++index) out[index] = ftq_e4m3_from_float(src[index] * scale);
+}
+
 void ftq_generate_uniform(uint8_t* out, size_t count, uint32_t seed) {
 #pragma omp parallel for schedule(static)
   for (size_t index = 0; index < count; ++index) {

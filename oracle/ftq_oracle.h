@@ -37,6 +37,7 @@ enum { FTQ_C_COLMAJOR = 0 /* c[col*M+row] (S1-S4) */, FTQ_C_ROWMAJOR = 1 /* c[ro
 uint32_t ftq_mix_u32(uint32_t x);                       /* src/s0:93-100 */
 uint8_t ftq_e4m3_from_float(float x);                   /* __nv_fp8_e4m3(float): RNE, saturate to +-448, NaN -> 0x7f */
 float ftq_e4m3_to_float(uint8_t v);
+void ftq_quantize_f32(const float* src, size_t count, float scale, uint8_t* out);  /* E4M3(src * scale) */
 void ftq_generate_uniform(uint8_t* out, size_t count, uint32_t seed);          /* src/s0:102-110 */
 void ftq_generate_normal(uint8_t* out, size_t count, uint32_t seed, float sigma, float post_scale);
 

@@ -69,6 +69,12 @@ class Oracle:
     def encode(self, x):
         return int(self.lib.ftq_e4m3_from_float(ctypes.c_float(x)))
 
+    def quantize(self, src, scale=1.0):
+        src = np.ascontiguousarray(src, dtype=np.float32)
+        out = np.empty(src.size, dtype=np.uint8)
+        self.lib.ftq_quantize_f32(_ptr(src), ctypes.c_size_t(src.size), ctypes.c_float(scale), _ptr(out))
+        return out
+
     def generate_uniform(self, count, seed):
         out = np.empty(count, dtype=np.uint8)
         self.lib.ftq_generate_uniform(_ptr(out), ctypes.c_size_t(count), ctypes.c_uint32(seed))

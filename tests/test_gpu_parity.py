@@ -322,6 +322,36 @@ def test_host_entry_point_pipelined(ftg, oracle):
         host.close()
 
 
+def test_quantize_a_fused_with_band_sums(ftg, oracle):
+    """A produced on the device from FP32 / BF16 / FP16 with its band sums in the same pass: the bytes equal the oracle's
+    quantiser and the cache equals a fresh prepare on those bytes, bit for bit."""
+    m, n, k = 256, 320, 416
+    g = torch.Generator(device="cpu").manual_seed(31)
+    src32 = torch.randn((m, k), generator=g) * 3.0
+    src32[0, :8] = torch.tensor([0.0, -0.0, 1e6, -1e6, 17.0, 19.0, 2.0 ** -10, 447.9])
+    b = ftg.generate_fp8((n, k), SEED_B)
+    bh = b.cpu().numpy().ravel()
+    for dtype, scale in [(torch.float32, 1.0), (torch.bfloat16, 0.5), (torch.float16, 2.0), (torch.float32, 0.013)]:
+        src = src32.to(dtype)
+        a = torch.zeros((m, k), dtype=torch.uint8, device="cuda")
+        op = ftg.AbftGemm(a, b)  # prepared on a placeholder A, as a serving loop would do once
+        op.quantize_a(src.cuda(), scale)
+        want_a = oracle.quantize(src.float().numpy().ravel(), scale)
+        np.testing.assert_array_equal(a.cpu().numpy().ravel(), want_a)
+        got = op.cache()
+        want = oracle.expected(want_a, bh, m, n, k)
+        for name in ("a_sums", "a_magnitudes", "b_sums", "b_magnitudes", "expected_rows", "expected_cols", "row_scales", "col_scales"):
+            np.testing.assert_array_equal(got[name].numpy().view(np.uint32), want[name].view(np.uint32), err_msg=name)
+        c = op.new_output()
+        op.run(c, [(3, 4, 5, 50.0)])
+        rep = op.report()
+        assert (rep.bad_tiles, rep.corrected_tiles) == (1, 1)
+        np.testing.assert_allclose(c.cpu().numpy(), oracle.gemm_f32(want_a, bh, m, n, k), atol=2e-2)
+        with pytest.raises(ValueError):
+            op.quantize_a(src.cuda()[:128], scale)
+        op.close()
+
+
 def test_invalid_arguments_are_rejected(ftg):
     a = torch.zeros((128, 128), dtype=torch.uint8, device="cuda")
     b = torch.zeros((256, 128), dtype=torch.uint8, device="cuda")

@@ -224,3 +224,16 @@ def test_full_pass_reports_clean(oracle):
     c, secs, s = oracle.full_pass(a, b, m, n, k)
     assert s.bad_tiles == 0 and len(secs) == 3 and all(t >= 0 for t in secs)
     np.testing.assert_array_equal(c, oracle.gemm_f32(a, b, m, n, k))
+
+
+def test_quantize_matches_the_scalar_codec(oracle):
+    rng = np.random.default_rng(5)
+    src = np.concatenate([rng.standard_normal(4000) * 10.0 ** rng.integers(-4, 3, 4000), [0.0, -0.0, 448.0, 449.0, 1e9, -1e9, 2.0 ** -9,
+                          2.0 ** -10, 0.0009765625 * 1.5, 17.0, 18.0, 19.0]]).astype(np.float32)
+    for scale in (1.0, 0.37, 8.0):
+        got = oracle.quantize(src, scale)
+        want = np.array([oracle.encode(float(np.float32(x) * np.float32(scale))) for x in src], dtype=np.uint8)
+        np.testing.assert_array_equal(got, want)
+    # ties go to the even mantissa: 17 -> 16, 19 -> 20 (step 2 between 16 and 32), and the format saturates at 448
+    np.testing.assert_array_equal(oracle.decode(oracle.quantize(np.array([17.0, 18.0, 19.0, 1e9, -1e9], np.float32))),
+                                  np.array([16.0, 18.0, 20.0, 448.0, -448.0], np.float32))
