@@ -21,7 +21,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libf
 
 class FtOptions(ctypes.Structure):
     _fields_ = [("abs_tol", ctypes.c_float), ("rel_tol", ctypes.c_float), ("sm_limit", ctypes.c_int),
-                ("single_cta", ctypes.c_int), ("reserved", ctypes.c_int * 4)]
+                ("single_cta", ctypes.c_int), ("exact_prepare", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
 
 
 class FtFault(ctypes.Structure):

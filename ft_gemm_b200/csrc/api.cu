@@ -98,6 +98,10 @@ struct ft_gemm_handle {
   float *expected_rows = nullptr, *expected_cols = nullptr, *row_scales = nullptr, *col_scales = nullptr;
   DeviceReport* report = nullptr;
   CUtensorMap tmap_a{}, tmap_b{};
+  // tensor-core prepare: digit planes of the band sums (in the cache allocation) and their maps
+  uint8_t *planes_as = nullptr, *planes_am = nullptr, *planes_bs = nullptr, *planes_bm = nullptr;
+  CUtensorMap tmap_b128{}, tmap_as{}, tmap_am{}, tmap_bs{}, tmap_bm{};
+  int* prepare_status = nullptr;
   bool pair = false;  // 2-CTA form: clusters of two CTAs per 256x256 tile
   cudaEvent_t ev0 = nullptr, ev_mid = nullptr, ev1 = nullptr;
   bool prepare_timed = false;
@@ -124,16 +128,32 @@ int check_shape(int m, int n, int k) {
   return FT_OK;
 }
 
-int fill_cache(ft_gemm_handle* h, int which, cudaStream_t stream) {
+// The four checksum arrays from the operands and their band sums; `which` says whose band sums changed (bit 0 A, bit 1 B).
+int fill_expected(ft_gemm_handle* h, int which, cudaStream_t stream) {
   const int band_rows_a = h->m / 64, band_rows_b = (h->n + 63) / 64;
+  if (h->options.exact_prepare != 0) {
+    // expected_rows[(I,J),r] = sum_k A[64I+r,k] * b_sums[J,k]
+    FT_CUDA(launch_expected(h->a, h->b_sums, h->b_mags, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0, stream));
+    // expected_cols[(I,J),c] = sum_k a_sums[I,k] * B[64J+c,k]
+    FT_CUDA(launch_expected(h->b, h->a_sums, h->a_mags, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1, stream));
+    return FT_OK;
+  }
+  if (which & 1) FT_CUDA(launch_split_band_digits(h->a_sums, h->a_mags, h->planes_as, h->planes_am, band_rows_a, h->k, stream));
+  if (which & 2) FT_CUDA(launch_split_band_digits(h->b_sums, h->b_mags, h->planes_bs, h->planes_bm, band_rows_b, h->k, stream));
+  FT_CUDA(launch_expected_mma(h->tmap_a, h->tmap_bs, h->tmap_bm, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0,
+                              h->sm_count, h->prepare_status, stream));
+  FT_CUDA(launch_expected_mma(h->tmap_b128, h->tmap_as, h->tmap_am, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1,
+                              h->sm_count, h->prepare_status, stream));
+  return FT_OK;
+}
+
+int fill_cache(ft_gemm_handle* h, int which, cudaStream_t stream) {
   FT_CUDA(cudaEventRecord(h->ev0, stream));
   if (which & 1) FT_CUDA(launch_band_sums(h->a, h->a_sums, h->a_mags, h->m, h->k, stream));
   if (which & 2) FT_CUDA(launch_band_sums(h->b, h->b_sums, h->b_mags, h->n, h->k, stream));
   FT_CUDA(cudaEventRecord(h->ev_mid, stream));
-  // expected_rows[(I,J),r] = sum_k A[64I+r,k] * b_sums[J,k]
-  FT_CUDA(launch_expected(h->a, h->b_sums, h->b_mags, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0, stream));
-  // expected_cols[(I,J),c] = sum_k a_sums[I,k] * B[64J+c,k]
-  FT_CUDA(launch_expected(h->b, h->a_sums, h->a_mags, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1, stream));
+  int rc = fill_expected(h, which, stream);
+  if (rc != FT_OK) return rc;
   FT_CUDA(cudaEventRecord(h->ev1, stream));
   h->prepare_timed = true;
   h->last_stream = stream;
@@ -236,6 +256,7 @@ void ft_options_default(ft_options* options) {
   options->rel_tol = 2.0e-5f;
   options->sm_limit = 0;
   options->single_cta = 0;
+  options->exact_prepare = 0;
 }
 
 const char* ft_gemm_last_error(void) { return g_error; }
@@ -287,9 +308,13 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   size_t a_meta = static_cast<size_t>(m / 64) * k, b_meta = static_cast<size_t>((n + 63) / 64) * k;
   size_t checks = static_cast<size_t>(m / 64) * ((n + 63) / 64) * 64;
   size_t floats = 2 * a_meta + 2 * b_meta + 4 * checks;
-  h->cache_bytes = floats * sizeof(float);
-  cudaError_t err = cudaMalloc(&h->cache_base, h->cache_bytes);
+  const size_t planes_a = opts.exact_prepare != 0 ? 0 : prepare_mma_plane_bytes(m / 64, k);
+  const size_t planes_b = opts.exact_prepare != 0 ? 0 : prepare_mma_plane_bytes((n + 63) / 64, k);
+  h->cache_bytes = floats * sizeof(float) + 2 * planes_a + 2 * planes_b;
+  cudaError_t err = opts.exact_prepare != 0 ? cudaSuccess : configure_prepare_mma();
+  if (err == cudaSuccess) err = cudaMalloc(&h->cache_base, h->cache_bytes);
   if (err == cudaSuccess) err = cudaMalloc(&h->report, sizeof(DeviceReport));
+  if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->prepare_status), sizeof(int));
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev0);
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev_mid);
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev1);
@@ -307,12 +332,28 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   h->expected_cols = cursor, cursor += checks;
   h->row_scales = cursor, cursor += checks;
   h->col_scales = cursor, cursor += checks;
+  if (opts.exact_prepare == 0) {  // every offset is a multiple of 16 bytes: K % 32 == 0 and plane rows come in groups of 160
+    uint8_t* bytes = reinterpret_cast<uint8_t*>(cursor);
+    h->planes_as = bytes, bytes += planes_a;
+    h->planes_am = bytes, bytes += planes_a;
+    h->planes_bs = bytes, bytes += planes_b;
+    h->planes_bm = bytes, bytes += planes_b;
+  }
 
   rc = make_operand_map(&h->tmap_a, a, m, k, 128);
   if (rc == FT_OK) rc = make_operand_map(&h->tmap_b, b, n, k, h->pair ? 128 : 256);
+  if (rc == FT_OK && opts.exact_prepare == 0) {
+    const int rows_a = prepare_mma_plane_rows(m / 64), rows_b = prepare_mma_plane_rows((n + 63) / 64);
+    rc = make_operand_map(&h->tmap_b128, b, n, k, 128);
+    if (rc == FT_OK) rc = make_operand_map(&h->tmap_as, h->planes_as, rows_a, k, 160);
+    if (rc == FT_OK) rc = make_operand_map(&h->tmap_am, h->planes_am, rows_a, k, 160);
+    if (rc == FT_OK) rc = make_operand_map(&h->tmap_bs, h->planes_bs, rows_b, k, 160);
+    if (rc == FT_OK) rc = make_operand_map(&h->tmap_bm, h->planes_bm, rows_b, k, 160);
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (rc == FT_OK) {
     cudaError_t merr = cudaMemsetAsync(h->report, 0, sizeof(DeviceReport), stream);
+    if (merr == cudaSuccess) merr = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
     if (merr != cudaSuccess) rc = fail(FT_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(merr));
   }
   if (rc == FT_OK) rc = fill_cache(h, 3, stream);
@@ -335,13 +376,12 @@ int ft_gemm_fp8_abft_quantize_a(ft_gemm_handle* h, const void* src, int src_dtyp
   if ((reinterpret_cast<uintptr_t>(src) & 15) != 0) return fail(FT_ERR_INVALID, "the source must be 16-byte aligned");
   if (!(scale == scale) || scale == 0.0f) return fail(FT_ERR_INVALID, "scale must be a non-zero number");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  const int band_rows_a = h->m / 64, band_rows_b = (h->n + 63) / 64;
   FT_CUDA(cudaEventRecord(h->ev0, stream));
   // A and its band sums in one pass over the source; the caller's A buffer is written here
   FT_CUDA(launch_quantize_band_sums(src, src_dtype, const_cast<void*>(h->a), h->a_sums, h->a_mags, h->m, h->k, scale, stream));
   FT_CUDA(cudaEventRecord(h->ev_mid, stream));
-  FT_CUDA(launch_expected(h->a, h->b_sums, h->b_mags, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0, stream));
-  FT_CUDA(launch_expected(h->b, h->a_sums, h->a_mags, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1, stream));
+  int rc = fill_expected(h, 1, stream);
+  if (rc != FT_OK) return rc;
   FT_CUDA(cudaEventRecord(h->ev1, stream));
   h->prepare_timed = true;
   h->last_stream = stream;
@@ -429,6 +469,9 @@ int ft_gemm_fp8_abft_report(ft_gemm_handle* h, ft_report* out) {
   FT_CUDA(cudaStreamSynchronize(h->last_stream));
   DeviceReport dev;
   FT_CUDA(cudaMemcpy(&dev, h->report, sizeof(DeviceReport), cudaMemcpyDeviceToHost));
+  int prepare_status = 0;
+  FT_CUDA(cudaMemcpy(&prepare_status, h->prepare_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (prepare_status != 0) dev.status = prepare_status;  // a prepare kernel gave up: the cache is not valid
   std::memset(out, 0, sizeof(*out));
   out->status = dev.status != 0 ? FT_ERR_TIMEOUT : FT_OK;
   out->bad_tiles = dev.bad_tiles;
@@ -481,6 +524,7 @@ int ft_gemm_fp8_abft_destroy(ft_gemm_handle* h) {
   if (h->last_stream != nullptr || h->cache_base != nullptr) cudaStreamSynchronize(h->last_stream);
   cudaFree(h->cache_base);
   cudaFree(h->report);
+  cudaFree(h->prepare_status);
   if (h->ev0) cudaEventDestroy(h->ev0);
   if (h->ev_mid) cudaEventDestroy(h->ev_mid);
   if (h->ev1) cudaEventDestroy(h->ev1);

@@ -60,6 +60,16 @@ cudaError_t launch_band_sums_f16(const void* x, float* sums, float* mags, size_t
 cudaError_t launch_expected_f16(const void* x, const float* band_sums, const float* band_mags, float* expected, float* scales, int rows,
                                 int nbands, int k, int mode, int batch, cudaStream_t stream);
 
+// Expected checksums on the tensor cores (prepare_mma.cu): the band sums are split into five E4M3 digit planes
+// (plane rows = prepare_mma_plane_rows(nbands), k bytes each), then X times the planes gives the four cache arrays.
+// tmap_x: X [rows, k] with a 128-row box; tmap_ws / tmap_wm: the planes of the sums / magnitudes with a 160-row box.
+cudaError_t configure_prepare_mma();
+size_t prepare_mma_plane_bytes(int nbands, int k);
+int prepare_mma_plane_rows(int nbands);
+cudaError_t launch_split_band_digits(const float* sums, const float* mags, void* ws, void* wm, int nbands, int k, cudaStream_t stream);
+cudaError_t launch_expected_mma(const CUtensorMap& tmap_x, const CUtensorMap& tmap_ws, const CUtensorMap& tmap_wm, float* expected,
+                                float* scales, int rows, int nbands, int k, int mode, int sm_count, int* status, cudaStream_t stream);
+
 // Fused FP8 GEMM + ABFT checker/corrector.  tmap_a / tmap_b describe A[M,K] and
 // B[N,K] with 128-byte-swizzled boxes of (128 K-bytes x 128 rows) and
 // (128 K-bytes x 256 rows).

@@ -1,0 +1,343 @@
+// Expected checksums on the tensor cores.
+//
+// expected_rows[(I,J),r] = sum_k A[64I+r,k] * b_sums[J,k] is a GEMM of A against
+// the band sums of B, and the three other cache arrays are the same with |.| or
+// with the operands swapped (src/s4_cluster_multicast_abft_fp8_gemm.cu:237-294).
+// The reference and expected_checksums_kernel (prepare.cu) evaluate it with FP32
+// FMAs on the CUDA cores, M*N*K/16 of them.  Here it runs as FP8 tcgen05.mma:
+//   * a band sum is a sum of 64 E4M3 values, i.e. an integer multiple of 2^-9
+//     below 2^24 * 2^-9, held exactly by FP32.  split_band_digits_kernel writes it
+//     as five signed radix-32 digits d in [-15, 16] (exact E4M3 integers), one
+//     byte plane per digit: sum = 2^-9 * (d0 + 32 d1 + ... + 32^4 d4);
+//   * X (A or B itself, straight from the caller's memory by TMA, no conversion)
+//     times the digit planes gives five FP32 accumulators per checksum, each a sum
+//     of exact products; the epilogue recombines them by Horner's rule in FP32;
+//   * the scales need |X|: a helper warpgroup clears the sign bits of each staged
+//     X tile into a second shared-memory tile (same swizzled layout).
+// The result equals the reference's value up to FP32 accumulation order (the
+// digits are exact), not bit for bit; the CUDA-core kernel remains for that.
+//
+// One CTA (192 threads) per SM, persistent over tiles of 128 rows of X x 32 bands:
+//   warp 0      TMA producer: X tile 128x128 B, digit planes of sums and of
+//               magnitudes 160x128 B each, 3 stages;
+//   warp 1      one thread issues, per 32 B of K, X * Ws^T -> TMEM columns [0,160)
+//               and |X| * Wm^T -> columns [160,320) (M128 N160 K32);
+//   warps 2-5   |X| tiles during the main loop, then the epilogue: thread = row.
+// Every wait is bounded; on expiry the kernel sets *status and leaves.
+#include <cuda.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace ftg {
+
+namespace {
+
+constexpr int kPmRows = 128;                    // rows of X per tile
+constexpr int kPmBands = 32;                    // bands per tile
+constexpr int kPmDigits = 5;                    // radix-32 digits per band sum
+constexpr int kPmCols = kPmBands * kPmDigits;   // 160 accumulator columns per operand
+constexpr int kPmBlockK = 128;
+constexpr int kPmStages = 3;
+constexpr int kPmXBytes = kPmRows * kPmBlockK;  // 16 KiB
+constexpr int kPmWBytes = kPmCols * kPmBlockK;  // 20 KiB
+constexpr int kPmStageBytes = 2 * kPmXBytes + 2 * kPmWBytes;
+constexpr int kPmThreads = 192;
+constexpr uint32_t kPmTmemColumns = 512;
+constexpr uint64_t kPmTimeoutNs = 2000000000ull;
+
+struct PmTail {
+  uint64_t full[kPmStages];      // TMA data landed
+  uint64_t abs_full[kPmStages];  // |X| written
+  uint64_t empty[kPmStages];     // MMAs have read the stage
+  uint64_t acc_full, acc_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr int kPmSmemBytes = kPmStages * kPmStageBytes + static_cast<int>(sizeof(PmTail));
+
+__device__ __forceinline__ bool pm_any(bool flag) {  // OR over the 128 threads of warps 2-5
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(flag))
+      : "memory");
+  return out != 0;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Digit planes.  sums / mags: [nbands, k] FP32.  Plane row of (band J, digit d):
+// (J / 32) * 160 + d * 32 + J % 32, each row k bytes; bands past nbands (padding of
+// the last group of 32) are written as zeros.  grid (ceil(k / 256), padded bands).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) split_band_digits_kernel(const float* __restrict__ sums, const float* __restrict__ mags,
+                                                                uint8_t* __restrict__ ws, uint8_t* __restrict__ wm, int nbands,
+                                                                int k) {
+  const int band = blockIdx.y;
+  const int kk = blockIdx.x * 256 + threadIdx.x;
+  if (kk >= k) return;
+  const size_t row0 = static_cast<size_t>(band / kPmBands) * kPmCols + band % kPmBands;
+  const bool valid = band < nbands;
+  const float values[2] = {valid ? sums[static_cast<size_t>(band) * k + kk] : 0.0f, valid ? mags[static_cast<size_t>(band) * k + kk] : 0.0f};
+  uint8_t* const planes[2] = {ws, wm};
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const float v = values[which];
+    uint32_t t = static_cast<uint32_t>(fabsf(v) * 512.0f);  // exact: a multiple of 2^-9 below 2^15
+    const float sign = v < 0.0f ? -1.0f : 1.0f;
+#pragma unroll
+    for (int d = 0; d < kPmDigits; ++d) {
+      int digit = static_cast<int>(t & 31u);
+      t >>= 5;
+      if (digit > 16) {  // signed digits keep every plane an exact E4M3 integer
+        digit -= 32;
+        t += 1;
+      }
+      planes[which][(row0 + static_cast<size_t>(d) * kPmBands) * k + kk] =
+          static_cast<uint8_t>(__nv_cvt_float_to_fp8(sign * static_cast<float>(digit), __NV_SATFINITE, __NV_E4M3));
+    }
+  }
+}
+
+// mode 0 (X = A, bands of B): out index = ((row / 64) * nbands + band) * 64 + row % 64
+// mode 1 (X = B, bands of A): out index = (band * ceil(rows / 64) + row / 64) * 64 + row % 64
+__global__ void __launch_bounds__(kPmThreads, 1)
+expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_ws,
+                              const __grid_constant__ CUtensorMap tmap_wm, float* __restrict__ expected, float* __restrict__ scales,
+                              int rows, int nbands, int k, int mode, int* __restrict__ status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(status, 2);
+    return;
+  }
+  uint8_t* smem_x = smem_raw;
+  uint8_t* smem_ax = smem_raw + kPmStages * kPmXBytes;
+  uint8_t* smem_ws = smem_raw + 2 * kPmStages * kPmXBytes;
+  uint8_t* smem_wm = smem_ws + kPmStages * kPmWBytes;
+  PmTail& tail = *reinterpret_cast<PmTail*>(smem_raw + kPmStages * kPmStageBytes);
+  volatile int* abort_flag = &tail.abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_blocks = (rows + kPmRows - 1) / kPmRows;
+  const int groups = (nbands + kPmBands - 1) / kPmBands;
+  const int num_tiles = row_blocks * groups;
+  const int num_kb = (k + kPmBlockK - 1) / kPmBlockK;
+  const int worker = blockIdx.x, workers = gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPmStages; ++s) {
+      mbar_init(&tail.full[s], 1);
+      mbar_init(&tail.abs_full[s], 128);
+      mbar_init(&tail.empty[s], 1);
+    }
+    mbar_init(&tail.acc_full, 1);
+    mbar_init(&tail.acc_empty, 128);
+    tail.abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_x);
+    prefetch_tensormap(&tmap_ws);
+    prefetch_tensormap(&tmap_wm);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail.tmem_base, kPmTmemColumns);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tail.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------- producer
+      int s = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int t = worker; t < num_tiles && alive; t += workers) {
+        const int group = t % groups, row_block = t / groups;  // neighbouring CTAs share the X tile in L2
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, kPmTimeoutNs)) {
+            alive = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&tail.full[s], kPmXBytes + 2 * kPmWBytes);
+          tma_load_2d(smem_x + s * kPmXBytes, &tmap_x, &tail.full[s], kb * kPmBlockK, row_block * kPmRows);
+          tma_load_2d(smem_ws + s * kPmWBytes, &tmap_ws, &tail.full[s], kb * kPmBlockK, group * kPmCols);
+          tma_load_2d(smem_wm + s * kPmWBytes, &tmap_wm, &tail.full[s], kb * kPmBlockK, group * kPmCols);
+          if (++s == kPmStages) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc_e4m3_f32(kPmRows, kPmCols);
+      int s = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool alive = true;
+      for (int t = worker; t < num_tiles && alive; t += workers) {
+        if (!mbar_wait_bounded(&tail.acc_empty, acc_phase ^ 1, abort_flag, kPmTimeoutNs)) break;
+        tcgen05_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&tail.full[s], phase, abort_flag, kPmTimeoutNs) ||
+              !mbar_wait_bounded(&tail.abs_full[s], phase, abort_flag, kPmTimeoutNs)) {
+            alive = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint64_t desc_x = make_smem_desc_sw128(smem_u32(smem_x + s * kPmXBytes));
+          const uint64_t desc_ax = make_smem_desc_sw128(smem_u32(smem_ax + s * kPmXBytes));
+          const uint64_t desc_ws = make_smem_desc_sw128(smem_u32(smem_ws + s * kPmWBytes));
+          const uint64_t desc_wm = make_smem_desc_sw128(smem_u32(smem_wm + s * kPmWBytes));
+#pragma unroll
+          for (int kk = 0; kk < kPmBlockK / 32; ++kk) {  // +32 bytes of K inside the swizzle row = +2 in the address field
+            umma_f8f6f4(tmem_base, desc_x + 2 * kk, desc_ws + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f8f6f4(tmem_base + kPmCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&tail.empty[s]);
+          if (++s == kPmStages) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (alive) umma_commit(&tail.acc_full);
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- |X| tiles, then the epilogue
+    const int tid = threadIdx.x - 64;  // 0..127
+    const int quarter = warp & 3;      // TMEM lanes [32 * quarter, +32) belong to this warp
+    const int row_in_block = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int rows64 = (rows + 63) >> 6;
+    int s = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool alive = true;
+    for (int t = worker; t < num_tiles && alive; t += workers) {
+      const int group = t % groups, row_block = t / groups;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        bool ok = true;
+        if (tid == 0) ok = mbar_wait_bounded(&tail.full[s], phase, abort_flag, kPmTimeoutNs);
+        if (pm_any(!ok)) {  // uniform over the 128 threads
+          alive = false;
+          break;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(smem_x + s * kPmXBytes);
+        uint4* dst = reinterpret_cast<uint4*>(smem_ax + s * kPmXBytes);
+#pragma unroll
+        for (int c = 0; c < kPmXBytes / 16 / 128; ++c) {  // the swizzle permutes whole 16-byte chunks: a bytewise AND keeps the layout
+          uint4 v = src[c * 128 + tid];
+          v.x &= 0x7f7f7f7fu;
+          v.y &= 0x7f7f7f7fu;
+          v.z &= 0x7f7f7f7fu;
+          v.w &= 0x7f7f7f7fu;
+          dst[c * 128 + tid] = v;
+        }
+        fence_proxy_async_shared();
+        mbar_arrive(&tail.abs_full[s]);
+        if (++s == kPmStages) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+      if (!alive) break;
+      bool ok = true;
+      if (tid == 0) ok = mbar_wait_bounded(&tail.acc_full, acc_phase, abort_flag, kPmTimeoutNs);
+      if (pm_any(!ok)) break;
+      acc_phase ^= 1;
+      tcgen05_fence_after();
+      // Horner over the digits, most significant first: value = 2^-9 * sum_d 32^d * acc_d
+      float e[2][2][16];  // [sums | magnitudes][band half][band]
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t base = lane_addr + which * kPmCols + half * 16;
+          tmem_ld_32x32b_x16(base + (kPmDigits - 1) * kPmBands, e[which][half]);
+          tmem_wait_ld();
+#pragma unroll
+          for (int d = kPmDigits - 2; d >= 0; --d) {
+            float a[16];
+            tmem_ld_32x32b_x16(base + d * kPmBands, a);
+            tmem_wait_ld();
+#pragma unroll
+            for (int b = 0; b < 16; ++b) e[which][half][b] = __fmaf_rn(e[which][half][b], 32.0f, a[b]);
+          }
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(&tail.acc_empty);  // the accumulators are in registers: the next tile may start
+      const int row = row_block * kPmRows + row_in_block;
+      if (row < rows64 * 64) {  // rows of the last 64-row group past `rows` were zero-filled by the copy: their checksums are zeros
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int b = 0; b < 16; ++b) {
+            const int band = group * kPmBands + half * 16 + b;
+            if (band < nbands) {
+              const size_t tile = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band : static_cast<size_t>(band) * rows64 + (row >> 6);
+              const size_t out = tile * 64 + (row & 63);
+              expected[out] = e[0][half][b] * 0.001953125f;
+              scales[out] = e[1][half][b] * 0.001953125f;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------- teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if (tail.abort_flag != 0) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);  // copies and MMAs still in flight land before TMEM and smem go away
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kPmTmemColumns);
+  }
+}
+
+cudaError_t configure_prepare_mma() {
+  return cudaFuncSetAttribute(expected_checksums_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPmSmemBytes);
+}
+
+size_t prepare_mma_plane_bytes(int nbands, int k) {
+  return static_cast<size_t>((nbands + kPmBands - 1) / kPmBands) * kPmCols * k;
+}
+
+int prepare_mma_plane_rows(int nbands) { return (nbands + kPmBands - 1) / kPmBands * kPmCols; }
+
+cudaError_t launch_split_band_digits(const float* sums, const float* mags, void* ws, void* wm, int nbands, int k, cudaStream_t stream) {
+  const int padded = (nbands + kPmBands - 1) / kPmBands * kPmBands;
+  dim3 grid((k + 255) / 256, padded);
+  split_band_digits_kernel<<<grid, 256, 0, stream>>>(sums, mags, static_cast<uint8_t*>(ws), static_cast<uint8_t*>(wm), nbands, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_expected_mma(const CUtensorMap& tmap_x, const CUtensorMap& tmap_ws, const CUtensorMap& tmap_wm, float* expected,
+                                float* scales, int rows, int nbands, int k, int mode, int sm_count, int* status, cudaStream_t stream) {
+  const int tiles = ((rows + kPmRows - 1) / kPmRows) * ((nbands + kPmBands - 1) / kPmBands);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  expected_checksums_mma_kernel<<<grid, kPmThreads, kPmSmemBytes, stream>>>(tmap_x, tmap_ws, tmap_wm, expected, scales, rows, nbands, k,
+                                                                            mode, status);
+  return cudaGetLastError();
+}
+
+}  // namespace ftg

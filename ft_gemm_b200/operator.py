@@ -86,7 +86,8 @@ class AbftGemm:
     """Prepared ABFT FP8 GEMM for one (A[M,K], B[N,K]) pair of E4M3 tensors."""
 
     def __init__(self, a: torch.Tensor, b: torch.Tensor, abs_tol: float = 1.0e-2, rel_tol: float = 2.0e-5,
-                 sm_limit: int = 0, single_cta: bool = False, stream: Optional[torch.cuda.Stream] = None):
+                 sm_limit: int = 0, single_cta: bool = False, exact_prepare: bool = False,
+                 stream: Optional[torch.cuda.Stream] = None):
         _check_operand(a, "A")
         _check_operand(b, "B")
         if a.shape[1] != b.shape[1]:
@@ -99,6 +100,8 @@ class AbftGemm:
         self.lib.ft_options_default(ctypes.byref(options))
         options.abs_tol, options.rel_tol, options.sm_limit = abs_tol, rel_tol, sm_limit
         options.single_cta = int(single_cta)
+        options.exact_prepare = int(exact_prepare)
+        self.exact_prepare = bool(exact_prepare)
         self.handle = ctypes.c_void_p()
         with torch.cuda.device(a.device):
             _abi.check(self.lib.ft_gemm_fp8_abft_prepare(ctypes.byref(self.handle), ctypes.c_void_p(a.data_ptr()),

@@ -56,7 +56,10 @@ typedef struct {
   float rel_tol;  /* default 2e-5 */
   int sm_limit;   /* 0 = one persistent CTA per SM; >0 caps the grid (testing) */
   int single_cta; /* 0 = pair two CTAs on one 256x256 tile when M % 256 == 0; 1 = always one CTA per 128x256 tile */
-  int reserved[4];
+  int exact_prepare; /* 0 (default): the expected checksums are computed on the tensor cores (band sums split into exact
+                        E4M3 digits; equal to the reference's values up to FP32 accumulation order); 1: on the CUDA
+                        cores in the reference's summation order (src/s4:264-282), bit-identical to its cache, ~10x slower */
+  int reserved[3];
 } ft_options;
 
 /* A test fault: `value` is added to the accumulator element (row, col) of ABFT

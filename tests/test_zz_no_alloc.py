@@ -40,7 +40,7 @@ def test_noalloc_prepare_matches_prepare_twice_in_a_row():
         a = ftg.generate_fp8((m, k), seeds[0])
         b = ftg.generate_fp8((n, k), seeds[1])
         got = _noalloc(ftg, a, b)
-        op = ftg.AbftGemm(a, b)
+        op = ftg.AbftGemm(a, b, exact_prepare=True)
         want = op.cache()
         for name, value in got.items():
             np.testing.assert_array_equal(value.view(np.uint32), want[name].numpy().ravel().view(np.uint32), err_msg=name)
