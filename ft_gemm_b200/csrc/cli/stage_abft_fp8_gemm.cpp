@@ -46,6 +46,10 @@ int main(int argc, char** argv) {
   CLI_FT(ft_gemm_fp8_abft_prepare(&handle, d_a, d_b, o.m, o.n, o.k, &options, stream));
   ft_report report;
   CLI_FT(ft_gemm_fp8_abft_report(handle, &report));
+  // The timings reported below are those of a second fill of the cache: the first one also pays for loading the
+  // prepare kernels onto the device (lazy module loading), which is not part of the operator's cost.
+  CLI_FT(ft_gemm_fp8_abft_refresh(handle, 3, stream));
+  CLI_FT(ft_gemm_fp8_abft_report(handle, &report));
   float input_metadata_ms = report.prepare_input_ms, expected_metadata_ms = report.prepare_expected_ms;
   float metadata_prepare_ms = input_metadata_ms + expected_metadata_ms;
   ft_cache_view cache;

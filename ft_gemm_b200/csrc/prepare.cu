@@ -64,43 +64,73 @@ __global__ void generate_fp8_kernel(uint8_t* out, size_t count, uint32_t seed, i
 
 // ---------------------------------------------------------------------------
 // band sums: x is [rows, k] FP8; one band = 64 consecutive rows.
-// grid (k / (16 * 128), bands), 128 threads; each thread owns 16 consecutive k.
+// grid (ceil(k / 1024), bands), 256 threads: 64 chunks of 16 consecutive k x 4 quarters of 16 rows.
 // ---------------------------------------------------------------------------
 constexpr int kBandThreads = 128;
 
-__global__ void __launch_bounds__(kBandThreads) band_sums_kernel(const uint8_t* __restrict__ x, float* __restrict__ sums,
-                                                                 float* __restrict__ mags, int rows, int k) {
-  int band = blockIdx.y;
-  int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 16;
-  if (k0 >= k) return;
-  const uint8_t* base = x + static_cast<size_t>(band) * 64 * k + k0;
+// A sum of 64 E4M3 values (multiples of 2^-9, at most 448 in magnitude) is a multiple of 2^-9 below 2^24 * 2^-9, so
+// every partial sum is exact in FP32 and the order of the additions cannot change the result: the 64 rows of a band
+// are summed as four quarters of 16 rows by four threads and combined through shared memory, which gives the bits of
+// the reference's serial loop (src/s4:194-235) with four times as many loads in flight.
+constexpr int kBandQuarters = 4;
+constexpr int kBandChunks = 64;  // 16-byte chunks of k per CTA
+
+__global__ void __launch_bounds__(kBandQuarters* kBandChunks) band_sums_kernel(const uint8_t* __restrict__ x, float* __restrict__ sums,
+                                                                               float* __restrict__ mags, int rows, int k) {
+  __shared__ float part[2][kBandQuarters - 1][kBandChunks][17];  // [sums | mags][quarter 1..3][chunk][16 + pad]
+  const int band = blockIdx.y;
+  const int chunk = threadIdx.x % kBandChunks, quarter = threadIdx.x / kBandChunks;
+  const int k0 = (blockIdx.x * kBandChunks + chunk) * 16;
+  const bool active = k0 < k;
   const int valid = min(64, rows - band * 64);  // the last band of B may be short (src/s3:203)
   float s[16], m[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) s[i] = m[i] = 0.0f;
-#pragma unroll 8
-  for (int row = 0; row < valid; ++row) {
-    uint4 packed = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(row) * k));
-    uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+  if (active) {
+    const uint8_t* base = x + (static_cast<size_t>(band) * 64 + quarter * 16) * k + k0;
+    const int my_rows = max(0, min(16, valid - quarter * 16));
+#pragma unroll 16
+    for (int row = 0; row < my_rows; ++row) {
+      uint4 packed = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(row) * k));
+      uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < 4; ++w) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        __half2_raw pair = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(words[w] >> (16 * h)), __NV_E4M3);
-        float2 f = __half22float2(__half2(pair));
-        s[w * 4 + h * 2 + 0] += f.x;
-        m[w * 4 + h * 2 + 0] += fabsf(f.x);
-        s[w * 4 + h * 2 + 1] += f.y;
-        m[w * 4 + h * 2 + 1] += fabsf(f.y);
+        for (int h = 0; h < 2; ++h) {
+          __half2_raw pair = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(words[w] >> (16 * h)), __NV_E4M3);
+          float2 f = __half22float2(__half2(pair));
+          s[w * 4 + h * 2 + 0] += f.x;
+          m[w * 4 + h * 2 + 0] += fabsf(f.x);
+          s[w * 4 + h * 2 + 1] += f.y;
+          m[w * 4 + h * 2 + 1] += fabsf(f.y);
+        }
       }
     }
   }
-  float4* so = reinterpret_cast<float4*>(sums + static_cast<size_t>(band) * k + k0);
-  float4* mo = reinterpret_cast<float4*>(mags + static_cast<size_t>(band) * k + k0);
+  if (quarter > 0) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    so[q] = make_float4(s[4 * q], s[4 * q + 1], s[4 * q + 2], s[4 * q + 3]);
-    mo[q] = make_float4(m[4 * q], m[4 * q + 1], m[4 * q + 2], m[4 * q + 3]);
+    for (int i = 0; i < 16; ++i) {
+      part[0][quarter - 1][chunk][i] = s[i];
+      part[1][quarter - 1][chunk][i] = m[i];
+    }
+  }
+  __syncthreads();
+  if (quarter == 0 && active) {
+#pragma unroll
+    for (int q = 0; q < kBandQuarters - 1; ++q) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        s[i] += part[0][q][chunk][i];
+        m[i] += part[1][q][chunk][i];
+      }
+    }
+    float4* so = reinterpret_cast<float4*>(sums + static_cast<size_t>(band) * k + k0);
+    float4* mo = reinterpret_cast<float4*>(mags + static_cast<size_t>(band) * k + k0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      so[q] = make_float4(s[4 * q], s[4 * q + 1], s[4 * q + 2], s[4 * q + 3]);
+      mo[q] = make_float4(m[4 * q], m[4 * q + 1], m[4 * q + 2], m[4 * q + 3]);
+    }
   }
 }
 
@@ -375,8 +405,8 @@ cudaError_t launch_generate(void* out, size_t count, uint32_t seed, int dist, fl
 }
 
 cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, int k, cudaStream_t stream) {
-  dim3 grid((k / 16 + kBandThreads - 1) / kBandThreads, (rows + 63) / 64);
-  band_sums_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const uint8_t*>(x), sums, mags, rows, k);
+  dim3 grid((k / 16 + kBandChunks - 1) / kBandChunks, (rows + 63) / 64);
+  band_sums_kernel<<<grid, kBandQuarters * kBandChunks, 0, stream>>>(static_cast<const uint8_t*>(x), sums, mags, rows, k);
   return cudaGetLastError();
 }
 
