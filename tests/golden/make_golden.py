@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the reference's OWN kernels.
 
-Needs a GPU and the harness binaries oracle/_ref/ref_harness_s0 and
-oracle/_ref/ref_harness_s4 (built by `make -C oracle ref` where the reference
+Needs a GPU and the harness binaries oracle/_ref/ref_harness_s0,
+oracle/_ref/ref_harness_s4 and oracle/_ref/ref_harness_gs (built by `make -C oracle ref` where the reference
 checkout is available; they compile the reference's .cu files in place and launch
 its kernels unmodified).  Usage, on a machine with a GPU:
 
@@ -25,6 +25,9 @@ REF = os.path.join(ROOT, "oracle", "_ref")
 S4_CASES = [(128, 256, 128, True), (64, 200, 96, True), (256, 512, 384, False), (128, 256, 1024, False)]
 S0_CASES = [(64, 64, 64, True), (40, 56, 48, True), (96, 80, 160, False)]
 S0_SCENARIOS = ("clean", "inject", "two_rc", "same_row", "cancel")
+# GEMM + softmax cross-nonlinearity check: (M, N, K, fault_row, fault_col, fault_value)
+GS_CASES = [(64, 64, 64, 32, 32, 1.0), (96, 200, 128, 5, 199, -0.75), (128, 1000, 256, 100, 0, 2.5)]
+GS_PHASES = ("clean", "fault", "recovered")
 
 
 def _read(path, dtype):
@@ -62,6 +65,29 @@ def run_s0(m, n, k, keep_inputs, outdir):
         np.savez_compressed(os.path.join(outdir, f"s0_path_{m}x{n}x{k}.npz"), **data)
 
 
+def run_gs(m, n, k, fault_row, fault_col, fault_value, outdir):
+    with tempfile.TemporaryDirectory() as tmp:
+        subprocess.run([os.path.join(REF, "ref_harness_gs"), str(m), str(n), str(k), str(fault_row), str(fault_col), str(fault_value),
+                        tmp], check=True)
+        data = {"a": _read(os.path.join(tmp, "a.u8"), np.uint8), "b": _read(os.path.join(tmp, "b.u8"), np.uint8),
+                "logits": _read(os.path.join(tmp, "logits.f32"), np.float32),
+                "expected_sum": _read(os.path.join(tmp, "expected_sum.f64"), np.float64),
+                "expected_weighted": _read(os.path.join(tmp, "expected_weighted.f64"), np.float64)}
+        for p in GS_PHASES:
+            prob = _read(os.path.join(tmp, f"probabilities_{p}.f32"), np.float32)
+            if m * n <= 20000:
+                data["probabilities_" + p] = prob
+            else:  # the large case keeps the faulty row only
+                data["probabilities_row_" + p] = prob.reshape(m, n)[fault_row].copy()
+            for name in ("actual_sum", "actual_weighted", "probability_sum", "log_z", "correction_delta"):
+                data[f"{name}_{p}"] = _read(os.path.join(tmp, f"{name}_{p}.f64"), np.float64)
+            for name in ("detected", "estimated_col", "counts"):
+                data[f"{name}_{p}"] = _read(os.path.join(tmp, f"{name}_{p}.i32"), np.int32)
+        data["shape"] = np.array([m, n, k], dtype=np.int32)
+        data["fault"] = np.array([fault_row, fault_col, fault_value], dtype=np.float64)
+        np.savez_compressed(os.path.join(outdir, f"gs_{m}x{n}x{k}.npz"), **data)
+
+
 def main():
     outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(outdir, exist_ok=True)
@@ -69,6 +95,8 @@ def main():
         run_s4(*case, outdir)
     for case in S0_CASES:
         run_s0(*case, outdir)
+    for case in GS_CASES:
+        run_gs(*case, outdir)
     print("golden fixtures written to", outdir, sorted(os.listdir(outdir)))
 
 
