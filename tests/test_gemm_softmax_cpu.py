@@ -72,6 +72,7 @@ def test_identities_on_random_logits():
     assert gs.analyze(es, ew, gs.softmax_checks(y), n)["counts"].tolist() == [0, 0]
     y[3, 17] += np.float32(1e-3)  # w_17 = -265: the weighted identity fires, the unweighted one cannot locate it
     assert gs.analyze(es, ew, gs.softmax_checks(y), n)["counts"].tolist() == [1, 0]
+    y = x.copy()
     y[3, 17] += np.float32(0.5)
     out = gs.analyze(es, ew, gs.softmax_checks(y), n)
     assert out["counts"].tolist() == [1, 1] and out["estimated_col"][3] == 17
