@@ -8,8 +8,8 @@ ARCH      ?= -gencode arch=compute_100a,code=sm_100a
 NVCCFLAGS ?= -O3 -std=c++17 -lineinfo $(ARCH) -Xcompiler -fPIC -Xptxas -v
 CSRC      := ft_gemm_b200/csrc
 LIB       := ft_gemm_b200/lib/libft_gemm_b200.so
-OBJS      := build/obj/prepare.o build/obj/prepare_mma.o build/obj/abft_gemm.o build/obj/api.o build/obj/noalloc.o build/obj/ft_attention.o build/obj/api_attention.o
-HDRS      := include/ft_gemm.h include/ft_attention.h $(CSRC)/kernels.h $(CSRC)/attention_kernels.h $(CSRC)/abft_tile_check.cuh $(CSRC)/sm100_ptx.cuh
+OBJS      := build/obj/prepare.o build/obj/prepare_mma.o build/obj/abft_gemm.o build/obj/api.o build/obj/noalloc.o build/obj/ft_attention.o build/obj/api_attention.o build/obj/gemm_softmax.o
+HDRS      := include/ft_gemm.h include/ft_attention.h include/ft_gemm_softmax.h $(CSRC)/kernels.h $(CSRC)/attention_kernels.h $(CSRC)/abft_tile_check.cuh $(CSRC)/sm100_ptx.cuh
 
 FAULT_TRIALS    ?= 100
 FAULT_MIN_VALUE ?= 1
@@ -29,7 +29,7 @@ $(LIB): $(OBJS)
 	@mkdir -p ft_gemm_b200/lib
 	$(NVCC) $(ARCH) -shared -o $@ $(OBJS)
 
-cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench build/ft_flash_attention
+cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench build/ft_flash_attention build/gemm_softmax_abft
 
 build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
@@ -38,6 +38,9 @@ build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 build/ft_flash_attention: $(CSRC)/cli/ft_flash_attention.cpp $(CSRC)/cli/cli_common.h $(LIB)
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+
+build/gemm_softmax_abft: $(CSRC)/cli/gemm_softmax_abft.cpp $(CSRC)/cli/cli_common.h $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 build/cublaslt_fp8_bench: $(CSRC)/cli/cublaslt_fp8_bench.cpp $(CSRC)/cli/cli_common.h $(LIB)

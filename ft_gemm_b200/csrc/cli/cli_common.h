@@ -53,6 +53,10 @@ struct ArgReader {
     const char* text = find(name);
     return text ? std::strtof(text, nullptr) : value;
   }
+  double get_double(const char* name, double value) const {
+    const char* text = find(name);
+    return text ? std::strtod(text, nullptr) : value;
+  }
   std::string get_string(const char* name, const char* value) const {
     const char* text = find(name);
     return text ? text : value;

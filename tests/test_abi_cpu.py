@@ -9,7 +9,7 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HEADERS = [os.path.join(ROOT, "include", name) for name in ("ft_gemm.h", "ft_attention.h")]
+HEADERS = [os.path.join(ROOT, "include", name) for name in ("ft_gemm.h", "ft_attention.h", "ft_gemm_softmax.h")]
 
 
 def declared_functions():
@@ -38,7 +38,7 @@ def test_library_exports_every_declared_symbol(lib_path):
 
 def test_header_compiles_as_c(tmp_path):
     src = tmp_path / "t.c"
-    src.write_text('#include "ft_gemm.h"\n#include "ft_attention.h"\nint main(void){ft_options o; ft_report r; ft_attn_report a; (void)o; (void)r; (void)a; return FT_OK;}\n')
+    src.write_text('#include "ft_gemm.h"\n#include "ft_attention.h"\n#include "ft_gemm_softmax.h"\nint main(void){ft_options o; ft_report r; ft_attn_report a; ft_gs_report g; (void)o; (void)r; (void)a; (void)g; return FT_OK;}\n')
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-c", str(src), "-o",
                     str(tmp_path / "t.o")], check=True)
 

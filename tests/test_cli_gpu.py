@@ -89,6 +89,32 @@ def test_attention_program():
     assert rc == 1 and "Invalid options" in err
 
 
+def test_gemm_softmax_program():
+    """Same lines and exit-code rule as the reference's prototype (src/gemm_softmax_abft.cu:465-521)."""
+    exe = os.path.join(BUILD, "gemm_softmax_abft")
+    if not os.path.exists(exe):
+        subprocess.run(["make", "-C", ROOT, "cli"], check=True, stdout=subprocess.DEVNULL)
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=300)  # defaults: 64^3, fault +1 at (32, 32)
+    assert out.returncode == 0
+    lines = out.stdout.splitlines()
+    assert lines[0] == "GEMM + Softmax cross-nonlinearity ABFT"
+    assert lines[1] == "shape: M=64 N=64 K=64, scale=1/sqrt(K), input=FP8 E4M3, output=FP32"
+    assert any(line.startswith("clean run: detected_rows=0 located_rows=0 max_projection_residual=") for line in lines)
+    assert "fault: row=32 col=32 injected_delta=+1.000000" in lines
+    assert "detection: detected_rows=1 located_rows=1 estimated_col=32 estimated_delta=+1.000000" in lines
+    assert any(line.startswith("recovery: post_detected_rows=0 max_probability_error=") for line in lines)
+    assert lines[-1] == "verification: PASS"
+    out = subprocess.run([exe, "--m", "100", "--n", "300", "--k", "72", "--fault-row", "99", "--fault-col", "0", "--fault-value", "-2.5"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "estimated_col=0 estimated_delta=-2.500000" in out.stdout
+    out = subprocess.run([exe, "--no-fault", "--m", "256", "--n", "512", "--k", "128"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "fault:" not in out.stdout
+    out = subprocess.run([exe, "--n", "1"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 1 and "Invalid shape, fault, or tolerance option." in out.stderr
+    out = subprocess.run([exe, "--fault-row", "64"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 1 and "Fault position must satisfy row < M and col < N." in out.stderr
+
+
 def test_cublaslt_program():
     rc, rep, _ = run("cublaslt_fp8_bench", "--m", 1024, "--n", 1024, "--k", 1024, "--warmup", 2, "--repeat", 5)
     assert rc == 0 and rep["verification"] == "PASS" and rep["benchmark"] == "cuBLASLt FP8 E4M3 GEMM"
