@@ -21,7 +21,7 @@ FAULT_NONE, FAULT_SCORE, FAULT_SOFTMAX, FAULT_SOFTMAX_STATE, FAULT_OUTPUT = 0, 1
 class FtAttnOptions(ctypes.Structure):
     _fields_ = [("score_abs_tol", ctypes.c_float), ("score_rel_tol", ctypes.c_float), ("pv_abs_tol", ctypes.c_float),
                 ("pv_rel_tol", ctypes.c_float), ("softmax_abs_tol", ctypes.c_float), ("softmax_rel_tol", ctypes.c_float),
-                ("protect_softmax", ctypes.c_int), ("causal", ctypes.c_int)]
+                ("protect_softmax", ctypes.c_int), ("causal", ctypes.c_int), ("exact_prepare", ctypes.c_int)]
 
 
 class FtAttnFault(ctypes.Structure):
@@ -89,7 +89,8 @@ class FtAttention:
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, score_abs_tol: float = 1.0e-2,
                  score_rel_tol: float = 2.0e-5, pv_abs_tol: float = 2.0e-3, pv_rel_tol: float = 2.0e-3,
-                 protect_softmax: bool = False, causal: bool = False, stream: Optional[torch.cuda.Stream] = None):
+                 protect_softmax: bool = False, causal: bool = False, exact_prepare: bool = False,
+                 stream: Optional[torch.cuda.Stream] = None):
         for t, name in ((q, "Q"), (k, "K"), (v, "V")):
             if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 4 or not t.is_contiguous() or t.shape != q.shape:
                 raise ValueError(f"{name} must be a contiguous [B, H, N, D] float16 CUDA tensor of the same shape as Q")
@@ -102,6 +103,7 @@ class FtAttention:
         options.pv_abs_tol, options.pv_rel_tol = pv_abs_tol, pv_rel_tol
         options.protect_softmax = int(protect_softmax)
         options.causal = int(causal)
+        options.exact_prepare = int(exact_prepare)
         self.handle = ctypes.c_void_p()
         with torch.cuda.device(q.device):
             _abi.check(self.lib.ft_attention_fp16_abft_prepare(

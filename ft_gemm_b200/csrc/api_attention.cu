@@ -1,5 +1,6 @@
 // C-ABI of the fault-tolerant attention forward: see include/ft_attention.h.
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -29,7 +30,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // [rows, cols] FP16, cols contiguous; box = 64 columns (128 bytes) x 128 rows, 128-byte swizzle.
-int make_f16_map(CUtensorMap* map, const void* base, size_t rows, size_t cols) {
+int make_f16_map(CUtensorMap* map, const void* base, size_t rows, size_t cols, unsigned box_rows = 128u) {
   static EncodeTiledFn encode = nullptr;
   if (encode == nullptr) {
     void* sym = nullptr;
@@ -42,7 +43,7 @@ int make_f16_map(CUtensorMap* map, const void* base, size_t rows, size_t cols) {
   }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {64u, 128u};
+  cuuint32_t box[2] = {64u, box_rows};
   cuuint32_t elem[2] = {1u, 1u};
   CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -65,6 +66,12 @@ struct ft_attn_handle {
   float *v_sum = nullptr, *v_weighted = nullptr;
   AttnDeviceReport* report = nullptr;
   CUtensorMap tmap_q{}, tmap_k{}, tmap_vt{};
+  // tensor-core prepare: FP16 pieces of the band sums (one allocation) and their maps
+  void* planes = nullptr;
+  void *q_ws = nullptr, *q_wm = nullptr, *k_ws = nullptr, *k_wm = nullptr;
+  CUtensorMap tmap_q_ws{}, tmap_q_wm{}, tmap_k_ws{}, tmap_k_wm{};
+  int* prepare_status = nullptr;
+  int sm_count = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   cudaStream_t last_stream = nullptr;
 };
@@ -82,12 +89,15 @@ void ft_attn_options_default(ft_attn_options* o) {
   o->softmax_rel_tol = 2.0e-5f;
   o->protect_softmax = 0;
   o->causal = 0;
+  o->exact_prepare = 0;
 }
 
 int ft_attention_fp16_abft_destroy(ft_attn_handle* h) {
   if (h == nullptr) return FT_OK;
   cudaStreamSynchronize(h->last_stream);
   cudaFree(h->vt);
+  cudaFree(h->planes);
+  cudaFree(h->prepare_status);
   cudaFree(h->cache);
   cudaFree(h->report);
   if (h->ev0) cudaEventDestroy(h->ev0);
@@ -119,6 +129,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   ATTN_CUDA(cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10) return noalloc_fail(FT_ERR_UNSUPPORTED, "this library needs an sm_100 GPU (found sm_%d%d)", prop.major, prop.minor);
   ATTN_CUDA(configure_attention());
+  if (opts.exact_prepare == 0) ATTN_CUDA(configure_prepare_mma());
 
   ft_attn_handle* h = new (std::nothrow) ft_attn_handle();
   if (h == nullptr) return noalloc_fail(FT_ERR_INVALID, "out of host memory");
@@ -130,6 +141,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   h->q = q;
   h->k = k;
   h->v = v;
+  h->sm_count = prop.multiProcessorCount;
   const size_t bh = static_cast<size_t>(batch) * heads;
   const size_t bands = bh * (seq / 64);
   const size_t band_floats = bands * head_dim;
@@ -140,6 +152,10 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&h->cache), h->cache_bytes);
   if (err == cudaSuccess) err = cudaMalloc(&h->vt, bh * seq * head_dim * 2);
   if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->report), sizeof(AttnDeviceReport));
+  if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->prepare_status), sizeof(int));
+  const int nbands = seq / 64;
+  const size_t ws_elems = bh * prepare_mma_plane_rows_f16(nbands, 0) * head_dim, wm_elems = bh * prepare_mma_plane_rows_f16(nbands, 1) * head_dim;
+  if (err == cudaSuccess && opts.exact_prepare == 0) err = cudaMalloc(&h->planes, 2 * (ws_elems + wm_elems) * 2);
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev0);
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev1);
   if (err != cudaSuccess) {
@@ -162,20 +178,46 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   int rc = make_f16_map(&h->tmap_q, q, bh * seq, head_dim);
   if (rc == FT_OK) rc = make_f16_map(&h->tmap_k, k, bh * seq, head_dim);
   if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt, h->vt, bh * head_dim, seq);
+  if (rc == FT_OK && opts.exact_prepare == 0) {
+    __half* cursor16 = static_cast<__half*>(h->planes);
+    h->q_ws = cursor16, cursor16 += ws_elems;
+    h->q_wm = cursor16, cursor16 += wm_elems;
+    h->k_ws = cursor16, cursor16 += ws_elems;
+    h->k_wm = cursor16, cursor16 += wm_elems;
+    const size_t ws_rows = bh * prepare_mma_plane_rows_f16(nbands, 0), wm_rows = bh * prepare_mma_plane_rows_f16(nbands, 1);
+    rc = make_f16_map(&h->tmap_q_ws, h->q_ws, ws_rows, head_dim, 96u);
+    if (rc == FT_OK) rc = make_f16_map(&h->tmap_q_wm, h->q_wm, wm_rows, head_dim, 64u);
+    if (rc == FT_OK) rc = make_f16_map(&h->tmap_k_ws, h->k_ws, ws_rows, head_dim, 96u);
+    if (rc == FT_OK) rc = make_f16_map(&h->tmap_k_wm, h->k_wm, wm_rows, head_dim, 64u);
+  }
   if (rc == FT_OK) {
     err = cudaMemsetAsync(h->report, 0, sizeof(AttnDeviceReport), stream);
+    if (err == cudaSuccess) err = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
     if (err == cudaSuccess) err = cudaEventRecord(h->ev0, stream);
     if (err == cudaSuccess) err = launch_attn_prepare_v(v, h->vt, h->v_sum, h->v_weighted, static_cast<int>(bh), seq, stream);
     if (err == cudaSuccess) err = launch_band_sums_f16(q, h->q_sums, h->q_mags, bh * seq, head_dim, stream);
     if (err == cudaSuccess) err = launch_band_sums_f16(k, h->k_sums, h->k_mags, bh * seq, head_dim, stream);
     // per head: S = Q K^T is the GEMM A = Q [N, D], B = K [N, D]
-    if (err == cudaSuccess) {
-      err = launch_expected_f16(q, h->k_sums, h->k_mags, h->expected_rows, h->row_scales, seq, seq / 64, head_dim, 0,
-                                static_cast<int>(bh), stream);
-    }
-    if (err == cudaSuccess) {
-      err = launch_expected_f16(k, h->q_sums, h->q_mags, h->expected_cols, h->col_scales, seq, seq / 64, head_dim, 1,
-                                static_cast<int>(bh), stream);
+    if (opts.exact_prepare != 0) {
+      if (err == cudaSuccess) {
+        err = launch_expected_f16(q, h->k_sums, h->k_mags, h->expected_rows, h->row_scales, seq, seq / 64, head_dim, 0,
+                                  static_cast<int>(bh), stream);
+      }
+      if (err == cudaSuccess) {
+        err = launch_expected_f16(k, h->q_sums, h->q_mags, h->expected_cols, h->col_scales, seq, seq / 64, head_dim, 1,
+                                  static_cast<int>(bh), stream);
+      }
+    } else {
+      if (err == cudaSuccess) err = launch_split_band_pieces_f16(h->k_sums, h->k_mags, h->k_ws, h->k_wm, nbands, head_dim, static_cast<int>(bh), stream);
+      if (err == cudaSuccess) err = launch_split_band_pieces_f16(h->q_sums, h->q_mags, h->q_ws, h->q_wm, nbands, head_dim, static_cast<int>(bh), stream);
+      if (err == cudaSuccess) {
+        err = launch_expected_mma_f16(h->tmap_q, h->tmap_k_ws, h->tmap_k_wm, h->expected_rows, h->row_scales, seq, nbands, head_dim, 0,
+                                      static_cast<int>(bh), h->sm_count, h->prepare_status, stream);
+      }
+      if (err == cudaSuccess) {
+        err = launch_expected_mma_f16(h->tmap_k, h->tmap_q_ws, h->tmap_q_wm, h->expected_cols, h->col_scales, seq, nbands, head_dim, 1,
+                                      static_cast<int>(bh), h->sm_count, h->prepare_status, stream);
+      }
     }
     if (err == cudaSuccess) err = cudaEventRecord(h->ev1, stream);
     if (err != cudaSuccess) rc = noalloc_fail(FT_ERR_CUDA, "attention prepare failed: %s", cudaGetErrorString(err));
@@ -253,6 +295,9 @@ int ft_attention_fp16_abft_report(ft_attn_handle* h, ft_attn_report* out) {
   ATTN_CUDA(cudaStreamSynchronize(h->last_stream));
   AttnDeviceReport dev;
   ATTN_CUDA(cudaMemcpy(&dev, h->report, sizeof(dev), cudaMemcpyDeviceToHost));
+  int prepare_status = 0;
+  ATTN_CUDA(cudaMemcpy(&prepare_status, h->prepare_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (prepare_status != 0) dev.status = prepare_status;  // a prepare kernel gave up: the cache is not valid
   std::memset(out, 0, sizeof(*out));
   out->status = dev.status != 0 ? FT_ERR_TIMEOUT : FT_OK;
   out->score_detected = dev.score_detected;

@@ -40,10 +40,11 @@ int main(int argc, char** argv) {
   opt.softmax_abs_tol = args.get_float("--softmax-abs-tol", opt.softmax_abs_tol);
   opt.softmax_rel_tol = args.get_float("--softmax-rel-tol", opt.softmax_rel_tol);
   opt.protect_softmax = args.has_flag("--protect-softmax") ? 1 : 0;
+  opt.exact_prepare = args.has_flag("--exact-prepare") ? 1 : 0;
   if (args.has_flag("--help")) {
     std::printf(
         "Usage: %s [--batch N --heads N --sequence N --head-dim 128 --warmup N --repeat N --causal]\n"
-        "       [--protect-softmax --softmax-abs-tol X --softmax-rel-tol X]\n"
+        "       [--protect-softmax --softmax-abs-tol X --softmax-rel-tol X --exact-prepare]\n"
         "       [--fault-stage none|score|softmax|softmax-state|output --fault-batch N --fault-head N --fault-query N --fault-index N --fault-value X]\n"
         "       [--score-abs-tol X --score-rel-tol X --pv-abs-tol X --pv-rel-tol X]\n"
         "       [--verify-abs-tol X --verify-rel-tol X --verify-rows N --dist normal|grid]\n",
@@ -88,9 +89,14 @@ int main(int argc, char** argv) {
   CLI_FT(ft_attention_generate_f16(d_v, count, 0x31415926U, dist_id, 1.0f, stream));
   CLI_CUDA(cudaStreamSynchronize(stream));
 
+  // The metadata time reported is that of a second prepare: the first one also pays for loading the prepare kernels onto
+  // the device (lazy module loading), which is not part of the operator's cost.
   ft_attn_handle* handle = nullptr;
-  CLI_FT(ft_attention_fp16_abft_prepare(&handle, d_q, d_k, d_v, batch, heads, sequence, head_dim, &opt, stream));
   ft_attn_report report;
+  CLI_FT(ft_attention_fp16_abft_prepare(&handle, d_q, d_k, d_v, batch, heads, sequence, head_dim, &opt, stream));
+  CLI_FT(ft_attention_fp16_abft_report(handle, &report));
+  CLI_FT(ft_attention_fp16_abft_destroy(handle));
+  CLI_FT(ft_attention_fp16_abft_prepare(&handle, d_q, d_k, d_v, batch, heads, sequence, head_dim, &opt, stream));
   CLI_FT(ft_attention_fp16_abft_report(handle, &report));
   float metadata_ms = report.prepare_ms;
   for (int i = 0; i < warmup; ++i) CLI_FT(ft_attention_fp16_abft_run(handle, d_out, nullptr, stream));

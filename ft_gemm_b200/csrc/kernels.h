@@ -69,6 +69,14 @@ int prepare_mma_plane_rows(int nbands);
 cudaError_t launch_split_band_digits(const float* sums, const float* mags, void* ws, void* wm, int nbands, int k, cudaStream_t stream);
 cudaError_t launch_expected_mma(const CUtensorMap& tmap_x, const CUtensorMap& tmap_ws, const CUtensorMap& tmap_wm, float* expected,
                                 float* scales, int rows, int nbands, int k, int mode, int sm_count, int* status, cudaStream_t stream);
+// FP16 form for the attention path: the band sums (times 2^-7) as 3 + 2 FP16 pieces per band; `batch` problems back to back.
+// Plane rows per problem: prepare_mma_plane_rows_f16(nbands, 0 sums | 1 magnitudes), k FP16 elements each; maps with a 96- / 64-row box.
+int prepare_mma_plane_rows_f16(int nbands, int which);
+cudaError_t launch_split_band_pieces_f16(const float* sums, const float* mags, void* ws, void* wm, int nbands, int k, int batch,
+                                         cudaStream_t stream);
+cudaError_t launch_expected_mma_f16(const CUtensorMap& tmap_x, const CUtensorMap& tmap_ws, const CUtensorMap& tmap_wm, float* expected,
+                                    float* scales, int rows, int nbands, int k, int mode, int batch, int sm_count, int* status,
+                                    cudaStream_t stream);
 
 // Fused FP8 GEMM + ABFT checker/corrector.  tmap_a / tmap_b describe A[M,K] and
 // B[N,K] with 128-byte-swizzled boxes of (128 K-bytes x 128 rows) and

@@ -4,27 +4,34 @@
 // the band sums of B, and the three other cache arrays are the same with |.| or
 // with the operands swapped (src/s4_cluster_multicast_abft_fp8_gemm.cu:237-294).
 // The reference and expected_checksums_kernel (prepare.cu) evaluate it with FP32
-// FMAs on the CUDA cores, M*N*K/16 of them.  Here it runs as FP8 tcgen05.mma:
-//   * a band sum is a sum of 64 E4M3 values, i.e. an integer multiple of 2^-9
-//     below 2^24 * 2^-9, held exactly by FP32.  split_band_digits_kernel writes it
-//     as five signed radix-32 digits d in [-15, 16] (exact E4M3 integers), one
-//     byte plane per digit: sum = 2^-9 * (d0 + 32 d1 + ... + 32^4 d4);
-//   * X (A or B itself, straight from the caller's memory by TMA, no conversion)
-//     times the digit planes gives five FP32 accumulators per checksum, each a sum
-//     of exact products; the epilogue recombines them by Horner's rule in FP32;
-//   * the scales need |X|: a helper warpgroup clears the sign bits of each staged
-//     X tile into a second shared-memory tile (same swizzled layout).
-// The result equals the reference's value up to FP32 accumulation order (the
-// digits are exact), not bit for bit; the CUDA-core kernel remains for that.
+// FMAs on the CUDA cores, M*N*K/16 of them.  Here it runs as tcgen05.mma: the FP32
+// band sums are written as a few planes in the operand's own format whose weighted
+// sum is the band sum, X (A or B itself, straight from the caller's memory by TMA,
+// no conversion) times the planes gives one FP32 accumulator per plane, each a sum
+// of exact products, and the epilogue recombines them.
+//   FP8 (the GEMM path): a sum of 64 E4M3 values is an integer multiple of 2^-9
+//     below 2^24 * 2^-9; five signed radix-32 digits d in [-15, 16] (exact E4M3
+//     integers) hold it exactly: sum = 2^-9 * (d0 + 32 d1 + ... + 32^4 d4); Horner.
+//   FP16 (the attention path): the band sum times 2^-7 (so that 64 * 65504 cannot
+//     overflow) is split into FP16 pieces hi + mid + lo (two pieces for the
+//     magnitudes); what falls below the FP16 subnormal step is dropped, an absolute
+//     error under 2^-17 per band-sum element.
+// The scales need |X|: a helper warpgroup clears the sign bits of each staged X
+// tile into a second shared-memory tile (same swizzled layout).
+// The result equals the reference's value up to FP32 accumulation order, not bit
+// for bit; the CUDA-core kernel remains for that.
 //
 // One CTA (192 threads) per SM, persistent over tiles of 128 rows of X x 32 bands:
-//   warp 0      TMA producer: X tile 128x128 B, digit planes of sums and of
-//               magnitudes 160x128 B each, 3 stages;
-//   warp 1      one thread issues, per 32 B of K, X * Ws^T -> TMEM columns [0,160)
-//               and |X| * Wm^T -> columns [160,320) (M128 N160 K32);
+//   warp 0      TMA producer: X tile 128 rows x 128 B, plane tiles of sums and of
+//               magnitudes, 3 stages;
+//   warp 1      one thread issues, per 32 B of K, X * Ws^T and |X| * Wm^T into two
+//               column ranges of one TMEM accumulator (M128, N = planes x 32);
 //   warps 2-5   |X| tiles during the main loop, then the epilogue: thread = row.
+// `batch` independent problems of the same shape (attention heads) are laid out back
+// to back in X, in the planes and in the outputs.
 // Every wait is bounded; on expiry the kernel sets *status and leaves.
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -36,18 +43,33 @@ namespace ftg {
 
 namespace {
 
-constexpr int kPmRows = 128;                    // rows of X per tile
-constexpr int kPmBands = 32;                    // bands per tile
-constexpr int kPmDigits = 5;                    // radix-32 digits per band sum
-constexpr int kPmCols = kPmBands * kPmDigits;   // 160 accumulator columns per operand
-constexpr int kPmBlockK = 128;
+constexpr int kPmRows = 128;   // rows of X per tile
+constexpr int kPmBands = 32;   // bands per tile
 constexpr int kPmStages = 3;
-constexpr int kPmXBytes = kPmRows * kPmBlockK;  // 16 KiB
-constexpr int kPmWBytes = kPmCols * kPmBlockK;  // 20 KiB
-constexpr int kPmStageBytes = 2 * kPmXBytes + 2 * kPmWBytes;
+constexpr int kPmXBytes = kPmRows * 128;  // 16 KiB: 128 rows x one 128-byte swizzle row of K
 constexpr int kPmThreads = 192;
 constexpr uint32_t kPmTmemColumns = 512;
 constexpr uint64_t kPmTimeoutNs = 2000000000ull;
+
+struct PmFp8 {
+  static constexpr int kSumPlanes = 5, kMagPlanes = 5;
+  static constexpr int kBlockKElems = 128;  // elements of K per 128-byte row
+  static constexpr uint32_t kAbsMask = 0x7f7f7f7fu;
+  static constexpr bool kHalf = false;
+};
+struct PmF16 {
+  static constexpr int kSumPlanes = 3, kMagPlanes = 2;
+  static constexpr int kBlockKElems = 64;
+  static constexpr uint32_t kAbsMask = 0x7fff7fffu;
+  static constexpr bool kHalf = true;
+};
+
+template <class Cfg>
+struct PmLayout {
+  static constexpr int kSumCols = Cfg::kSumPlanes * kPmBands, kMagCols = Cfg::kMagPlanes * kPmBands;
+  static constexpr int kWsBytes = kSumCols * 128, kWmBytes = kMagCols * 128;
+  static constexpr int kStageBytes = 2 * kPmXBytes + kWsBytes + kWmBytes;
+};
 
 struct PmTail {
   uint64_t full[kPmStages];      // TMA data landed
@@ -58,7 +80,10 @@ struct PmTail {
   int abort_flag;
 };
 
-constexpr int kPmSmemBytes = kPmStages * kPmStageBytes + static_cast<int>(sizeof(PmTail));
+template <class Cfg>
+constexpr int pm_smem_bytes() {
+  return kPmStages * PmLayout<Cfg>::kStageBytes + static_cast<int>(sizeof(PmTail));
+}
 
 __device__ __forceinline__ bool pm_any(bool flag) {  // OR over the 128 threads of warps 2-5
   uint32_t out;
@@ -76,9 +101,10 @@ __device__ __forceinline__ bool pm_any(bool flag) {  // OR over the 128 threads 
 }  // namespace
 
 // ---------------------------------------------------------------------------
-// Digit planes.  sums / mags: [nbands, k] FP32.  Plane row of (band J, digit d):
-// (J / 32) * 160 + d * 32 + J % 32, each row k bytes; bands past nbands (padding of
-// the last group of 32) are written as zeros.  grid (ceil(k / 256), padded bands).
+// Planes.  sums / mags: [bands_total, k] FP32 (bands_total = batch * nbands).  Per
+// problem the planes of band J lie at rows (J / 32) * (planes * 32) + p * 32 + J % 32
+// of that problem's block of ceil(nbands / 32) * planes * 32 rows, each row k
+// elements; bands past nbands (padding of the last group) are written as zeros.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) split_band_digits_kernel(const float* __restrict__ sums, const float* __restrict__ mags,
                                                                 uint8_t* __restrict__ ws, uint8_t* __restrict__ wm, int nbands,
@@ -86,7 +112,8 @@ __global__ void __launch_bounds__(256) split_band_digits_kernel(const float* __r
   const int band = blockIdx.y;
   const int kk = blockIdx.x * 256 + threadIdx.x;
   if (kk >= k) return;
-  const size_t row0 = static_cast<size_t>(band / kPmBands) * kPmCols + band % kPmBands;
+  constexpr int kCols = PmFp8::kSumPlanes * kPmBands;
+  const size_t row0 = static_cast<size_t>(band / kPmBands) * kCols + band % kPmBands;
   const bool valid = band < nbands;
   const float values[2] = {valid ? sums[static_cast<size_t>(band) * k + kk] : 0.0f, valid ? mags[static_cast<size_t>(band) * k + kk] : 0.0f};
   uint8_t* const planes[2] = {ws, wm};
@@ -96,7 +123,7 @@ __global__ void __launch_bounds__(256) split_band_digits_kernel(const float* __r
     uint32_t t = static_cast<uint32_t>(fabsf(v) * 512.0f);  // exact: a multiple of 2^-9 below 2^15
     const float sign = v < 0.0f ? -1.0f : 1.0f;
 #pragma unroll
-    for (int d = 0; d < kPmDigits; ++d) {
+    for (int d = 0; d < PmFp8::kSumPlanes; ++d) {
       int digit = static_cast<int>(t & 31u);
       t >>= 5;
       if (digit > 16) {  // signed digits keep every plane an exact E4M3 integer
@@ -109,12 +136,42 @@ __global__ void __launch_bounds__(256) split_band_digits_kernel(const float* __r
   }
 }
 
+// grid (ceil(k / 256), padded bands per problem, batch)
+__global__ void __launch_bounds__(256) split_band_pieces_f16_kernel(const float* __restrict__ sums, const float* __restrict__ mags,
+                                                                    __half* __restrict__ ws, __half* __restrict__ wm, int nbands, int k) {
+  const int band = blockIdx.y, problem = blockIdx.z;
+  const int kk = blockIdx.x * 256 + threadIdx.x;
+  if (kk >= k) return;
+  const int groups = (nbands + kPmBands - 1) / kPmBands;
+  const bool valid = band < nbands;
+  const size_t src = (static_cast<size_t>(problem) * nbands + band) * k + kk;
+  float s = valid ? sums[src] * 0.0078125f : 0.0f;  // 2^-7: exact, and 64 * 65504 * 2^-7 fits FP16
+  float m = valid ? mags[src] * 0.0078125f : 0.0f;
+  const size_t ws_row = (static_cast<size_t>(problem) * groups + band / kPmBands) * (PmF16::kSumPlanes * kPmBands) + band % kPmBands;
+  const size_t wm_row = (static_cast<size_t>(problem) * groups + band / kPmBands) * (PmF16::kMagPlanes * kPmBands) + band % kPmBands;
+#pragma unroll
+  for (int p = 0; p < PmF16::kSumPlanes; ++p) {
+    const __half piece = __float2half_rn(s);
+    s -= __half2float(piece);  // exact
+    ws[(ws_row + static_cast<size_t>(p) * kPmBands) * k + kk] = piece;
+  }
+#pragma unroll
+  for (int p = 0; p < PmF16::kMagPlanes; ++p) {
+    const __half piece = __float2half_rn(m);
+    m -= __half2float(piece);
+    wm[(wm_row + static_cast<size_t>(p) * kPmBands) * k + kk] = piece;
+  }
+}
+
 // mode 0 (X = A, bands of B): out index = ((row / 64) * nbands + band) * 64 + row % 64
 // mode 1 (X = B, bands of A): out index = (band * ceil(rows / 64) + row / 64) * 64 + row % 64
+// per problem; problem p adds p * ceil(rows / 64) * nbands * 64.
+template <class Cfg>
 __global__ void __launch_bounds__(kPmThreads, 1)
 expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_ws,
                               const __grid_constant__ CUtensorMap tmap_wm, float* __restrict__ expected, float* __restrict__ scales,
-                              int rows, int nbands, int k, int mode, int* __restrict__ status) {
+                              int rows, int nbands, int k, int mode, int batch, int* __restrict__ status) {
+  using L = PmLayout<Cfg>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   if ((smem_u32(smem_raw) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicExch(status, 2);
@@ -123,15 +180,16 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   uint8_t* smem_x = smem_raw;
   uint8_t* smem_ax = smem_raw + kPmStages * kPmXBytes;
   uint8_t* smem_ws = smem_raw + 2 * kPmStages * kPmXBytes;
-  uint8_t* smem_wm = smem_ws + kPmStages * kPmWBytes;
-  PmTail& tail = *reinterpret_cast<PmTail*>(smem_raw + kPmStages * kPmStageBytes);
+  uint8_t* smem_wm = smem_ws + kPmStages * L::kWsBytes;
+  PmTail& tail = *reinterpret_cast<PmTail*>(smem_raw + kPmStages * L::kStageBytes);
   volatile int* abort_flag = &tail.abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_blocks = (rows + kPmRows - 1) / kPmRows;
   const int groups = (nbands + kPmBands - 1) / kPmBands;
-  const int num_tiles = row_blocks * groups;
-  const int num_kb = (k + kPmBlockK - 1) / kPmBlockK;
+  const int tiles_per_problem = row_blocks * groups;
+  const int num_tiles = tiles_per_problem * batch;
+  const int num_kb = (k + Cfg::kBlockKElems - 1) / Cfg::kBlockKElems;
   const int worker = blockIdx.x, workers = gridDim.x;
 
   if (threadIdx.x == 0) {
@@ -164,16 +222,19 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       uint32_t phase = 0;
       bool alive = true;
       for (int t = worker; t < num_tiles && alive; t += workers) {
-        const int group = t % groups, row_block = t / groups;  // neighbouring CTAs share the X tile in L2
+        const int problem = t / tiles_per_problem, local = t % tiles_per_problem;
+        const int group = local % groups, row_block = local / groups;  // neighbouring CTAs share the X tile in L2
+        const int x_row = problem * rows + row_block * kPmRows;         // batch > 1 only with rows a multiple of 128
+        const int w_group = problem * groups + group;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, kPmTimeoutNs)) {
             alive = false;
             break;
           }
-          mbar_arrive_expect_tx(&tail.full[s], kPmXBytes + 2 * kPmWBytes);
-          tma_load_2d(smem_x + s * kPmXBytes, &tmap_x, &tail.full[s], kb * kPmBlockK, row_block * kPmRows);
-          tma_load_2d(smem_ws + s * kPmWBytes, &tmap_ws, &tail.full[s], kb * kPmBlockK, group * kPmCols);
-          tma_load_2d(smem_wm + s * kPmWBytes, &tmap_wm, &tail.full[s], kb * kPmBlockK, group * kPmCols);
+          mbar_arrive_expect_tx(&tail.full[s], kPmXBytes + L::kWsBytes + L::kWmBytes);
+          tma_load_2d(smem_x + s * kPmXBytes, &tmap_x, &tail.full[s], kb * Cfg::kBlockKElems, x_row);
+          tma_load_2d(smem_ws + s * L::kWsBytes, &tmap_ws, &tail.full[s], kb * Cfg::kBlockKElems, w_group * L::kSumCols);
+          tma_load_2d(smem_wm + s * L::kWmBytes, &tmap_wm, &tail.full[s], kb * Cfg::kBlockKElems, w_group * L::kMagCols);
           if (++s == kPmStages) {
             s = 0;
             phase ^= 1;
@@ -184,7 +245,8 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(kPmRows, kPmCols);
+      constexpr uint32_t idesc_s = Cfg::kHalf ? make_idesc_f16_f32(kPmRows, L::kSumCols) : make_idesc_e4m3_f32(kPmRows, L::kSumCols);
+      constexpr uint32_t idesc_m = Cfg::kHalf ? make_idesc_f16_f32(kPmRows, L::kMagCols) : make_idesc_e4m3_f32(kPmRows, L::kMagCols);
       int s = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
@@ -200,12 +262,18 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           tcgen05_fence_after();
           const uint64_t desc_x = make_smem_desc_sw128(smem_u32(smem_x + s * kPmXBytes));
           const uint64_t desc_ax = make_smem_desc_sw128(smem_u32(smem_ax + s * kPmXBytes));
-          const uint64_t desc_ws = make_smem_desc_sw128(smem_u32(smem_ws + s * kPmWBytes));
-          const uint64_t desc_wm = make_smem_desc_sw128(smem_u32(smem_wm + s * kPmWBytes));
+          const uint64_t desc_ws = make_smem_desc_sw128(smem_u32(smem_ws + s * L::kWsBytes));
+          const uint64_t desc_wm = make_smem_desc_sw128(smem_u32(smem_wm + s * L::kWmBytes));
 #pragma unroll
-          for (int kk = 0; kk < kPmBlockK / 32; ++kk) {  // +32 bytes of K inside the swizzle row = +2 in the address field
-            umma_f8f6f4(tmem_base, desc_x + 2 * kk, desc_ws + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-            umma_f8f6f4(tmem_base + kPmCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {  // one MMA consumes 32 bytes of K; +32 bytes inside the swizzle row = +2 in the address field
+            const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
+            if (Cfg::kHalf) {
+              umma_f16(tmem_base, desc_x + 2 * kk, desc_ws + 2 * kk, idesc_s, accumulate);
+              umma_f16(tmem_base + L::kSumCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc_m, accumulate);
+            } else {
+              umma_f8f6f4(tmem_base, desc_x + 2 * kk, desc_ws + 2 * kk, idesc_s, accumulate);
+              umma_f8f6f4(tmem_base + L::kSumCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc_m, accumulate);
+            }
           }
           umma_commit(&tail.empty[s]);
           if (++s == kPmStages) {
@@ -228,7 +296,8 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     uint32_t phase = 0, acc_phase = 0;
     bool alive = true;
     for (int t = worker; t < num_tiles && alive; t += workers) {
-      const int group = t % groups, row_block = t / groups;
+      const int problem = t / tiles_per_problem, local = t % tiles_per_problem;
+      const int group = local % groups, row_block = local / groups;
       for (int kb = 0; kb < num_kb; ++kb) {
         bool ok = true;
         if (tid == 0) ok = mbar_wait_bounded(&tail.full[s], phase, abort_flag, kPmTimeoutNs);
@@ -239,12 +308,12 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         const uint4* src = reinterpret_cast<const uint4*>(smem_x + s * kPmXBytes);
         uint4* dst = reinterpret_cast<uint4*>(smem_ax + s * kPmXBytes);
 #pragma unroll
-        for (int c = 0; c < kPmXBytes / 16 / 128; ++c) {  // the swizzle permutes whole 16-byte chunks: a bytewise AND keeps the layout
+        for (int c = 0; c < kPmXBytes / 16 / 128; ++c) {  // the swizzle permutes whole 16-byte chunks: clearing sign bits keeps the layout
           uint4 v = src[c * 128 + tid];
-          v.x &= 0x7f7f7f7fu;
-          v.y &= 0x7f7f7f7fu;
-          v.z &= 0x7f7f7f7fu;
-          v.w &= 0x7f7f7f7fu;
+          v.x &= Cfg::kAbsMask;
+          v.y &= Cfg::kAbsMask;
+          v.z &= Cfg::kAbsMask;
+          v.w &= Cfg::kAbsMask;
           dst[c * 128 + tid] = v;
         }
         fence_proxy_async_shared();
@@ -260,29 +329,32 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       if (pm_any(!ok)) break;
       acc_phase ^= 1;
       tcgen05_fence_after();
-      // Horner over the digits, most significant first: value = 2^-9 * sum_d 32^d * acc_d
+      // recombination, last plane first: FP8 digits by Horner (value = 2^-9 * sum_d 32^d * acc_d), FP16 pieces lo + mid + hi
       float e[2][2][16];  // [sums | magnitudes][band half][band]
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
+        const int planes = which == 0 ? Cfg::kSumPlanes : Cfg::kMagPlanes;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const uint32_t base = lane_addr + which * kPmCols + half * 16;
-          tmem_ld_32x32b_x16(base + (kPmDigits - 1) * kPmBands, e[which][half]);
+          const uint32_t base = lane_addr + which * L::kSumCols + half * 16;
+          tmem_ld_32x32b_x16(base + (planes - 1) * kPmBands, e[which][half]);
           tmem_wait_ld();
 #pragma unroll
-          for (int d = kPmDigits - 2; d >= 0; --d) {
+          for (int d = planes - 2; d >= 0; --d) {
             float a[16];
             tmem_ld_32x32b_x16(base + d * kPmBands, a);
             tmem_wait_ld();
 #pragma unroll
-            for (int b = 0; b < 16; ++b) e[which][half][b] = __fmaf_rn(e[which][half][b], 32.0f, a[b]);
+            for (int b = 0; b < 16; ++b) e[which][half][b] = Cfg::kHalf ? e[which][half][b] + a[b] : __fmaf_rn(e[which][half][b], 32.0f, a[b]);
           }
         }
       }
       tcgen05_fence_before();
       mbar_arrive(&tail.acc_empty);  // the accumulators are in registers: the next tile may start
+      const float unit = Cfg::kHalf ? 128.0f : 0.001953125f;  // undo the 2^-7 of the FP16 pieces / the 2^9 of the FP8 digits
       const int row = row_block * kPmRows + row_in_block;
       if (row < rows64 * 64) {  // rows of the last 64-row group past `rows` were zero-filled by the copy: their checksums are zeros
+        const size_t problem_base = static_cast<size_t>(problem) * rows64 * nbands * 64;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -290,9 +362,9 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
             const int band = group * kPmBands + half * 16 + b;
             if (band < nbands) {
               const size_t tile = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band : static_cast<size_t>(band) * rows64 + (row >> 6);
-              const size_t out = tile * 64 + (row & 63);
-              expected[out] = e[0][half][b] * 0.001953125f;
-              scales[out] = e[1][half][b] * 0.001953125f;
+              const size_t out = problem_base + tile * 64 + (row & 63);
+              expected[out] = e[0][half][b] * unit;
+              scales[out] = e[1][half][b] * unit;
             }
           }
         }
@@ -315,14 +387,16 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
 }
 
 cudaError_t configure_prepare_mma() {
-  return cudaFuncSetAttribute(expected_checksums_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPmSmemBytes);
+  cudaError_t err = cudaFuncSetAttribute(expected_checksums_mma_kernel<PmFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, pm_smem_bytes<PmFp8>());
+  if (err != cudaSuccess) return err;
+  return cudaFuncSetAttribute(expected_checksums_mma_kernel<PmF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, pm_smem_bytes<PmF16>());
 }
 
-size_t prepare_mma_plane_bytes(int nbands, int k) {
-  return static_cast<size_t>((nbands + kPmBands - 1) / kPmBands) * kPmCols * k;
+int prepare_mma_plane_rows(int nbands) { return (nbands + kPmBands - 1) / kPmBands * (PmFp8::kSumPlanes * kPmBands); }
+size_t prepare_mma_plane_bytes(int nbands, int k) { return static_cast<size_t>(prepare_mma_plane_rows(nbands)) * k; }
+int prepare_mma_plane_rows_f16(int nbands, int which) {
+  return (nbands + kPmBands - 1) / kPmBands * ((which == 0 ? PmF16::kSumPlanes : PmF16::kMagPlanes) * kPmBands);
 }
-
-int prepare_mma_plane_rows(int nbands) { return (nbands + kPmBands - 1) / kPmBands * kPmCols; }
 
 cudaError_t launch_split_band_digits(const float* sums, const float* mags, void* ws, void* wm, int nbands, int k, cudaStream_t stream) {
   const int padded = (nbands + kPmBands - 1) / kPmBands * kPmBands;
@@ -331,12 +405,37 @@ cudaError_t launch_split_band_digits(const float* sums, const float* mags, void*
   return cudaGetLastError();
 }
 
+cudaError_t launch_split_band_pieces_f16(const float* sums, const float* mags, void* ws, void* wm, int nbands, int k, int batch,
+                                         cudaStream_t stream) {
+  const int padded = (nbands + kPmBands - 1) / kPmBands * kPmBands;
+  for (int first = 0; first < batch; first += 65535) {  // grid.z limit
+    const int count = batch - first < 65535 ? batch - first : 65535;
+    const int groups = padded / kPmBands;
+    dim3 grid((k + 255) / 256, padded, count);
+    split_band_pieces_f16_kernel<<<grid, 256, 0, stream>>>(
+        sums + static_cast<size_t>(first) * nbands * k, mags + static_cast<size_t>(first) * nbands * k,
+        static_cast<__half*>(ws) + static_cast<size_t>(first) * groups * PmF16::kSumPlanes * kPmBands * k,
+        static_cast<__half*>(wm) + static_cast<size_t>(first) * groups * PmF16::kMagPlanes * kPmBands * k, nbands, k);
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t launch_expected_mma(const CUtensorMap& tmap_x, const CUtensorMap& tmap_ws, const CUtensorMap& tmap_wm, float* expected,
                                 float* scales, int rows, int nbands, int k, int mode, int sm_count, int* status, cudaStream_t stream) {
   const int tiles = ((rows + kPmRows - 1) / kPmRows) * ((nbands + kPmBands - 1) / kPmBands);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  expected_checksums_mma_kernel<<<grid, kPmThreads, kPmSmemBytes, stream>>>(tmap_x, tmap_ws, tmap_wm, expected, scales, rows, nbands, k,
-                                                                            mode, status);
+  expected_checksums_mma_kernel<PmFp8><<<grid, kPmThreads, pm_smem_bytes<PmFp8>(), stream>>>(tmap_x, tmap_ws, tmap_wm, expected, scales, rows,
+                                                                                            nbands, k, mode, 1, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_expected_mma_f16(const CUtensorMap& tmap_x, const CUtensorMap& tmap_ws, const CUtensorMap& tmap_wm, float* expected,
+                                    float* scales, int rows, int nbands, int k, int mode, int batch, int sm_count, int* status,
+                                    cudaStream_t stream) {
+  const long long tiles = static_cast<long long>((rows + kPmRows - 1) / kPmRows) * ((nbands + kPmBands - 1) / kPmBands) * batch;
+  const int grid = tiles < sm_count ? static_cast<int>(tiles) : sm_count;
+  expected_checksums_mma_kernel<PmF16><<<grid, kPmThreads, pm_smem_bytes<PmF16>(), stream>>>(tmap_x, tmap_ws, tmap_wm, expected, scales, rows,
+                                                                                            nbands, k, mode, batch, status);
   return cudaGetLastError();
 }
 

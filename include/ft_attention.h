@@ -51,6 +51,9 @@ typedef struct {
   int causal;            /* 0 (default): every key; 1: key <= query only (src/ft_flash_attention_a14.cu:130, 708, 836):
                             key tiles beyond the diagonal are skipped, the diagonal tile is verified unmasked and
                             masked afterwards; score / softmax faults must then have index <= query (a14:278) */
+  int exact_prepare;     /* 0 (default): the expected score checksums are computed on the tensor cores from FP16 pieces of the
+                            band sums (absolute error below 2^-17 per band-sum element); 1: on the CUDA cores in the
+                            reference GEMM's summation order (src/s4:264-282), about 10x slower */
 } ft_attn_options;
 
 /* Fault stages use the reference's numbering (src/ft_flash_attention_a0.cu:27-33);

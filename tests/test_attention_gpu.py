@@ -33,10 +33,12 @@ def _np(t):
     return t.cpu().numpy()
 
 
-@pytest.mark.parametrize("b,h,n", [(1, 1, 128), (1, 2, 256), (2, 3, 512)])
-def test_clean_forward(ftg, b, h, n):
+@pytest.mark.parametrize("exact_prepare", [False, True])
+@pytest.mark.parametrize("b,h,n", [(1, 1, 128), (1, 2, 256), (2, 3, 512), (1, 2, 2176)])
+def test_clean_forward(ftg, b, h, n, exact_prepare):
+    """exact_prepare=False: score checksums from FP16 pieces of the band sums on the tensor cores; True: CUDA cores."""
     q, k, v = _qkv(b, h, n, seed=n)
-    op = ftg.FtAttention(q, k, v)
+    op = ftg.FtAttention(q, k, v, exact_prepare=exact_prepare)
     out = op.new_output()
     op.run(out)
     rep = op.report()
@@ -49,10 +51,11 @@ def test_clean_forward(ftg, b, h, n):
     op.close()
 
 
-def test_score_faults_match_oracle(ftg):
+@pytest.mark.parametrize("exact_prepare", [False, True])
+def test_score_faults_match_oracle(ftg, exact_prepare):
     b, h, n = 1, 2, 512
     q, k, v = _qkv(b, h, n, seed=7)
-    op = ftg.FtAttention(q, k, v)
+    op = ftg.FtAttention(q, k, v, exact_prepare=exact_prepare)
     clean = op.new_output()
     op.run(clean)
     assert op.report().score_detected == 0
