@@ -156,6 +156,7 @@ def main():
     parser.add_argument("--impl", default="b200")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-attention", action="store_true")
     parser.add_argument("--m", type=int, default=M_PER_RANK, help="rows of A per rank (default: the 8192 of the headline shape)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -249,6 +250,38 @@ def main():
         e2e["with_prepare_value"] = 2.0 * m_rank * n * k / (time.perf_counter() - t0) / 1e12
         host.close()
 
+    # ---- the second operator of the path: fault-tolerant attention forward, B4 H32 N4096 D128, heads sharded over the ranks ----
+    attention = None
+    if not args.no_attention:
+        batch_heads, seq, dim = 4 * 32, 4096, 128
+        first, count = ftg.shard_heads(batch_heads, rank, world)
+        gen = torch.Generator(device=device).manual_seed(0x12345678 + first)
+        q, kk_, v = (torch.randn((1, count, seq, dim), generator=gen, device=device, dtype=torch.float32).to(torch.float16) for _ in range(3))
+        attn = ftg.FtAttention(q, kk_, v)
+        out = attn.new_output()
+        for _ in range(3):
+            attn.run(out)
+        barrier()
+        start.record()
+        attn_steps = 5
+        for _ in range(attn_steps):
+            attn.run(out)
+        stop.record()
+        barrier()
+        ta = torch.tensor([start.elapsed_time(stop) / attn_steps], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ta, op=dist.ReduceOp.MAX)
+        clean = attn.report()
+        attn.run(out, (ftg.FAULT_SCORE, 0, count // 2, seq // 2 + 1, seq - 96, 12.0))
+        faulty = attn.report()
+        attention = {"workload": f"ft_attention_fwd B*H={batch_heads} N={seq} D={dim} FP16, non-causal, heads sharded over {world} GPU(s)",
+                     "ms": float(ta.item()), "tflops": 4.0 * batch_heads * seq * seq * dim / (float(ta.item()) * 1e-3) / 1e12,
+                     "prepare_ms": clean.prepare_ms, "clean": [clean.score_detected, clean.pv_detected, clean.failed_rows],
+                     "score_fault": [faulty.score_detected, faulty.score_corrected, faulty.pv_detected],
+                     "score_checksum_noise_ratio": clean.max_score_noise}
+        attn.close()
+        del q, kk_, v, out
+
     # ---- same-box cuBLASLt FP8 without ABFT: the overhead reference (not part of the product path) ----
     cublaslt = None
     if rank == 0:
@@ -298,6 +331,8 @@ def main():
             line["frac_of_cublaslt_fp8"] = per_gpu / cublaslt["tflops"]
         if e2e is not None:
             line["e2e"] = e2e
+        if attention is not None:
+            line["attention"] = attention
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = {k_: v for k_, v in cpu_baseline(2048).items() if k_ not in ("seconds", "prepare_seconds")}
         print(json.dumps(line))
