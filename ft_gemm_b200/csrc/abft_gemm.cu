@@ -137,7 +137,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   // the launch covers the window [row0, row0+rows) x [col0, col0+cols) of C; checksum indices stay global
-  const int num_m = p.rows / Cfg::kTileM;
+  const int num_m = (p.rows + Cfg::kTileM - 1) / Cfg::kTileM;  // the last row block may reach past M: zero-filled like the columns
   const int num_n = (p.cols + kBlockN - 1) / kBlockN;  // the last column block may reach past N: the copies fill zeros there
   const int first_mb = p.row0 / Cfg::kTileM;
   const int first_nb = p.col0 / kBlockN;
@@ -313,11 +313,25 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int row0 = mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM;  // first row of this CTA's part
       const int grow = row0 + quarter * 32 + lane;
       const int tile_row = row0 / kGroupCols + pair;
+      // a 64-row band that starts past M holds nothing: its two warps only take part in handing the accumulator back
+      const bool band_valid = tile_row * kGroupCols < p.m;
+      const int valid_rows = min(kGroupCols, p.m - tile_row * kGroupCols);
       // 64-column groups of this tile that hold at least one column of C (src/s3:418-419)
       const int groups_here = min(kGroups, (p.n - nb * kBlockN + kGroupCols - 1) / kGroupCols);
 #pragma unroll 1
       for (int g = 0; g < groups_here; ++g) {
         const int valid_cols = min(kGroupCols, p.n - nb * kBlockN - g * kGroupCols);
+        if (!band_valid) {  // uniform over the two warps of the band
+          if (g == groups_here - 1) {
+            tcgen05_fence_before();
+            if (kPair) {
+              mbar_arrive_cluster(map_to_cta(smem_u32(&tail.tmem_empty[acc]), 0));
+            } else {
+              mbar_arrive(&tail.tmem_empty[acc]);
+            }
+          }
+          continue;
+        }
         const int tile_id = tile_row * tile_cols + nb * kGroups + g;
         const size_t cache = static_cast<size_t>(tile_id) * kGroupCols;
         const float exp_row = __ldg(p.expected_rows + cache + r_local);
@@ -347,7 +361,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
           for (int f = 0; f < FT_MAX_FAULTS; ++f) {
             if (f < p.faults.count && p.faults.tile[f] == tile_id) {
-              int fr = min(p.faults.row[f], kGroupCols - 1);
+              int fr = min(p.faults.row[f], valid_rows - 1);
               int fc = min(p.faults.col[f], valid_cols - 1);
               if (fr == r_local) {
 #pragma unroll
@@ -475,10 +489,10 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
         // C is column-major [N,M]: for a fixed column the 32 lanes write 32 consecutive floats
         float* cptr = p.c + static_cast<size_t>(nb * kBlockN + g * kGroupCols) * p.m + grow;
-        if (valid_cols == kGroupCols) {
+        if (valid_cols == kGroupCols && valid_rows == kGroupCols) {
 #pragma unroll
           for (int c = 0; c < kGroupCols; ++c) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);
-        } else {
+        } else if (r_local < valid_rows) {
 #pragma unroll
           for (int c = 0; c < kGroupCols; ++c) {
             if (c < valid_cols) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);

@@ -119,18 +119,19 @@ struct ft_gemm_handle {
 namespace {
 
 int check_shape(int m, int n, int k) {
-  // the shape rule of the reference's stages with boundary tiles (src/s3_warpspecialized_abft_fp8_gemm.cu:144-154)
-  if (m <= 0 || n <= 0 || k <= 0 || m % 128 != 0 || k % 32 != 0) {
-    return fail(FT_ERR_INVALID, "Invalid options. Require M%%128==0, K%%32==0, and positive shape (got M=%d N=%d K=%d).", m, n, k);
+  // Any positive M and N (boundary tiles in both directions, as the reference's first stage takes them,
+  // src/s0_tiled_abft_fp8_gemm.cu:143-144); K in whole 16-byte chunks, which the copy engine needs for the row pitch.
+  if (m <= 0 || n <= 0 || k <= 0 || k % 16 != 0) {
+    return fail(FT_ERR_INVALID, "Invalid options. Require K%%16==0 and positive shape (got M=%d N=%d K=%d).", m, n, k);
   }
-  long long tiles = static_cast<long long>(m / 64) * ((n + 63) / 64);
+  long long tiles = static_cast<long long>((m + 63) / 64) * ((n + 63) / 64);
   if (tiles * 64 > 0x7fffffffLL) return fail(FT_ERR_INVALID, "shape too large: %lld ABFT tiles", tiles);
   return FT_OK;
 }
 
 // The four checksum arrays from the operands and their band sums; `which` says whose band sums changed (bit 0 A, bit 1 B).
 int fill_expected(ft_gemm_handle* h, int which, cudaStream_t stream) {
-  const int band_rows_a = h->m / 64, band_rows_b = (h->n + 63) / 64;
+  const int band_rows_a = (h->m + 63) / 64, band_rows_b = (h->n + 63) / 64;
   if (h->options.exact_prepare != 0) {
     // expected_rows[(I,J),r] = sum_k A[64I+r,k] * b_sums[J,k]
     FT_CUDA(launch_expected(h->a, h->b_sums, h->b_mags, h->expected_rows, h->row_scales, h->m, band_rows_b, h->k, 0, stream));
@@ -301,14 +302,14 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
     int tiles = (m / 256) * ((n + 255) / 256);
     h->grid = 2 * std::max(1, std::min(tiles, sm_cap / 2));
   } else {
-    int tiles = (m / 128) * ((n + 255) / 256);
+    int tiles = ((m + 127) / 128) * ((n + 255) / 256);
     h->grid = std::min(tiles, sm_cap);
   }
 
-  size_t a_meta = static_cast<size_t>(m / 64) * k, b_meta = static_cast<size_t>((n + 63) / 64) * k;
-  size_t checks = static_cast<size_t>(m / 64) * ((n + 63) / 64) * 64;
+  size_t a_meta = static_cast<size_t>((m + 63) / 64) * k, b_meta = static_cast<size_t>((n + 63) / 64) * k;
+  size_t checks = static_cast<size_t>((m + 63) / 64) * ((n + 63) / 64) * 64;
   size_t floats = 2 * a_meta + 2 * b_meta + 4 * checks;
-  const size_t planes_a = opts.exact_prepare != 0 ? 0 : prepare_mma_plane_bytes(m / 64, k);
+  const size_t planes_a = opts.exact_prepare != 0 ? 0 : prepare_mma_plane_bytes((m + 63) / 64, k);
   const size_t planes_b = opts.exact_prepare != 0 ? 0 : prepare_mma_plane_bytes((n + 63) / 64, k);
   h->cache_bytes = floats * sizeof(float) + 2 * planes_a + 2 * planes_b;
   cudaError_t err = opts.exact_prepare != 0 ? cudaSuccess : configure_prepare_mma();
@@ -343,7 +344,7 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   rc = make_operand_map(&h->tmap_a, a, m, k, 128);
   if (rc == FT_OK) rc = make_operand_map(&h->tmap_b, b, n, k, h->pair ? 128 : 256);
   if (rc == FT_OK && opts.exact_prepare == 0) {
-    const int rows_a = prepare_mma_plane_rows(m / 64), rows_b = prepare_mma_plane_rows((n + 63) / 64);
+    const int rows_a = prepare_mma_plane_rows((m + 63) / 64), rows_b = prepare_mma_plane_rows((n + 63) / 64);
     rc = make_operand_map(&h->tmap_b128, b, n, k, 128);
     if (rc == FT_OK) rc = make_operand_map(&h->tmap_as, h->planes_as, rows_a, k, 160);
     if (rc == FT_OK) rc = make_operand_map(&h->tmap_am, h->planes_am, rows_a, k, 160);
@@ -407,11 +408,11 @@ int ft_gemm_fp8_abft_run_window(ft_gemm_handle* h, float* c, const ft_fault* fau
     return fail(FT_ERR_INVALID, "n_faults must be in [0, %d]", FT_MAX_FAULTS);
   }
   const int tile_m = h->pair ? 256 : 128;
-  if (row0 < 0 || rows <= 0 || col0 < 0 || cols <= 0 || row0 % tile_m != 0 || rows % tile_m != 0 || col0 % 256 != 0 ||
-      row0 + rows > h->m || col0 + cols > h->n || (cols % 256 != 0 && col0 + cols != h->n)) {
+  if (row0 < 0 || rows <= 0 || col0 < 0 || cols <= 0 || row0 % tile_m != 0 || col0 % 256 != 0 || row0 + rows > h->m ||
+      col0 + cols > h->n || (rows % tile_m != 0 && row0 + rows != h->m) || (cols % 256 != 0 && col0 + cols != h->n)) {
     return fail(FT_ERR_INVALID,
                 "window rows [%d,+%d) cols [%d,+%d) must lie inside %dx%d on multiples of %d rows and 256 columns (the last "
-                "column block may be short)",
+                "row and column blocks may be short)",
                 row0, rows, col0, cols, h->m, h->n, tile_m);
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -422,7 +423,7 @@ int ft_gemm_fp8_abft_run_window(ft_gemm_handle* h, float* c, const ft_fault* fau
   params.col0 = col0;
   params.cols = cols;
   params.faults.count = n_faults;
-  int tile_count = (h->m / 64) * ((h->n + 63) / 64);
+  int tile_count = ((h->m + 63) / 64) * ((h->n + 63) / 64);
   for (int i = 0; i < n_faults; ++i) {
     if (faults[i].tile < 0 || faults[i].tile >= tile_count || faults[i].row < 0 || faults[i].col < 0) {
       return fail(FT_ERR_INVALID, "fault %d is outside the %d ABFT tiles", i, tile_count);
@@ -434,7 +435,7 @@ int ft_gemm_fp8_abft_run_window(ft_gemm_handle* h, float* c, const ft_fault* fau
   }
   // one small memset in place of the reference's two counter memsets
   if (zero_report) FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
-  int tiles = (rows / tile_m) * ((cols + 255) / 256);
+  int tiles = ((rows + tile_m - 1) / tile_m) * ((cols + 255) / 256);
   int grid = h->pair ? std::min(h->grid, 2 * tiles) : std::min(h->grid, tiles);
   FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, grid, h->pair, stream));
   h->last_stream = stream;
@@ -510,8 +511,8 @@ int ft_gemm_fp8_abft_cache(ft_gemm_handle* h, ft_cache_view* out) {
 int ft_gemm_fp8_abft_cache_read(ft_gemm_handle* h, int which, float* host_out, size_t count) {
   if (h == nullptr || host_out == nullptr || which < 0 || which > 7) return fail(FT_ERR_INVALID, "null pointer or bad array index");
   const float* arrays[8] = {h->a_sums, h->a_mags, h->b_sums, h->b_mags, h->expected_rows, h->expected_cols, h->row_scales, h->col_scales};
-  size_t a_meta = static_cast<size_t>(h->m / 64) * h->k, b_meta = static_cast<size_t>((h->n + 63) / 64) * h->k;
-  size_t checks = static_cast<size_t>(h->m / 64) * ((h->n + 63) / 64) * 64;
+  size_t a_meta = static_cast<size_t>((h->m + 63) / 64) * h->k, b_meta = static_cast<size_t>((h->n + 63) / 64) * h->k;
+  size_t checks = static_cast<size_t>((h->m + 63) / 64) * ((h->n + 63) / 64) * 64;
   size_t sizes[8] = {a_meta, a_meta, b_meta, b_meta, checks, checks, checks, checks};
   if (count > sizes[which]) return fail(FT_ERR_INVALID, "array %d holds %zu floats, %zu requested", which, sizes[which], count);
   FT_CUDA(cudaStreamSynchronize(h->last_stream));

@@ -97,7 +97,7 @@ inline void read_common(const ArgReader& args, CommonOptions& o) {
 }
 
 inline bool common_valid(const CommonOptions& o) {
-  return o.m > 0 && o.n > 0 && o.k > 0 && o.m % 128 == 0 && o.k % 32 == 0 && o.warmup >= 0 && o.repeat > 0 &&
+  return o.m > 0 && o.n > 0 && o.k > 0 && o.k % 16 == 0 && o.warmup >= 0 && o.repeat > 0 &&
          o.verify_samples >= 0 && o.verify_abs_tolerance >= 0.0f && o.verify_rel_tolerance >= 0.0f && o.abft_abs_tolerance >= 0.0f &&
          o.abft_rel_tolerance >= 0.0f && (o.dist == "uniform" || o.dist == "normal" || o.dist == "llm");
 }
@@ -213,8 +213,8 @@ inline StageTimings time_stage(ft_gemm_handle* handle, float* d_c, const CommonO
 }
 
 inline void print_common_header(const CommonOptions& o, const char* version_key, const char* version) {
-  int tile_count = (o.m / 64) * ((o.n + 63) / 64);
-  int cta_tiles = (o.m / 128) * ((o.n + 255) / 256);
+  int tile_count = ((o.m + 63) / 64) * ((o.n + 63) / 64);
+  int cta_tiles = ((o.m + 127) / 128) * ((o.n + 255) / 256);
   std::printf("%s: %s\n", version_key, version);
   bool pair = o.m % 256 == 0;
   std::printf("instruction_tile: %s, cta_tile: 128x256x128, tma_stage_k: 128, stages: %d\n", pair ? "256x256x32 (2 CTAs)" : "128x256x32",

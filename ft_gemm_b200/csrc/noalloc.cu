@@ -43,13 +43,13 @@ extern "C" int ft_gemm_fp8_abft_expected_noalloc(const void* a, const void* b, i
       col_scales == nullptr) {
     return noalloc_fail(FT_ERR_INVALID, "null operand or output pointer");
   }
-  if (m <= 0 || n <= 0 || k <= 0 || m % 128 != 0 || k % 32 != 0) {
-    return noalloc_fail(FT_ERR_INVALID, "Invalid options. Require M%%128==0, K%%32==0, and positive shape.");
+  if (m <= 0 || n <= 0 || k <= 0 || k % 16 != 0) {
+    return noalloc_fail(FT_ERR_INVALID, "Invalid options. Require K%%16==0 and positive shape.");
   }
   if ((reinterpret_cast<uintptr_t>(a) & 15) != 0 || (reinterpret_cast<uintptr_t>(b) & 15) != 0) {
     return noalloc_fail(FT_ERR_INVALID, "A and B must be 16-byte aligned");
   }
-  const size_t a_meta = static_cast<size_t>(m / 64) * k, b_meta = static_cast<size_t>((n + 63) / 64) * k;
+  const size_t a_meta = static_cast<size_t>((m + 63) / 64) * k, b_meta = static_cast<size_t>((n + 63) / 64) * k;
   const size_t needed = 2 * (a_meta + b_meta);
   if (needed > kScratchFloats) {
     return noalloc_fail(FT_ERR_INVALID,
@@ -88,7 +88,7 @@ extern "C" int ft_gemm_fp8_abft_expected_noalloc(const void* a, const void* b, i
   err = launch_band_sums(a, a_sums, a_mags, m, k, stream);
   if (err == cudaSuccess) err = launch_band_sums(b, b_sums, b_mags, n, k, stream);
   if (err == cudaSuccess) err = launch_expected(a, b_sums, b_mags, expected_rows, row_scales, m, (n + 63) / 64, k, 0, stream);
-  if (err == cudaSuccess) err = launch_expected(b, a_sums, a_mags, expected_cols, col_scales, n, m / 64, k, 1, stream);
+  if (err == cudaSuccess) err = launch_expected(b, a_sums, a_mags, expected_cols, col_scales, n, (m + 63) / 64, k, 1, stream);
   if (err != cudaSuccess) return noalloc_fail(FT_ERR_CUDA, "launching the prepare kernels failed: %s", cudaGetErrorString(err));
   return FT_OK;
 }

@@ -170,7 +170,7 @@ __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
 template <class S>
 __global__ void __launch_bounds__(kBandThreads) quantize_band_sums_kernel(const S* __restrict__ src, uint8_t* __restrict__ dst,
                                                                           float* __restrict__ sums, float* __restrict__ mags,
-                                                                          int k, float scale) {
+                                                                          int rows, int k, float scale) {
   const int band = blockIdx.y;
   const int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 8;
   if (k0 >= k) return;
@@ -178,8 +178,9 @@ __global__ void __launch_bounds__(kBandThreads) quantize_band_sums_kernel(const 
   float s[8], m[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) s[i] = m[i] = 0.0f;
+  const int valid = min(64, rows - band * 64);
 #pragma unroll 8
-  for (int row = 0; row < 64; ++row) {
+  for (int row = 0; row < valid; ++row) {
     float v[8];
     load8(src + base + static_cast<size_t>(row) * k, v);
     uint32_t packed[2] = {0u, 0u};
@@ -412,14 +413,14 @@ cudaError_t launch_band_sums(const void* x, float* sums, float* mags, int rows, 
 
 cudaError_t launch_quantize_band_sums(const void* src, int src_dtype, void* dst, float* sums, float* mags, int rows, int k, float scale,
                                       cudaStream_t stream) {
-  dim3 grid((k / 8 + kBandThreads - 1) / kBandThreads, rows / 64);
+  dim3 grid((k / 8 + kBandThreads - 1) / kBandThreads, (rows + 63) / 64);
   uint8_t* out = static_cast<uint8_t*>(dst);
   if (src_dtype == 0) {
-    quantize_band_sums_kernel<float><<<grid, kBandThreads, 0, stream>>>(static_cast<const float*>(src), out, sums, mags, k, scale);
+    quantize_band_sums_kernel<float><<<grid, kBandThreads, 0, stream>>>(static_cast<const float*>(src), out, sums, mags, rows, k, scale);
   } else if (src_dtype == 1) {
-    quantize_band_sums_kernel<__nv_bfloat16><<<grid, kBandThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), out, sums, mags, k, scale);
+    quantize_band_sums_kernel<__nv_bfloat16><<<grid, kBandThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), out, sums, mags, rows, k, scale);
   } else {
-    quantize_band_sums_kernel<__half><<<grid, kBandThreads, 0, stream>>>(static_cast<const __half*>(src), out, sums, mags, k, scale);
+    quantize_band_sums_kernel<__half><<<grid, kBandThreads, 0, stream>>>(static_cast<const __half*>(src), out, sums, mags, rows, k, scale);
   }
   return cudaGetLastError();
 }

@@ -114,7 +114,7 @@ class AbftGemm:
 
     @property
     def tile_count(self) -> int:
-        return (self.m // _abi.FT_ABFT_TILE) * self.tile_cols
+        return -(-self.m // _abi.FT_ABFT_TILE) * self.tile_cols
 
     def new_output(self) -> torch.Tensor:
         """C as the reference lays it out: [N, M] with M contiguous (column-major C[M,N])."""
@@ -180,7 +180,7 @@ class AbftGemm:
         view = _abi.FtCacheView()
         _abi.check(self.lib.ft_gemm_fp8_abft_cache(self.handle, ctypes.byref(view)))
         tiles = self.tile_count
-        shapes = {"a_sums": (self.m // 64, self.k), "a_magnitudes": (self.m // 64, self.k),
+        shapes = {"a_sums": (-(-self.m // 64), self.k), "a_magnitudes": (-(-self.m // 64), self.k),
                   "b_sums": (-(-self.n // 64), self.k), "b_magnitudes": (-(-self.n // 64), self.k),
                   "expected_rows": (tiles, 64), "expected_cols": (tiles, 64), "row_scales": (tiles, 64),
                   "col_scales": (tiles, 64)}

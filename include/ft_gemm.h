@@ -16,12 +16,14 @@
  *   B  [N,K]  FP8 E4M3, K contiguous
  *   C  [N,M]  FP32 column-major: element (row r, column c) at C[c*M + r]
  *   ABFT tiles are 64x64; tile_id = (r/64) * ceil(N/64) + (c/64)
- *   M % 128 == 0 and K % 32 == 0, N any positive value: the shape rule of the
- *   reference's stages with boundary tiles (src/s3_warpspecialized_abft_fp8_gemm.cu:
- *   144-154, 418-419); the last tile column then holds N % 64 valid columns and its
- *   cached checksums past them are zeros (src/s4_cluster_multicast_abft_fp8_gemm.cu:
- *   284-293).  The final stage's stricter N % 256 == 0, K % 128 == 0 (src/s4:163-169)
- *   is a special case.
+ *   Any positive M and N, K % 16 == 0.  The reference's tensor-core stages take
+ *   boundary tiles in N (src/s3_warpspecialized_abft_fp8_gemm.cu:144-154, 418-419:
+ *   M % 128 == 0, K % 32 == 0), its first stage any shape
+ *   (src/s0_tiled_abft_fp8_gemm.cu:143-144); here the last tile row / column holds
+ *   M % 64 / N % 64 valid rows / columns, cached checksums past them are zeros
+ *   (src/s4_cluster_multicast_abft_fp8_gemm.cu:284-293) and fault positions are
+ *   clamped into the valid part.  The final stage's M % 128 == 0, N % 256 == 0,
+ *   K % 128 == 0 (src/s4:163-169) is a special case.
  *
  * Every function returns FT_OK (0) or a negative FT_ERR_* code; the text of the
  * last error of the calling thread is available from ft_gemm_last_error().
@@ -154,9 +156,9 @@ int ft_gemm_fp8_abft_run(ft_gemm_handle* handle, float* c, const ft_fault* fault
 /* The same launch restricted to the window rows [row0, row0+rows) x columns
  * [col0, col0+cols) of the product (the reference always launches the whole grid,
  * src/s4_cluster_multicast_abft_fp8_gemm.cu:657-672).  `c` is still the base of
- * the full [N,M] output, tile ids in faults and records stay global.  rows and
- * row0 must be multiples of 256 (128 for a handle in the one-CTA form), cols and
- * col0 of 256.  With zero_report = 0 the counters of earlier windows are kept, so
+ * the full [N,M] output, tile ids in faults and records stay global.  row0 and
+ * rows must be multiples of 256 (128 for a handle in the one-CTA form), col0 and
+ * cols of 256, except that a window may end at M or N.  With zero_report = 0 the counters of earlier windows are kept, so
  * a caller whose operands arrive in pieces can cover the product with several
  * windows and read one report. */
 int ft_gemm_fp8_abft_run_window(ft_gemm_handle* handle, float* c, const ft_fault* faults, int n_faults, int row0, int rows,

@@ -182,15 +182,16 @@ double ftq_dot_f64(const uint8_t* a, const uint8_t* b, int row, int col, int n, 
 void ftq_band_sums(const uint8_t* a, const uint8_t* b, float* a_sums, float* a_mags, float* b_sums, float* b_mags, int m, int n,
                    int k, int tile) {
   const float* dec = decode_table();
-  int tile_rows = m / tile;
+  int tile_rows = (m + tile - 1) / tile; /* the reference requires M % 128 == 0; a short last band is treated like a short last band of B */
   int tile_cols = (n + tile - 1) / tile;
 #pragma omp parallel for schedule(static)
   for (int t = 0; t < tile_rows + tile_cols; ++t) {
     if (t < tile_rows) {
       int row_begin = t * tile;
+      int valid_rows = m - row_begin < tile ? m - row_begin : tile;
       for (int kk = 0; kk < k; ++kk) {
         float sum = 0.0f, magnitude = 0.0f;
-        for (int row = 0; row < tile; ++row) {
+        for (int row = 0; row < valid_rows; ++row) {
           float value = dec[a[(size_t)(row_begin + row) * k + kk]];
           sum += value;
           magnitude += fabsf(value);
@@ -231,7 +232,7 @@ void ftq_expected_from_bands(const uint8_t* a, const uint8_t* b, const float* a_
                              const float* b_mags, float* expected_rows, float* expected_cols, float* row_scales,
                              float* col_scales, int m, int n, int k, int tile) {
   const float* dec = decode_table();
-  int tile_rows = m / tile;
+  int tile_rows = (m + tile - 1) / tile;
   int tile_cols = (n + tile - 1) / tile;
   long total = (long)tile_rows * tile_cols;
 #pragma omp parallel for schedule(static)
@@ -239,12 +240,15 @@ void ftq_expected_from_bands(const uint8_t* a, const uint8_t* b, const float* a_
     int tile_row = (int)(tile_id / tile_cols);
     int tile_col = (int)(tile_id % tile_cols);
     int valid_cols = n - tile_col * tile < tile ? n - tile_col * tile : tile;
+    int valid_rows = m - tile_row * tile < tile ? m - tile_row * tile : tile; /* rows past M: zeros, as for columns past N */
     for (int check = 0; check < 2 * tile; ++check) {
       int is_row = check < tile;
       int idx = is_row ? check : check - tile;
       float pe[32], ps[32];
       for (int l = 0; l < 32; ++l) pe[l] = ps[l] = 0.0f;
-      if (is_row) {
+      if (is_row && idx >= valid_rows) {
+        /* nothing to add */
+      } else if (is_row) {
         const uint8_t* arow = a + (size_t)(tile_row * tile + idx) * k;
         const float* bs = b_sums + (size_t)tile_col * k;
         const float* bm = b_mags + (size_t)tile_col * k;

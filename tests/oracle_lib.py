@@ -97,7 +97,7 @@ class Oracle:
 
     # -- expected checksums
     def band_sums(self, a, b, m, n, k, tile=64):
-        tr, tc = m // tile, (n + tile - 1) // tile
+        tr, tc = (m + tile - 1) // tile, (n + tile - 1) // tile
         out = [np.empty((tr, k), np.float32), np.empty((tr, k), np.float32), np.empty((tc, k), np.float32),
                np.empty((tc, k), np.float32)]
         self.lib.ftq_band_sums(_ptr(a), _ptr(b), *[_ptr(x) for x in out], m, n, k, tile)
@@ -105,7 +105,7 @@ class Oracle:
 
     def expected(self, a, b, m, n, k, tile=64, bands=None):
         bands = bands or self.band_sums(a, b, m, n, k, tile)
-        tiles = (m // tile) * ((n + tile - 1) // tile)
+        tiles = ((m + tile - 1) // tile) * ((n + tile - 1) // tile)
         out = {name: np.full((tiles, tile), np.nan, np.float32) for name in
                ("expected_rows", "expected_cols", "row_scales", "col_scales")}
         self.lib.ftq_expected_from_bands(_ptr(a), _ptr(b), _ptr(bands["a_sums"]), _ptr(bands["a_magnitudes"]),

@@ -43,7 +43,8 @@ def test_generator_bit_exact(ftg, oracle):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 384), (384, 256, 2048), (1024, 1024, 1024),
-                                   (128, 200, 96), (256, 320, 160), (384, 1000, 416), (128, 7, 32)])  # the last four: boundary tiles
+                                   (128, 200, 96), (256, 320, 160), (384, 1000, 416), (128, 7, 32),  # boundary tiles in N
+                                   (200, 136, 96), (1, 1, 16), (330, 257, 48), (65, 300, 272)])  # and in M, K % 16 == 0
 def test_expected_cache_bit_exact(ftg, oracle, m, n, k):
     """exact_prepare: CUDA-core kernels in the reference's summation order."""
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k)
@@ -58,7 +59,8 @@ def test_expected_cache_bit_exact(ftg, oracle, m, n, k):
 
 @pytest.mark.parametrize("m,n,k,dist", [(128, 256, 128, "uniform"), (256, 512, 384, "normal"), (384, 2304, 2048, "normal"),
                                         (1024, 1024, 1024, "uniform"), (128, 200, 96, "uniform"), (384, 1000, 416, "normal"),
-                                        (128, 7, 32, "uniform"), (4352, 64, 160, "normal")])
+                                        (128, 7, 32, "uniform"), (4352, 64, 160, "normal"), (200, 136, 96, "uniform"), (1, 1, 16, "uniform"),
+                                        (330, 257, 48, "normal"), (2500, 300, 272, "uniform")])
 def test_expected_cache_tensor_core_prepare(ftg, oracle, m, n, k, dist):
     """Default prepare: band sums as exact E4M3 digit planes times the operand on the tensor cores.  The band sums stay
     bit-exact; the checksums equal the reference's up to FP32 accumulation order (bound: 1e-6 of the magnitude sum)."""
@@ -85,7 +87,10 @@ def test_expected_cache_tensor_core_prepare(ftg, oracle, m, n, k, dist):
                                         (1024, 1024, 1024, "normal"), (2048, 256, 4096, "uniform"),
                                         # boundary tiles in N, K not a multiple of the 128-wide K block (src/s3:144-154)
                                         (128, 200, 96, "uniform"), (256, 1000, 416, "normal"), (512, 64, 32, "uniform"),
-                                        (384, 320, 2080, "uniform"), (256, 129, 224, "normal")])
+                                        (384, 320, 2080, "uniform"), (256, 129, 224, "normal"),
+                                        # boundary tiles in M as well, K a multiple of 16 only (src/s0:143-144 takes any shape)
+                                        (200, 136, 96, "uniform"), (1, 1, 16, "uniform"), (330, 257, 48, "normal"),
+                                        (1000, 1000, 1008, "normal"), (257, 64, 16, "uniform")])
 def test_gemm_and_clean_check(ftg, oracle, m, n, k, dist):
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k, dist)
     op = ftg.AbftGemm(a, b)
@@ -269,7 +274,7 @@ def test_host_buffer_entry_point(ftg, oracle):
 
 def test_fault_decisions_in_boundary_tiles(ftg, oracle):
     """N = 200: the last tile column holds 8 valid columns; a fault column past them is clamped (campaign:464-466)."""
-    for m, n, k in [(256, 200, 160), (128, 449, 96)]:
+    for m, n, k in [(256, 200, 160), (128, 449, 96), (200, 200, 80)]:
         a, b, ah, bh = _inputs(ftg, oracle, m, n, k)
         op = ftg.AbftGemm(a, b)
         c = op.new_output()
@@ -280,17 +285,22 @@ def test_fault_decisions_in_boundary_tiles(ftg, oracle):
         tile_cols = -(-n // 64)
         valid_last = n - (tile_cols - 1) * 64
         last = tile_cols - 1
-        for fault in [(last, 5, 0, 7.0), (tile_cols + last, 40, valid_last - 1, -9.0), (last, 63, 63, 12.0), (1, 2, 3, 4.0)]:
+        tile_rows = -(-m // 64)
+        valid_rows_last = m - (tile_rows - 1) * 64
+        bottom = (tile_rows - 1) * tile_cols  # first tile of the last tile row
+        for fault in [(last, 5, 0, 7.0), (tile_cols + last, 40, valid_last - 1, -9.0), (last, 63, 63, 12.0), (1, 2, 3, 4.0),
+                      (bottom, 63, 1, 6.0), (bottom + last, 0, 63, -8.0)]:
             rep = _compare_decisions(ftg, oracle, op, c_clean, cache, m, n, [fault])
             assert (rep.bad_tiles, rep.corrected_tiles) == (1, 1)
             want_col = min(fault[2], valid_last - 1) if fault[0] % tile_cols == last else fault[2]
-            assert (rep.records[0].bad_row, rep.records[0].bad_col) == (fault[1], want_col)
+            want_row = min(fault[1], valid_rows_last - 1) if fault[0] // tile_cols == tile_rows - 1 else fault[1]
+            assert (rep.records[0].bad_row, rep.records[0].bad_col) == (want_row, want_col)
         rep = _compare_decisions(ftg, oracle, op, c_clean, cache, m, n, [(last, 1, 0, 5.0), (last, 9, 0, 5.0)])
         assert (rep.bad_tiles, rep.corrected_tiles, rep.multi_fault_tiles) == (1, 0, 1)
         # the window form accepts a short last column block
         parts = torch.full_like(c, float("nan"))
         tile_m = 256 if m % 256 == 0 else 128
-        op.run_window(parts, 0, tile_m, 0, n)
+        op.run_window(parts, 0, min(m, tile_m), 0, n)
         if m > tile_m:
             op.run_window(parts, tile_m, m - tile_m, 0, n, zero_report=False)
         assert torch.equal(parts, c)
@@ -387,7 +397,7 @@ def test_invalid_arguments_are_rejected(ftg):
     a = torch.zeros((128, 128), dtype=torch.uint8, device="cuda")
     b = torch.zeros((256, 128), dtype=torch.uint8, device="cuda")
     with pytest.raises(ftg.FtGemmError) as e:
-        ftg.AbftGemm(a[:64].contiguous(), b)  # M % 128 != 0, the reference's own shape rule
+        ftg.AbftGemm(a[:, :120].contiguous(), b[:, :120].contiguous())  # K must come in whole 16-byte chunks
     assert e.value.code == ftg.FT_ERR_INVALID
     op = ftg.AbftGemm(a, b)
     c = op.new_output()

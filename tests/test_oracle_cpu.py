@@ -237,3 +237,22 @@ def test_quantize_matches_the_scalar_codec(oracle):
     # ties go to the even mantissa: 17 -> 16, 19 -> 20 (step 2 between 16 and 32), and the format saturates at 448
     np.testing.assert_array_equal(oracle.decode(oracle.quantize(np.array([17.0, 18.0, 19.0, 1e9, -1e9], np.float32))),
                                   np.array([16.0, 18.0, 20.0, 448.0, -448.0], np.float32))
+
+
+def test_ragged_m_is_the_transpose_of_ragged_n(oracle):
+    """The reference's cache kernels take a short last band of B (src/s4:203, 240, 284-293) but require M % 128 == 0.
+    The oracle treats a short last band of A the same way; this ties the extension to the pinned path: with A and B
+    swapped the row arrays of one problem are the column arrays of the other."""
+    m, n, k = 200, 136, 96
+    a, b = oracle.generate_uniform(m * k, 3), oracle.generate_uniform(n * k, 4)
+    ab = oracle.expected(a, b, m, n, k)
+    ba = oracle.expected(b, a, n, m, k)
+    tr, tc = -(-m // 64), -(-n // 64)
+    for rows, cols in (("expected_rows", "expected_cols"), ("row_scales", "col_scales")):
+        x = ab[rows].reshape(tr, tc, 64)
+        y = ba[cols].reshape(tc, tr, 64).transpose(1, 0, 2)
+        np.testing.assert_array_equal(x.view(np.uint32), y.view(np.uint32), err_msg=rows)
+        x = ab[cols].reshape(tr, tc, 64)
+        y = ba[rows].reshape(tc, tr, 64).transpose(1, 0, 2)
+        np.testing.assert_array_equal(x.view(np.uint32), y.view(np.uint32), err_msg=cols)
+    assert (ab["expected_rows"].reshape(tr, tc, 64)[-1, :, m - 64 * (tr - 1):] == 0).all()  # rows past M: zeros

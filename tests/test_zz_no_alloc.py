@@ -49,5 +49,5 @@ def test_noalloc_prepare_matches_prepare_twice_in_a_row():
     fake = ctypes.c_void_p(0x10000)
     rc = lib.ft_gemm_fp8_abft_expected_noalloc(fake, fake, 8192 + 128, 8192, 8192, fake, fake, fake, fake, None)
     assert rc == ftg.FT_ERR_INVALID and b"built-in array" in lib.ft_gemm_last_error()
-    rc = lib.ft_gemm_fp8_abft_expected_noalloc(fake, fake, 100, 256, 128, fake, fake, fake, fake, None)
+    rc = lib.ft_gemm_fp8_abft_expected_noalloc(fake, fake, 100, 256, 120, fake, fake, fake, fake, None)
     assert rc == ftg.FT_ERR_INVALID
