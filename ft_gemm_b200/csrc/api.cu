@@ -106,6 +106,11 @@ struct ft_gemm_handle {
   cudaEvent_t ev0 = nullptr, ev_mid = nullptr, ev1 = nullptr;
   bool prepare_timed = false;
   cudaStream_t last_stream = nullptr;
+  // K not a multiple of 16 (or operands not 16-byte aligned): zero-padded copies with K rounded up; `k` is then the
+  // padded K, user_k the caller's
+  const void *user_a = nullptr, *user_b = nullptr;
+  void *pad_a = nullptr, *pad_b = nullptr;
+  int user_k = 0;
   // device buffers owned by the host-buffer entry point
   void* own_a = nullptr;
   void* own_b = nullptr;
@@ -119,10 +124,11 @@ struct ft_gemm_handle {
 namespace {
 
 int check_shape(int m, int n, int k) {
-  // Any positive M and N (boundary tiles in both directions, as the reference's first stage takes them,
-  // src/s0_tiled_abft_fp8_gemm.cu:143-144); K in whole 16-byte chunks, which the copy engine needs for the row pitch.
-  if (m <= 0 || n <= 0 || k <= 0 || k % 16 != 0) {
-    return fail(FT_ERR_INVALID, "Invalid options. Require K%%16==0 and positive shape (got M=%d N=%d K=%d).", m, n, k);
+  // Any positive shape (boundary tiles in both directions, as the reference's first stage takes them,
+  // src/s0_tiled_abft_fp8_gemm.cu:143-144).  The copy engine needs a row pitch of whole 16-byte chunks: for other K the
+  // handle works on zero-padded copies of the operands.
+  if (m <= 0 || n <= 0 || k <= 0) {
+    return fail(FT_ERR_INVALID, "Invalid options. Require a positive shape (got M=%d N=%d K=%d).", m, n, k);
   }
   long long tiles = static_cast<long long>((m + 63) / 64) * ((n + 63) / 64);
   if (tiles * 64 > 0x7fffffffLL) return fail(FT_ERR_INVALID, "shape too large: %lld ABFT tiles", tiles);
@@ -145,6 +151,21 @@ int fill_expected(ft_gemm_handle* h, int which, cudaStream_t stream) {
                               h->sm_count, h->prepare_status, stream));
   FT_CUDA(launch_expected_mma(h->tmap_b128, h->tmap_as, h->tmap_am, h->expected_cols, h->col_scales, h->n, band_rows_a, h->k, 1,
                               h->sm_count, h->prepare_status, stream));
+  return FT_OK;
+}
+
+// Handles with padded operand copies: refreshes the copies of the operands that changed (bit 0 A, bit 1 B).  The padding
+// columns are zeros (E4M3 code 0), which add nothing to any product or sum.
+int copy_padded(ft_gemm_handle* h, int which, cudaStream_t stream) {
+  if (h->pad_a == nullptr) return FT_OK;
+  if (which & 1) {
+    FT_CUDA(cudaMemsetAsync(h->pad_a, 0, static_cast<size_t>(h->m) * h->k, stream));
+    FT_CUDA(cudaMemcpy2DAsync(h->pad_a, h->k, h->user_a, h->user_k, h->user_k, h->m, cudaMemcpyDeviceToDevice, stream));
+  }
+  if (which & 2) {
+    FT_CUDA(cudaMemsetAsync(h->pad_b, 0, static_cast<size_t>(h->n) * h->k, stream));
+    FT_CUDA(cudaMemcpy2DAsync(h->pad_b, h->k, h->user_b, h->user_k, h->user_k, h->n, cudaMemcpyDeviceToDevice, stream));
+  }
   return FT_OK;
 }
 
@@ -181,6 +202,7 @@ void fill_params(const ft_gemm_handle* h, float* c, GemmParams* params) {
 
 // Largest chunk count g <= kMaxPipeChunks for which M/g and N/g are whole tiles; 1 = no pipelining.
 int pipe_chunks(const ft_gemm_handle* h) {
+  if (h->pad_a != nullptr) return 1;  // padded operand copies are refreshed as a whole
   const int tile_m = h->pair ? 256 : 128;
   for (int g = kMaxPipeChunks; g > 1; g >>= 1) {
     if (h->m % (g * tile_m) == 0 && h->n % (g * 256) == 0) return g;
@@ -269,9 +291,9 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   *handle = nullptr;
   int rc = check_shape(m, n, k);
   if (rc != FT_OK) return rc;
-  if ((reinterpret_cast<uintptr_t>(a) & 15) != 0 || (reinterpret_cast<uintptr_t>(b) & 15) != 0) {
-    return fail(FT_ERR_INVALID, "A and B must be 16-byte aligned");
-  }
+  const bool padded = k % 16 != 0 || (reinterpret_cast<uintptr_t>(a) & 15) != 0 || (reinterpret_cast<uintptr_t>(b) & 15) != 0;
+  const int user_k = k;
+  k = (k + 15) / 16 * 16;
   ft_options opts;
   ft_options_default(&opts);
   if (options != nullptr) opts = *options;
@@ -295,6 +317,21 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   h->options = opts;
   h->a = a;
   h->b = b;
+  h->user_a = a;
+  h->user_b = b;
+  h->user_k = user_k;
+  if (padded) {
+    cudaError_t perr = cudaMalloc(&h->pad_a, static_cast<size_t>(m) * k);
+    if (perr == cudaSuccess) perr = cudaMalloc(&h->pad_b, static_cast<size_t>(n) * k);
+    if (perr != cudaSuccess) {
+      ft_gemm_fp8_abft_destroy(h);
+      return fail(FT_ERR_CUDA, "allocating the padded operand copies failed: %s", cudaGetErrorString(perr));
+    }
+    h->a = h->pad_a;
+    h->b = h->pad_b;
+    a = h->pad_a;
+    b = h->pad_b;
+  }
   h->sm_count = prop.multiProcessorCount;
   h->pair = (m % 256 == 0) && opts.single_cta == 0;
   int sm_cap = opts.sm_limit > 0 ? std::min(opts.sm_limit, h->sm_count) : h->sm_count;
@@ -357,6 +394,7 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
     if (merr == cudaSuccess) merr = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
     if (merr != cudaSuccess) rc = fail(FT_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(merr));
   }
+  if (rc == FT_OK) rc = copy_padded(h, 3, stream);
   if (rc == FT_OK) rc = fill_cache(h, 3, stream);
   if (rc != FT_OK) {
     ft_gemm_fp8_abft_destroy(h);
@@ -368,6 +406,8 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
 
 int ft_gemm_fp8_abft_refresh(ft_gemm_handle* h, int which, void* stream_ptr) {
   if (h == nullptr || (which & 3) == 0) return fail(FT_ERR_INVALID, "null handle or empty refresh mask");
+  int rc = copy_padded(h, which & 3, static_cast<cudaStream_t>(stream_ptr));
+  if (rc != FT_OK) return rc;
   return fill_cache(h, which & 3, static_cast<cudaStream_t>(stream_ptr));
 }
 
@@ -376,6 +416,7 @@ int ft_gemm_fp8_abft_quantize_a(ft_gemm_handle* h, const void* src, int src_dtyp
   if (src_dtype < FT_SRC_F32 || src_dtype > FT_SRC_F16) return fail(FT_ERR_INVALID, "src_dtype must be 0 (FP32), 1 (BF16) or 2 (FP16)");
   if ((reinterpret_cast<uintptr_t>(src) & 15) != 0) return fail(FT_ERR_INVALID, "the source must be 16-byte aligned");
   if (!(scale == scale) || scale == 0.0f) return fail(FT_ERR_INVALID, "scale must be a non-zero number");
+  if (h->pad_a != nullptr) return fail(FT_ERR_UNSUPPORTED, "the fused producer of A needs K %% 16 == 0 and a 16-byte aligned A");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   FT_CUDA(cudaEventRecord(h->ev0, stream));
   // A and its band sums in one pass over the source; the caller's A buffer is written here
@@ -529,6 +570,8 @@ int ft_gemm_fp8_abft_destroy(ft_gemm_handle* h) {
   if (h->ev0) cudaEventDestroy(h->ev0);
   if (h->ev_mid) cudaEventDestroy(h->ev_mid);
   if (h->ev1) cudaEventDestroy(h->ev1);
+  cudaFree(h->pad_a);
+  cudaFree(h->pad_b);
   cudaFree(h->own_a);
   cudaFree(h->own_b);
   cudaFree(h->own_c);
@@ -559,7 +602,7 @@ int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void
   ft_gemm_handle* h = reuse != nullptr ? *reuse : nullptr;
   size_t a_bytes = static_cast<size_t>(m) * k, b_bytes = static_cast<size_t>(n) * k, c_bytes = static_cast<size_t>(m) * n * 4;
   bool fresh = h == nullptr;
-  if (!fresh && (h->m != m || h->n != n || h->k != k || h->own_a == nullptr)) {
+  if (!fresh && (h->m != m || h->n != n || h->user_k != k || h->own_a == nullptr)) {
     return fail(FT_ERR_INVALID, "the handle passed for reuse was not created by this entry point with the same shape");
   }
   void *da = nullptr, *db = nullptr;
@@ -610,6 +653,8 @@ int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void
       }
     } else if (rc == FT_OK && prepare) {
       rc = ft_gemm_fp8_abft_refresh(h, 3, stream);
+    } else if (rc == FT_OK) {
+      rc = copy_padded(h, 3, stream);
     }
     if (rc == FT_OK) rc = ft_gemm_fp8_abft_run(h, dc, faults, n_faults, stream);
     if (rc == FT_OK) {

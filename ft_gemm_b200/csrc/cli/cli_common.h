@@ -97,7 +97,7 @@ inline void read_common(const ArgReader& args, CommonOptions& o) {
 }
 
 inline bool common_valid(const CommonOptions& o) {
-  return o.m > 0 && o.n > 0 && o.k > 0 && o.k % 16 == 0 && o.warmup >= 0 && o.repeat > 0 &&
+  return o.m > 0 && o.n > 0 && o.k > 0 && o.warmup >= 0 && o.repeat > 0 &&
          o.verify_samples >= 0 && o.verify_abs_tolerance >= 0.0f && o.verify_rel_tolerance >= 0.0f && o.abft_abs_tolerance >= 0.0f &&
          o.abft_rel_tolerance >= 0.0f && (o.dist == "uniform" || o.dist == "normal" || o.dist == "llm");
 }

@@ -33,12 +33,12 @@ int main(int argc, char** argv) {
         "       [--fault-min-value X --fault-max-value X]\n"
         "       [--fault-trials N --fault-seed N --double-trials N]\n"
         "       [--dist uniform|normal|llm]\n"
-        "Constraints: K %% 16 == 0; M and N may be any positive values (boundary tiles).\n",
+        "Constraints: any positive M, N and K (boundary tiles; K is padded to a multiple of 16 internally).\n",
         argv[0]);
     return EXIT_SUCCESS;
   }
   if (!common_valid(o) || fault_min_value <= 0.0f || fault_max_value < fault_min_value || fault_trials <= 0 || double_trials < 0) {
-    std::fprintf(stderr, "Invalid options. Require K%%16==0 and positive shape.\n");
+    std::fprintf(stderr, "Invalid options. Require a positive shape.\n");
     return EXIT_FAILURE;
   }
   CLI_CUDA(cudaSetDevice(0));

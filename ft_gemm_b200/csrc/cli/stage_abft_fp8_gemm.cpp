@@ -18,12 +18,12 @@ int main(int argc, char** argv) {
         "       [--verify-samples N --verify-abs-tol X --verify-rel-tol X]\n"
         "       [--abs-tol X --rel-tol X --fault-value X --inject-fault]\n"
         "       [--dist uniform|normal|llm]\n"
-        "Constraints: K %% 16 == 0; M and N may be any positive values (boundary tiles).\n",
+        "Constraints: any positive M, N and K (boundary tiles; K is padded to a multiple of 16 internally).\n",
         argv[0]);
     return EXIT_SUCCESS;
   }
   if (!common_valid(o) || fault_value <= 0.0f) {
-    std::fprintf(stderr, "Invalid options. Require K%%16==0 and positive shape.\n");
+    std::fprintf(stderr, "Invalid options. Require a positive shape.\n");
     return EXIT_FAILURE;
   }
   CLI_CUDA(cudaSetDevice(0));

@@ -180,8 +180,9 @@ class AbftGemm:
         view = _abi.FtCacheView()
         _abi.check(self.lib.ft_gemm_fp8_abft_cache(self.handle, ctypes.byref(view)))
         tiles = self.tile_count
-        shapes = {"a_sums": (-(-self.m // 64), self.k), "a_magnitudes": (-(-self.m // 64), self.k),
-                  "b_sums": (-(-self.n // 64), self.k), "b_magnitudes": (-(-self.n // 64), self.k),
+        kp = -(-self.k // 16) * 16  # the band-sum arrays of a handle with padded operand copies have ceil16(K) columns
+        shapes = {"a_sums": (-(-self.m // 64), kp), "a_magnitudes": (-(-self.m // 64), kp),
+                  "b_sums": (-(-self.n // 64), kp), "b_magnitudes": (-(-self.n // 64), kp),
                   "expected_rows": (tiles, 64), "expected_cols": (tiles, 64), "row_scales": (tiles, 64),
                   "col_scales": (tiles, 64)}
         out = {}
@@ -190,7 +191,7 @@ class AbftGemm:
             with torch.cuda.device(self.a.device):
                 _abi.check(self.lib.ft_gemm_fp8_abft_cache_read(self.handle, which, ctypes.c_void_p(host.data_ptr()),
                                                                 host.numel()))
-            out[name] = host
+            out[name] = host[:, :self.k].contiguous() if which < 4 else host
         return out
 
     def close(self):

@@ -16,7 +16,10 @@
  *   B  [N,K]  FP8 E4M3, K contiguous
  *   C  [N,M]  FP32 column-major: element (row r, column c) at C[c*M + r]
  *   ABFT tiles are 64x64; tile_id = (r/64) * ceil(N/64) + (c/64)
- *   Any positive M and N, K % 16 == 0.  The reference's tensor-core stages take
+ *   Any positive M, N and K (for K % 16 != 0, or operands that are not 16-byte
+ *   aligned, the handle works on zero-padded copies of A and B that _prepare and
+ *   _refresh fill; the band-sum arrays then have ceil16(K) columns).  The
+ *   reference's tensor-core stages take
  *   boundary tiles in N (src/s3_warpspecialized_abft_fp8_gemm.cu:144-154, 418-419:
  *   M % 128 == 0, K % 32 == 0), its first stage any shape
  *   (src/s0_tiled_abft_fp8_gemm.cu:143-144); here the last tile row / column holds

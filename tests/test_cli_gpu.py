@@ -46,14 +46,14 @@ def test_stage_program_clean_and_injected():
 
 
 def test_stage_program_rejects_bad_shapes():
-    for args in (["--m", 0], ["--n", 0], ["--k", 40], ["--repeat", 0]):
+    for args in (["--m", 0], ["--n", 0], ["--k", -8], ["--repeat", 0]):
         rc, rep, err = run("stage_abft_fp8_gemm", *args)
         assert rc == 1 and not rep and "Invalid options" in err
-    # boundary tiles: any M and N, K a multiple of 16
+    # boundary tiles: any M, N and K
     rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 256, "--n", 200, "--k", 96, "--repeat", 2, "--inject-fault", "--fault-value", 3.0)
     assert rc == 0 and (rep["bad_tiles"], rep["corrected_tiles"], rep["verification"]) == ("1", "1", "PASS")
     assert rep["shape"].startswith("M=256 N=200 K=96, abft_tiles=16")
-    rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 100, "--n", 300, "--k", 48, "--repeat", 2, "--inject-fault", "--fault-value", 3.0)
+    rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 100, "--n", 300, "--k", 50, "--repeat", 2, "--inject-fault", "--fault-value", 3.0)
     assert rc == 0 and (rep["bad_tiles"], rep["corrected_tiles"], rep["verification"]) == ("1", "1", "PASS")
 
 

@@ -44,7 +44,8 @@ def test_generator_bit_exact(ftg, oracle):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 384), (384, 256, 2048), (1024, 1024, 1024),
                                    (128, 200, 96), (256, 320, 160), (384, 1000, 416), (128, 7, 32),  # boundary tiles in N
-                                   (200, 136, 96), (1, 1, 16), (330, 257, 48), (65, 300, 272)])  # and in M, K % 16 == 0
+                                   (200, 136, 96), (1, 1, 16), (330, 257, 48), (65, 300, 272),  # and in M
+                                   (128, 256, 100), (77, 50, 7), (300, 300, 1)])  # any K: zero-padded copies inside the handle
 def test_expected_cache_bit_exact(ftg, oracle, m, n, k):
     """exact_prepare: CUDA-core kernels in the reference's summation order."""
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k)
@@ -90,7 +91,8 @@ def test_expected_cache_tensor_core_prepare(ftg, oracle, m, n, k, dist):
                                         (384, 320, 2080, "uniform"), (256, 129, 224, "normal"),
                                         # boundary tiles in M as well, K a multiple of 16 only (src/s0:143-144 takes any shape)
                                         (200, 136, 96, "uniform"), (1, 1, 16, "uniform"), (330, 257, 48, "normal"),
-                                        (1000, 1000, 1008, "normal"), (257, 64, 16, "uniform")])
+                                        (1000, 1000, 1008, "normal"), (257, 64, 16, "uniform"),
+                                        (128, 256, 100, "uniform"), (77, 50, 7, "normal"), (300, 300, 1, "uniform")])  # any K
 def test_gemm_and_clean_check(ftg, oracle, m, n, k, dist):
     a, b, ah, bh = _inputs(ftg, oracle, m, n, k, dist)
     op = ftg.AbftGemm(a, b)
@@ -393,11 +395,44 @@ def test_quantize_a_fused_with_band_sums(ftg, oracle):
         op.close()
 
 
+def test_padded_k_refresh_and_host_call(ftg, oracle):
+    """K = 100: the handle works on zero-padded copies; refresh must re-copy the operand that changed."""
+    m, n, k = 128, 192, 100
+    a, b, ah, bh = _inputs(ftg, oracle, m, n, k)
+    op = ftg.AbftGemm(a, b, exact_prepare=True)
+    c = op.new_output()
+    a2 = ftg.generate_fp8((m, k), 777)
+    a.copy_(a2)
+    op.refresh(a_changed=True, b_changed=False)
+    a2h = a2.cpu().numpy().ravel()
+    want = oracle.expected(a2h, bh, m, n, k)
+    got = op.cache()
+    for name in want:
+        np.testing.assert_array_equal(got[name].numpy().view(np.uint32), want[name].view(np.uint32), err_msg=name)
+    op.run(c, [(1, 2, 3, 9.0)])
+    rep = op.report()
+    assert (rep.bad_tiles, rep.corrected_tiles) == (1, 1)
+    np.testing.assert_allclose(c.cpu().numpy(), oracle.gemm_f32(a2h, bh, m, n, k), atol=1e-3)
+    with pytest.raises(ftg.FtGemmError):
+        op.quantize_a(torch.zeros((m, k), device="cuda"))  # the fused producer needs K % 16 == 0
+    op.close()
+    a_pin, b_pin = a2.cpu().pin_memory(), b.cpu().pin_memory()
+    c_pin = torch.empty((n, m), dtype=torch.float32).pin_memory()
+    host = ftg.HostAbftGemm(m, n, k)
+    for _ in range(2):  # the second call reuses the handle
+        assert host(a_pin, b_pin, c_pin).bad_tiles == 0
+        np.testing.assert_allclose(c_pin.numpy(), oracle.gemm_f32(a2h, bh, m, n, k), atol=1e-5 * k)
+    a_pin.copy_(ftg.generate_fp8((m, k), 778).cpu())
+    assert host(a_pin, b_pin, c_pin, prepare=True).bad_tiles == 0  # new A: prepare again, or the stale cache fires
+    np.testing.assert_allclose(c_pin.numpy(), oracle.gemm_f32(a_pin.numpy().ravel(), bh, m, n, k), atol=1e-5 * k)
+    host.close()
+
+
 def test_invalid_arguments_are_rejected(ftg):
     a = torch.zeros((128, 128), dtype=torch.uint8, device="cuda")
     b = torch.zeros((256, 128), dtype=torch.uint8, device="cuda")
     with pytest.raises(ftg.FtGemmError) as e:
-        ftg.AbftGemm(a[:, :120].contiguous(), b[:, :120].contiguous())  # K must come in whole 16-byte chunks
+        ftg.AbftGemm(a[:0].contiguous(), b)  # an empty operand: the shape must be positive
     assert e.value.code == ftg.FT_ERR_INVALID
     op = ftg.AbftGemm(a, b)
     c = op.new_output()
