@@ -6,10 +6,10 @@
 //   row checksum    serial sum of the thread's 64 values (the reference's order)
 //   column checksum transpose-reduce butterfly over the warp's 32 rows, combined
 //                   with the partner warp (the other 32 rows of the tile) through
-//                   shared memory and one 64-thread named barrier
+//                   shared memory; the caller synchronises the two warps
 //   decision        bad <=> |expected - actual| > abs + rel * max(1, scale)
 //   correction      iff exactly one bad row and one bad column:
-//                   v[row][col] += 0.5 * (row_delta + col_delta), in registers
+//                   v[row][col] += 0.5 * (row_delta + col_delta), applied by the caller
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -40,15 +40,12 @@ struct TileDecision {
   bool corrected;
 };
 
-// Called by the two warps (64 threads) that own the tile's rows; `half` says
-// which 32 rows this warp holds, `barrier_id` is the named barrier those two warps
-// (and nobody else) synchronise on.
-// `sc` must not be reused by the same warps before they have passed the barrier of
-// their NEXT call (callers alternate between two scratch areas).
-__device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane, int half, int barrier_id, TileScratch& sc, float exp_row,
-                                                        float scale_row, float exp_col0, float exp_col1, float scale_col0,
-                                                        float scale_col1, float abs_tol, float rel_tol, float& max_ratio) {
-  const int r_local = half * 32 + lane;
+// The check is split in two so that a caller can overlap the partner exchange with other work (a second tile, the
+// row maximum): abft_tile_sums() by each of the two warps (64 threads) that own the tile's rows, then a barrier over
+// those 64 threads, then abft_tile_decide().  `half` says which 32 rows this warp holds.  `sc` must not be written
+// again before both warps have finished abft_tile_decide().
+__device__ __forceinline__ void abft_tile_sums(const float (&v)[64], int lane, int half, TileScratch& sc, float exp_row, float scale_row,
+                                               float abs_tol, float rel_tol, float& max_ratio) {
   float row_sum = 0.0f;
 #pragma unroll
   for (int c = 0; c < 64; ++c) row_sum += v[c];
@@ -88,7 +85,12 @@ __device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane
     sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
     sc.rows[half].delta = first_delta;
   }
-  asm volatile("bar.sync %0, 64;" ::"r"(barrier_id) : "memory");
+}
+
+// The decision is the same in all 64 threads.  Nothing is corrected here: the caller applies
+// 0.5 * (row_delta + col_delta) to element (bad_row, bad_col) when `corrected` is set.
+__device__ __forceinline__ TileDecision abft_tile_decide(int lane, const TileScratch& sc, float exp_col0, float exp_col1, float scale_col0,
+                                                         float scale_col1, float abs_tol, float rel_tol, float& max_ratio) {
   const float col_delta0 = exp_col0 - (sc.colpart[0][lane] + sc.colpart[1][lane]);
   const float col_delta1 = exp_col1 - (sc.colpart[0][32 + lane] + sc.colpart[1][32 + lane]);
   const float col_thr0 = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_col0), abs_tol);
@@ -123,13 +125,6 @@ __device__ __forceinline__ TileDecision abft_check_tile(float (&v)[64], int lane
       d.col_delta = d1;
     }
     d.corrected = d.bad_rows == 1 && d.bad_cols == 1;
-    if (d.corrected && r_local == d.bad_row) {
-      const float both = d.row_delta + d.col_delta;
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        if (c == d.bad_col) v[c] = __fmaf_rn(0.5f, both, v[c]);
-      }
-    }
   }
   return d;
 }

@@ -379,21 +379,56 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           tmem_add_to_element(s_addr + p.fault_index % kAttnTile, lane, fault_row % 32, p.fault_value);
         }
 
-        // ---- pass 1: verify both 64x64 score tiles of this thread's band, track the row maximum
+        // ---- pass 1: verify both 64x64 score tiles of this thread's band, track the row maximum.  Both halves are
+        // loaded at once; row sums, column partials and the maximum of both are done before the one barrier with the
+        // partner warp, the two decisions after it.
         float row_max = -INFINITY;
+        if (!kProtect) {
+          float v0[64], v1[64];
+          tmem_ld_32x32b_x32(s_addr, v0);
+          tmem_ld_32x32b_x32(s_addr + 32, v0 + 32);
+          tmem_ld_32x32b_x32(s_addr + 64, v1);
+          tmem_ld_32x32b_x32(s_addr + 96, v1 + 32);
+          tmem_wait_ld();
+          abft_tile_sums(v0, lane, half, sh.scratch[t][pair][0], exp_row[0], scale_row[0], p.score_abs_tol, p.score_rel_tol, max_ratio);
+          abft_tile_sums(v1, lane, half, sh.scratch[t][pair][1], exp_row[1], scale_row[1], p.score_abs_tol, p.score_rel_tol, max_ratio);
+          if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (i > row_in_tile) v0[i] = -INFINITY;
+              if (64 + i > row_in_tile) v1[i] = -INFINITY;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, fmaxf(v0[i], v1[i]));
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+        }
+        bool reload_row = false;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const int key_band = j * 2 + c;
-          float v[64];
-          tmem_ld_32x32b_x32(s_addr + c * 64, v);
-          tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
-          tmem_wait_ld();
-          TileDecision d = abft_check_tile(v, lane, half, bar_pair, sh.scratch[t][pair][c], exp_row[c], scale_row[c], exp_col0[c],
-                                           exp_col1[c], scale_col0[c], scale_col1[c], p.score_abs_tol, p.score_rel_tol, max_ratio);
-          if ((d.bad_rows | d.bad_cols) != 0) {
+          if (kProtect) {  // this variant keeps fewer registers live: one half at a time, one barrier each
+            float v[64];
+            tmem_ld_32x32b_x32(s_addr + c * 64, v);
+            tmem_ld_32x32b_x32(s_addr + c * 64 + 32, v + 32);
+            tmem_wait_ld();
+            abft_tile_sums(v, lane, half, sh.scratch[t][pair][c], exp_row[c], scale_row[c], p.score_abs_tol, p.score_rel_tol, max_ratio);
+            if (diagonal) {
+#pragma unroll
+              for (int i = 0; i < 64; ++i) {
+                if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, v[i]);
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+          }
+          const TileDecision d = abft_tile_decide(lane, sh.scratch[t][pair][c], exp_col0[c], exp_col1[c], scale_col0[c], scale_col1[c],
+                                                  p.score_abs_tol, p.score_rel_tol, max_ratio);
+          if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps of the band
             if (d.corrected && d.bad_row / 32 == half) {
-              // the corrected score must also be what pass 2 reads back
+              // src/s4:493-497 on the accumulator itself: pass 2 reads the corrected score back
               tmem_add_to_element(s_addr + c * 64 + d.bad_col, lane, d.bad_row % 32, 0.5f * (d.row_delta + d.col_delta));
+              reload_row = true;
             }
             if (half == 0 && lane == 0) {
               atomicAdd(&p.report->score_detected, 1);
@@ -401,7 +436,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
               int slot = atomicAdd(&p.report->record_count, 1);
               if (slot < 16) {
                 ft_tile_record rec;
-                rec.tile = (bh * tile_cols + q_band) * tile_cols + key_band;
+                rec.tile = (bh * tile_cols + q_band) * tile_cols + j * 2 + c;
                 rec.bad_row_count = d.bad_rows;
                 rec.bad_col_count = d.bad_cols;
                 rec.bad_row = d.bad_row;
@@ -413,14 +448,19 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
               }
             }
           }
-          if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
+        }
+        if (reload_row) {  // warp-uniform and rare: the maximum of the corrected row is taken from the corrected scores
+          row_max = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float v[32];
+            tmem_ld_32x32b_x32(s_addr + c * 32, v);
+            tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-              if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+            for (int i = 0; i < 32; ++i) {
+              if (!diagonal || c * 32 + i <= row_in_tile) row_max = fmaxf(row_max, v[i]);
             }
           }
-#pragma unroll
-          for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, v[i]);
         }
 
         // ---- online softmax state (log2 domain)
