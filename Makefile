@@ -8,7 +8,7 @@ ARCH      ?= -gencode arch=compute_100a,code=sm_100a
 NVCCFLAGS ?= -O3 -std=c++17 -lineinfo $(ARCH) -Xcompiler -fPIC -Xptxas -v
 CSRC      := ft_gemm_b200/csrc
 LIB       := ft_gemm_b200/lib/libft_gemm_b200.so
-OBJS      := build/obj/prepare.o build/obj/prepare_mma.o build/obj/abft_gemm.o build/obj/api.o build/obj/noalloc.o build/obj/ft_attention.o build/obj/api_attention.o build/obj/gemm_softmax.o
+OBJS      := build/obj/prepare.o build/obj/prepare_mma.o build/obj/abft_gemm.o build/obj/api.o build/obj/noalloc.o build/obj/ft_attention.o build/obj/ft_attention_split.o build/obj/api_attention.o build/obj/gemm_softmax.o
 HDRS      := include/ft_gemm.h include/ft_attention.h include/ft_gemm_softmax.h $(CSRC)/kernels.h $(CSRC)/attention_kernels.h $(CSRC)/abft_tile_check.cuh $(CSRC)/sm100_ptx.cuh
 
 FAULT_TRIALS    ?= 100

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -129,6 +130,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   ATTN_CUDA(cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10) return noalloc_fail(FT_ERR_UNSUPPORTED, "this library needs an sm_100 GPU (found sm_%d%d)", prop.major, prop.minor);
   ATTN_CUDA(configure_attention());
+  ATTN_CUDA(configure_attention_split());
   if (opts.exact_prepare == 0) ATTN_CUDA(configure_prepare_mma());
 
   ft_attn_handle* h = new (std::nothrow) ft_attn_handle();
@@ -285,7 +287,17 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   ATTN_CUDA(cudaMemsetAsync(h->report, 0, 48, stream));
-  ATTN_CUDA(launch_attention(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
+  // The split-row kernel (two threads per query row) is the default; the whole-row kernel carries the softmax-stage
+  // protection and can be selected for comparison with FT_ATTENTION_KERNEL=row in the environment.
+  static const bool force_row = [] {
+    const char* choice = std::getenv("FT_ATTENTION_KERNEL");
+    return choice != nullptr && std::strcmp(choice, "row") == 0;
+  }();
+  if (params.protect_softmax != 0 || force_row) {
+    ATTN_CUDA(launch_attention(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
+  } else {
+    ATTN_CUDA(launch_attention_split(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
+  }
   h->last_stream = stream;
   return FT_OK;
 }

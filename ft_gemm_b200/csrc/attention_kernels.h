@@ -47,5 +47,9 @@ cudaError_t launch_generate_f16(void* out, size_t count, uint32_t seed, int dist
 cudaError_t configure_attention();
 cudaError_t launch_attention(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                              int batch_heads, cudaStream_t stream);
+// the split-row form (two threads per query row; no softmax-stage protection): ft_attention_split.cu
+cudaError_t configure_attention_split();
+cudaError_t launch_attention_split(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
+                                   int batch_heads, cudaStream_t stream);
 
 }  // namespace ftg

@@ -1,0 +1,537 @@
+// Fault-tolerant flash-attention forward, split-row form (the default kernel; the
+// form with one thread per whole row in ft_attention.cu serves the softmax-stage
+// protection).
+//
+// Same data flow as ft_attention.cu -- one CTA owns 256 queries of one (batch,
+// head) as two 128-query tiles A and B that share every 128-key K / V^T tile, S and
+// O live in TMEM, P goes through shared memory -- but every query row is worked on
+// by TWO threads: the softmax / verifier warpgroup (t, c) takes the key half c
+// (64 columns = exactly one 64x64 ABFT tile per 64-row band) of query tile t.
+//   warpgroup 0        warp 0 TMA producer, warp 1 MMA issuer (as before)
+//   warpgroups 1..4    (t, c) = (A,0), (A,1), (B,0), (B,1); 16 softmax warps per SM
+//                      instead of 8: the kernel is bound by latency (barriers, TMEM
+//                      loads, dependent FP32 chains), not by a pipe, and the second
+//                      set of warps fills the idle issue slots.
+// Per key tile the two threads of a row exchange one number, their row maxima
+// (shared memory + one 256-thread barrier); the running sums l, sum p*vsum,
+// sum p*vweighted stay per half and are added once at the end, where the output
+// projection check (src/ft_flash_attention_a0.cu:613-662) needs two more exchanges.
+// The ABFT check of a score tile still pairs the two warps that hold rows 0-31 and
+// 32-63 of the band (abft_tile_check.cuh); both belong to the same warpgroup.
+// Every wait is bounded; on expiry the kernel reports status and leaves.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "abft_tile_check.cuh"
+#include "attention_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace ftg {
+
+namespace {
+
+constexpr int kTile = 128;             // queries per tile, keys per tile, head dimension
+constexpr int kQTiles = 2;             // query tiles per CTA
+constexpr int kSlabBytes = 128 * 128;  // 128 rows x 64 FP16 (one 128-byte swizzle row each)
+constexpr int kTileBytes = 2 * kSlabBytes;
+constexpr int kThreads = 640;
+constexpr uint64_t kTimeoutNs = 2000000000ull;
+constexpr uint32_t kTmemS = 0;    // score buffers of tile A, B at columns 0, 128
+constexpr uint32_t kTmemO = 256;  // output accumulators of tile A, B at columns 256, 384
+
+struct SplitShared {
+  uint64_t q_full, k_full, k_empty, v_full, v_empty;
+  uint64_t s_full[kQTiles], s_empty[kQTiles];
+  uint64_t p_full[kQTiles], p_empty[kQTiles];
+  uint32_t tmem_base;
+  int abort_flag;
+  float4 v_meta[kQTiles][2][kTile / 2];    // [query tile][parity][key pair]: {sum_d V of both keys, sum_d w_d V of both keys}
+  TileScratch scratch[kQTiles][2][2];      // [query tile][key half][row pair]
+  float row_max[kQTiles][2][2][kTile];     // [query tile][parity][key half][row]: the half's row maximum of this key tile
+  float4 final_sums[kQTiles][2][kTile];    // [query tile][key half][row]: {l, sum p*vsum, sum p*vweighted, -}
+  float2 final_actual[kQTiles][2][kTile];  // [query tile][dim half][row]: {sum_d o, sum_d w_d o} over the half's 64 dims
+};
+
+constexpr int kSmemBytes = 6 * kTileBytes + static_cast<int>(sizeof(SplitShared)) + 1024;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Every lane polls the barrier itself (no CTA-level barrier around the wait); the verdict is made uniform over the warp.
+// A warp whose wait was abandoned stops working but keeps executing the named barriers of the remaining key tiles
+// (see the drain loop in the kernel), so that the warps it shares those barriers with are never left waiting.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const bool ok = mbar_wait_bounded(bar, parity, abort_flag, kTimeoutNs);
+  return __all_sync(0xffffffffU, ok);
+}
+
+// Adds `value` to one element of a TMEM column in place; executed by the whole warp that owns the row's lane quarter.
+__device__ __forceinline__ void tmem_add(uint32_t taddr_column, int lane, int target_lane, float value) {
+  float x;
+  tmem_ld_32x32b_x1(taddr_column, x);
+  tmem_wait_ld();
+  if (lane == target_lane) x += value;
+  tmem_st_32x32b_x1(taddr_column, x);
+  tmem_wait_st();
+}
+
+template <int Regs>
+__device__ __forceinline__ void reg_release() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Regs));
+}
+template <int Regs>
+__device__ __forceinline__ void reg_acquire() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Regs));
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1)
+ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smem_q = smem;                   // 2 query tiles
+  uint8_t* smem_k = smem + 2 * kTileBytes;  // 1 stage
+  uint8_t* smem_v = smem + 3 * kTileBytes;  // 1 stage
+  uint8_t* smem_p = smem + 4 * kTileBytes;  // 2 query tiles
+  SplitShared& sh = *reinterpret_cast<SplitShared*>(smem + 6 * kTileBytes);
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int group = warp >> 2;  // 0: producer + MMA; 1..4: softmax of (tile, key half) = (A,0), (A,1), (B,0), (B,1)
+  const int bh = blockIdx.y;
+  // causal CTAs get longer towards the end of the sequence: the longest are scheduled first
+  const int q_block = p.causal != 0 ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int q0 = q_block * kQTiles * kTile;
+  const int seq = p.seq;
+  const int num_tiles = seq / kTile;
+  const int row_base = bh * seq;  // first row of this head in the [B*H*N, D] matrices
+  const int qtiles = q0 + kQTiles * kTile <= seq ? kQTiles : 1;  // the last CTA of a head may own one tile
+  // causal (src/ft_flash_attention_a14.cu:708): query tile t stops after the key tile on its diagonal
+  const bool causal = p.causal != 0;
+  const int first_qtile = q0 / kTile;
+  auto tiles_of = [&](int t) { return causal ? min(num_tiles, first_qtile + t + 1) : num_tiles; };
+  const int cta_tiles = tiles_of(qtiles - 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh.q_full, 1);
+    mbar_init(&sh.k_full, 1);
+    mbar_init(&sh.k_empty, 1);
+    mbar_init(&sh.v_full, 1);
+    mbar_init(&sh.v_empty, 1);
+    for (int t = 0; t < kQTiles; ++t) {
+      mbar_init(&sh.s_full[t], 1);
+      mbar_init(&sh.s_empty[t], 256);  // both key halves have read S
+      mbar_init(&sh.p_full[t], 256);   // both halves of P are written
+      mbar_init(&sh.p_empty[t], 1);
+    }
+    sh.abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_vt);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (group == 0) {
+    reg_release<40>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------- producer
+      mbar_arrive_expect_tx(&sh.q_full, qtiles * kTileBytes);
+      for (int t = 0; t < qtiles; ++t) {
+        tma_load_2d(smem_q + t * kTileBytes, &tmap_q, &sh.q_full, 0, row_base + q0 + t * kTile);
+        tma_load_2d(smem_q + t * kTileBytes + kSlabBytes, &tmap_q, &sh.q_full, 64, row_base + q0 + t * kTile);
+      }
+      for (int j = 0; j < cta_tiles; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait_bounded(&sh.k_empty, ph ^ 1, abort_flag, kTimeoutNs)) break;
+        mbar_arrive_expect_tx(&sh.k_full, kTileBytes);
+        tma_load_2d(smem_k, &tmap_k, &sh.k_full, 0, row_base + j * kTile);
+        tma_load_2d(smem_k + kSlabBytes, &tmap_k, &sh.k_full, 64, row_base + j * kTile);
+        if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kTimeoutNs)) break;
+        mbar_arrive_expect_tx(&sh.v_full, kTileBytes);
+        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kTile, bh * kTile);
+        tma_load_2d(smem_v + kSlabBytes, &tmap_vt, &sh.v_full, j * kTile + 64, bh * kTile);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc_f16_f32(kTile, kTile);
+      bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kTimeoutNs);
+      for (int j = 0; j <= cta_tiles && alive; ++j) {
+        if (j < cta_tiles) {  // S_A, S_B = Q_{A,B} K_j^T
+          if (!mbar_wait_bounded(&sh.k_full, j & 1, abort_flag, kTimeoutNs)) break;
+          for (int t = 0; t < qtiles && alive; ++t) {
+            if (j >= tiles_of(t)) continue;
+            // the score buffer of tile t is free once both key halves have read S_{j-1} for the second time
+            if (!mbar_wait_bounded(&sh.s_empty[t], (j & 1) ^ 1, abort_flag, kTimeoutNs)) {
+              alive = false;
+              break;
+            }
+            tcgen05_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              uint64_t da = make_smem_desc_sw128(smem_u32(smem_q + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+              uint64_t db = make_smem_desc_sw128(smem_u32(smem_k + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+              umma_f16(tmem_base + kTmemS + t * kTile, da, db, idesc, kk != 0 ? 1u : 0u);
+            }
+            umma_commit(&sh.s_full[t]);
+          }
+          if (!alive) break;
+          umma_commit(&sh.k_empty);
+        }
+        if (j > 0) {  // O_{A,B} += P_i V_i for the previous key tile
+          const int i = j - 1;
+          if (!mbar_wait_bounded(&sh.v_full, i & 1, abort_flag, kTimeoutNs)) break;
+          for (int t = 0; t < qtiles && alive; ++t) {
+            if (i >= tiles_of(t)) continue;
+            if (!mbar_wait_bounded(&sh.p_full[t], i & 1, abort_flag, kTimeoutNs)) {
+              alive = false;
+              break;
+            }
+            tcgen05_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              uint64_t da = make_smem_desc_sw128(smem_u32(smem_p + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+              uint64_t db = make_smem_desc_sw128(smem_u32(smem_v + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+              umma_f16(tmem_base + kTmemO + t * kTile, da, db, idesc, (i | kk) != 0 ? 1u : 0u);
+            }
+            umma_commit(&sh.p_empty[t]);
+          }
+          if (!alive) break;
+          umma_commit(&sh.v_empty);
+        }
+      }
+    }
+  } else {
+    reg_acquire<104>();
+    // ------------------------------------------------------------- softmax / verifier: two threads per query row
+    const int t = (group - 1) >> 1;  // query tile of this warpgroup
+    const int c = (group - 1) & 1;   // key half of S / dim half of O this warpgroup works on
+    if (t < qtiles) {
+      const int quarter = warp & 3;
+      const int pair = quarter >> 1;
+      const int half = quarter & 1;
+      const int r_local = half * 32 + lane;
+      const int row_in_tile = quarter * 32 + lane;
+      const int tg = threadIdx.x & 127;
+      const int bar_tile = 1 + t;                         // 256-thread barrier of the two warpgroups of tile t (ids 1, 2)
+      const int bar_pair = 3 + 2 * (group - 1) + pair;    // 64-thread barrier of this 64-row band (ids 3..10)
+      const int tile_cols = seq / 64;
+      const size_t head_cache = static_cast<size_t>(bh) * tile_cols * tile_cols * 64;
+      const int q_tile0 = q0 + t * kTile;
+      const int q_band = q_tile0 / 64 + pair;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t s_addr = lane_addr + kTmemS + t * kTile + c * 64;  // this half's 64 score columns
+      const uint32_t o_addr = lane_addr + kTmemO + t * kTile + c * 64;  // this half's 64 output dims
+      uint8_t* p_row = smem_p + t * kTileBytes + c * kSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+      const bool fault_here = p.fault_bh == bh && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kTile;
+      const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE && (p.fault_index % kTile) / 64 == c;
+      const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_index / 64 == c;
+      const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
+      TileScratch& scratch = sh.scratch[t][c][pair];
+
+      float m_run = -INFINITY, l_run = 0.0f, exp_sum = 0.0f, exp_weighted = 0.0f, max_ratio = 0.0f;  // the sums: this half's share
+      bool alive = true;
+      const int my_tiles = tiles_of(t);
+      int drain_from = my_tiles;      // when a wait is abandoned: first key tile whose named barriers are still owed ...
+      bool drain_skip_first = false;  // ... unless that tile's two barriers were already passed
+      for (int j = 0; j < my_tiles; ++j) {
+        const int buf = j & 1;
+        const bool diagonal = causal && j == first_qtile + t;  // keys beyond the query are masked in this tile
+        // per-key sums of V for this half's 64 keys (read in pass 2; published by the 256-thread barrier of the exchange)
+        if (tg < 64) {
+          const size_t key = static_cast<size_t>(bh) * seq + j * kTile + c * 64 + tg;
+          float* meta = reinterpret_cast<float*>(&sh.v_meta[t][buf][(c * 64 + tg) >> 1]);  // pairs laid out for packed FP32 math
+          meta[tg & 1] = __ldg(p.v_sum + key);
+          meta[2 + (tg & 1)] = __ldg(p.v_weighted + key);
+        }
+        // cached expected checksums of this thread's 64x64 tile: fetched before the wait
+        const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
+        const float exp_row = __ldg(p.expected_rows + cache + r_local);
+        const float scale_row = __ldg(p.row_scales + cache + r_local);
+        const float exp_col0 = __ldg(p.expected_cols + cache + lane);
+        const float exp_col1 = __ldg(p.expected_cols + cache + 32 + lane);
+        const float scale_col0 = __ldg(p.col_scales + cache + lane);
+        const float scale_col1 = __ldg(p.col_scales + cache + 32 + lane);
+        if (!warp_wait(&sh.s_full[t], j & 1, abort_flag)) {
+          alive = false;
+          drain_from = j;
+          break;
+        }
+        tcgen05_fence_after();
+
+        // test hook: the fault enters the accumulator itself, before any checksum
+        if (score_fault && p.fault_index / kTile == j && fault_row / 32 == quarter) {
+          tmem_add(s_addr + p.fault_index % 64, lane, fault_row % 32, p.fault_value);
+        }
+
+        // ---- pass 1: verify this thread's 64x64 score tile, take the half's row maximum
+        float local_max = -INFINITY;
+        {
+          float v[64];
+          tmem_ld_32x32b_x32(s_addr, v);
+          tmem_ld_32x32b_x32(s_addr + 32, v + 32);
+          tmem_wait_ld();
+          abft_tile_sums(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
+          if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 64; ++i) local_max = fmaxf(local_max, v[i]);
+        }
+        asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+        {
+          const TileDecision d = abft_tile_decide(lane, scratch, exp_col0, exp_col1, scale_col0, scale_col1, p.score_abs_tol,
+                                                  p.score_rel_tol, max_ratio);
+          if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps of the band
+            if (d.corrected && d.bad_row / 32 == half) {
+              // src/s4:493-497 on the accumulator itself: pass 2 reads the corrected score back
+              tmem_add(s_addr + d.bad_col, lane, d.bad_row % 32, 0.5f * (d.row_delta + d.col_delta));
+              // warp-uniform and rare: the maximum of the corrected row is taken from the corrected scores
+              local_max = -INFINITY;
+#pragma unroll 1
+              for (int cc = 0; cc < 2; ++cc) {
+                float v[32];
+                tmem_ld_32x32b_x32(s_addr + cc * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (!diagonal || c * 64 + cc * 32 + i <= row_in_tile) local_max = fmaxf(local_max, v[i]);
+                }
+              }
+            }
+            if (half == 0 && lane == 0) {
+              atomicAdd(&p.report->score_detected, 1);
+              atomicAdd(d.corrected ? &p.report->score_corrected : &p.report->score_uncorrected, 1);
+              int slot = atomicAdd(&p.report->record_count, 1);
+              if (slot < 16) {
+                ft_tile_record rec;
+                rec.tile = (bh * tile_cols + q_band) * tile_cols + j * 2 + c;
+                rec.bad_row_count = d.bad_rows;
+                rec.bad_col_count = d.bad_cols;
+                rec.bad_row = d.bad_row;
+                rec.bad_col = d.bad_col;
+                rec.row_delta = d.row_delta;
+                rec.col_delta = d.col_delta;
+                rec.corrected = d.corrected ? 1 : 0;
+                p.report->records[slot] = rec;
+              }
+            }
+          }
+        }
+        // ---- the two halves of the row exchange their maxima
+        sh.row_max[t][buf][c][row_in_tile] = local_max;
+        asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+        const float row_max = fmaxf(local_max, sh.row_max[t][buf][c ^ 1][row_in_tile]);
+
+        // ---- online softmax state (log2 domain); identical in both threads of the row
+        const float m_new = fmaxf(m_run, row_max * p.scale_log2);
+        const float alpha = fast_exp2(m_run - m_new);  // 0 for the first tile (m_run = -inf)
+
+        if (j > 0) {
+          // PV of the previous tile must have finished: the P buffer is free and O is quiescent
+          if (!warp_wait(&sh.p_empty[t], (j - 1) & 1, abort_flag)) {
+            alive = false;
+            drain_from = j;
+            drain_skip_first = true;
+            break;
+          }
+          tcgen05_fence_after();
+          if (__any_sync(0xffffffffU, alpha != 1.0f)) {
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {  // this half's 64 output dims
+              float o[32];
+              tmem_ld_32x32b_x32(o_addr + cc * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tmem_st_32x32b_x32(o_addr + cc * 32, o);
+            }
+            tmem_wait_st();
+          }
+        }
+        // ---- pass 2: probabilities of this half, FP16 P slab for the MMA, this half's share of the expected projections
+        float l_tile = 0.0f, es_tile = 0.0f, ew_tile = 0.0f;
+        {
+          float v[64];
+          tmem_ld_32x32b_x32(s_addr, v);
+          tmem_ld_32x32b_x32(s_addr + 32, v + 32);
+          tmem_wait_ld();
+          tcgen05_fence_before();
+          mbar_arrive(&sh.s_empty[t]);  // in registers: the score buffer can take S of the next key tile
+          if (diagonal) {  // exp2(-inf) = 0: a masked key gets probability zero
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+            }
+          }
+          // two scores per instruction where the arithmetic allows it (packed FP32 pairs)
+          const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg_m2 = pack_f32x2(-m_new, -m_new);
+          unsigned long long l2 = pack_f32x2(0.0f, 0.0f), es2 = l2, ew2 = l2;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i0 = ch * 8 + 2 * e;
+              float a0, a1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(v[i0], v[i0 + 1]), scale2, neg_m2), a0, a1);
+              const __half2 h = __floats2half2_rn(fast_exp2(a0), fast_exp2(a1));
+              const float2 r = __half22float2(h);  // what the MMA will multiply by V
+              const unsigned long long r2 = pack_f32x2(r.x, r.y);
+              l2 = add_f32x2(l2, r2);
+              const float4 meta = sh.v_meta[t][buf][(c * 64 + i0) >> 1];
+              es2 = fma_f32x2(r2, pack_f32x2(meta.x, meta.y), es2);
+              ew2 = fma_f32x2(r2, pack_f32x2(meta.z, meta.w), ew2);
+              packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+            *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+          float lo, hi;
+          unpack_f32x2(l2, lo, hi);
+          l_tile = lo + hi;
+          unpack_f32x2(es2, lo, hi);
+          es_tile = lo + hi;
+          unpack_f32x2(ew2, lo, hi);
+          ew_tile = lo + hi;
+        }
+        l_run = __fmaf_rn(alpha, l_run, l_tile);
+        exp_sum = __fmaf_rn(alpha, exp_sum, es_tile);
+        exp_weighted = __fmaf_rn(alpha, exp_weighted, ew_tile);
+        m_run = m_new;
+        fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
+        tcgen05_fence_before();
+        mbar_arrive(&sh.p_full[t]);
+      }
+      // ---- output stage: projection check of O / l (src/ft_flash_attention_a0.cu:613-662), normalise, store
+      for (int jj = drain_from; jj < my_tiles; ++jj) {  // only after an abandoned wait: the barriers the other warps count on
+        if (jj == drain_from && drain_skip_first) continue;
+        asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+        asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+      }
+      // The two exchange barriers of the output stage are executed by every warp; a warp that gave up skips the work in
+      // between (the run is reported as timed out, its output is not valid).
+      alive = alive && warp_wait(&sh.p_empty[t], (my_tiles - 1) & 1, abort_flag);
+      if (alive) {
+        tcgen05_fence_after();
+        sh.final_sums[t][c][row_in_tile] = make_float4(l_run, exp_sum, exp_weighted, 0.0f);
+      }
+      asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+      if (!alive) asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+      if (alive) {
+        const float4 other = sh.final_sums[t][c ^ 1][row_in_tile];
+        // totals in a fixed order (half 0 + half 1) so that both threads of the row hold the same bits
+        const float l_total = c == 0 ? l_run + other.x : other.x + l_run;
+        const float es_total = c == 0 ? exp_sum + other.y : other.y + exp_sum;
+        const float ew_total = c == 0 ? exp_weighted + other.z : other.z + exp_weighted;
+        const float inv_l = 1.0f / l_total;
+        const int query = q_tile0 + row_in_tile;
+        const bool my_fault = output_fault && fault_row == row_in_tile;
+        float actual_sum = 0.0f, actual_weighted = 0.0f;
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          float o[32];
+          tmem_ld_32x32b_x32(o_addr + cc * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int dim = c * 64 + cc * 32 + i;
+            float x = o[i] * inv_l;
+            if (my_fault && p.fault_index == dim) x += p.fault_value;
+            actual_sum += x;
+            actual_weighted = __fmaf_rn(static_cast<float>(2 * dim - (kTile - 1)), x, actual_weighted);
+          }
+        }
+        sh.final_actual[t][c][row_in_tile] = make_float2(actual_sum, actual_weighted);
+        asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+        const float2 other_actual = sh.final_actual[t][c ^ 1][row_in_tile];
+        const float sum_total = c == 0 ? actual_sum + other_actual.x : other_actual.x + actual_sum;
+        const float weighted_total = c == 0 ? actual_weighted + other_actual.y : other_actual.y + actual_weighted;
+        const float expected_sum = es_total * inv_l;
+        const float expected_weighted = ew_total * inv_l;
+        const float delta_sum = sum_total - expected_sum;
+        const float delta_weighted = weighted_total - expected_weighted;
+        const float thr_sum = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_sum)), p.pv_abs_tol);
+        const float thr_weighted = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_weighted)), p.pv_abs_tol);
+        int recover_dim = -1;
+        if (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted) {  // the same in both threads of the row
+          if (fabsf(delta_sum) > thr_sum) {
+            const float observed_weight = delta_weighted / delta_sum;
+            const int dim = __float2int_rn(0.5f * (observed_weight + static_cast<float>(kTile - 1)));
+            if (dim >= 0 && dim < kTile && fabsf(observed_weight - static_cast<float>(2 * dim - (kTile - 1))) <= 0.25f) recover_dim = dim;
+          }
+          if (c == 0) {  // one of the two threads reports
+            atomicAdd(&p.report->pv_detected, 1);
+            atomicAdd(recover_dim >= 0 ? &p.report->pv_corrected : &p.report->failed_rows, 1);
+          }
+        }
+        float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kTile + c * 64;
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          float o[32];
+          tmem_ld_32x32b_x32(o_addr + cc * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int dim = c * 64 + cc * 32 + i;
+            float x = o[i] * inv_l;
+            if (my_fault && p.fault_index == dim) x += p.fault_value;
+            if (recover_dim == dim) x -= delta_sum;
+            o[i] = x;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+          }
+        }
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) max_ratio = fmaxf(max_ratio, __shfl_xor_sync(0xffffffffU, max_ratio, off));
+      if (lane == 0) atomicMax(&p.report->max_noise_bits, __float_as_int(max_ratio));
+    }
+  }
+
+  // ------------------------------------------------------------------- teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if (sh.abort_flag != 0) {
+    if (threadIdx.x == 0) atomicExch(&p.report->status, 1);
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+cudaError_t configure_attention_split() {
+  return cudaFuncSetAttribute(ft_attention_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+cudaError_t launch_attention_split(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
+                                   int batch_heads, cudaStream_t stream) {
+  dim3 grid((params.seq + kQTiles * kTile - 1) / (kQTiles * kTile), batch_heads);
+  ft_attention_split_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  return cudaGetLastError();
+}
+
+}  // namespace ftg

@@ -172,7 +172,8 @@ def test_softmax_stage_protection(ftg):
     op.run(clean)
     rep = op.report()
     assert (rep.softmax_detected, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
-    assert torch.equal(clean, plain)  # the protection changes nothing when nothing is wrong
+    # the protection changes nothing when nothing is wrong (the two kernels add the row sums in a different order)
+    assert float((clean - plain).abs().max()) < 2e-6
     want, _, _ = oa.forward(_np(q), _np(k), _np(v), protect_softmax=True)
     np.testing.assert_allclose(_np(clean), want, atol=2e-3, rtol=0)
     out = op.new_output()
@@ -235,11 +236,13 @@ def test_causal_forward_and_faults(ftg, n):
     op.close()
     # with the softmax-stage protection
     op = ftg.FtAttention(q, k, v, causal=True, protect_softmax=True)
-    op.run(out)
-    assert torch.equal(out, clean) and op.report().softmax_detected == 0
+    protected = op.new_output()
+    op.run(protected)
+    # the protected form runs in the whole-row kernel, which adds the row sums in another order than the split-row one
+    assert float((protected - clean).abs().max()) < 2e-6 and op.report().softmax_detected == 0
     fault = (ftg.FAULT_SOFTMAX, 0, 1, n - 1, n - 3, 0.25)
     op.run(out, fault)
     rep = op.report()
     assert (rep.softmax_detected, rep.softmax_corrected) == (1, 1)
-    assert torch.equal(out, clean)
+    assert torch.equal(out, protected)
     op.close()
