@@ -45,6 +45,25 @@ def test_stage_program_clean_and_injected():
     assert rc == 1 and rep["bad_tiles"] == "0" and rep["verification"] == "FAIL"
 
 
+def test_stage_program_added_flags():
+    """--fault2 (the tile is reported, not corrected), --seed, --json, --gpus."""
+    import json
+    rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 512, "--n", 512, "--k", 256, "--repeat", 2, "--fault2", "--fault-value", 3.0)
+    assert rc == 0 and (rep["bad_tiles"], rep["corrected_tiles"], rep["multi_fault_tiles"], rep["verification"]) == ("1", "0", "1", "PASS")
+    exe = os.path.join(BUILD, "stage_abft_fp8_gemm")
+    out = subprocess.run([exe, "--m", "256", "--n", "256", "--k", "128", "--repeat", "2", "--seed", "7", "--json"], capture_output=True,
+                         text=True, timeout=300)
+    assert out.returncode == 0
+    doc = json.loads(out.stdout.splitlines()[-1])
+    assert doc["verification"] == "PASS" and doc["bad_tiles"] == 0 and doc["gpus"] == 1 and doc["fused_gemm_tflops"] > 0
+    rc, rep, err = run("stage_abft_fp8_gemm", "--gpus", 64)
+    assert rc == 1 and "needs that many devices" in err
+    import torch
+    if torch.cuda.device_count() >= 2:
+        rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 1024, "--n", 512, "--k", 256, "--repeat", 2, "--gpus", 2, "--inject-fault")
+        assert rc == 0 and (rep["gpus"], rep["rows_per_gpu"], rep["bad_tiles"], rep["corrected_tiles"]) == ("2", "512", "1", "1")
+
+
 def test_stage_program_rejects_bad_shapes():
     for args in (["--m", 0], ["--n", 0], ["--k", -8], ["--repeat", 0]):
         rc, rep, err = run("stage_abft_fp8_gemm", *args)
