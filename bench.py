@@ -145,7 +145,38 @@ def run_reference(args):
             "config": {"workload": f"abft_fp8_gemm M=N=K=8192 (CPU: one {rows}-row band per step)", "m": rows, "n": N_DIM, "k": K_DIM},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": values[0]["cores"], "kind": "port", "sample": values[0]["sample"]},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    gpu_program = _reference_gpu_program()
+    if gpu_program is not None:
+        line["reference_gpu_s0"] = gpu_program
     print(json.dumps(line))
+
+
+def _reference_gpu_program():
+    """For the record beside the CPU arm: the one stage of the reference that runs on this GPU generation, its scalar
+    first stage, built unmodified from the reference's source (oracle/_ref/ref_program_s0), at 4096^3.  None when the
+    binary or a GPU is missing."""
+    import subprocess
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_program_s0")
+    if not os.path.exists(exe):
+        return None
+    try:
+        out = subprocess.run([exe, "--m", "4096", "--n", "4096", "--k", "4096", "--warmup", "2", "--repeat", "5"], capture_output=True,
+                             text=True, timeout=120)
+    except (OSError, subprocess.TimeoutExpired):
+        return None
+    if out.returncode != 0:
+        return None
+    keys = {}
+    for text in out.stdout.splitlines():
+        key, sep, value = text.partition(": ")
+        if sep:
+            keys[key] = value
+    try:
+        return {"shape": "M=N=K=4096", "steady_state_tflops": float(keys["steady_state_tflops"]),
+                "steady_state_ms": float(keys["avg_steady_state_end_to_end_time_ms"]),
+                "prepare_ms": float(keys["expected_prepare_time_ms"]), "verification": keys.get("verification")}
+    except (KeyError, ValueError):
+        return None
 
 
 def main():
