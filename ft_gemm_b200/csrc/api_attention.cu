@@ -111,9 +111,14 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
                                    int head_dim, const ft_attn_options* options, void* stream_ptr) {
   if (handle == nullptr || q == nullptr || k == nullptr || v == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or operand pointer");
   *handle = nullptr;
-  if (batch <= 0 || heads <= 0 || seq <= 0 || seq % 128 != 0 || head_dim != 128) {
-    return noalloc_fail(FT_ERR_INVALID, "Invalid options. Require head_dim == 128, sequence %% 128 == 0 and positive batch/heads (got B=%d H=%d N=%d D=%d).",
+  if (batch <= 0 || heads <= 0 || seq <= 0 || seq % 128 != 0 || (head_dim != 128 && head_dim != 64)) {
+    return noalloc_fail(FT_ERR_INVALID,
+                        "Invalid options. Require head_dim 64 or 128 (src/ft_flash_attention_a14.cu:267), sequence %% 128 == 0 and positive "
+                        "batch/heads (got B=%d H=%d N=%d D=%d).",
                         batch, heads, seq, head_dim);
+  }
+  if (head_dim == 64 && options != nullptr && options->protect_softmax != 0) {
+    return noalloc_fail(FT_ERR_UNSUPPORTED, "the softmax-stage protection is built for head_dim 128 only");
   }
   if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0) {
     return noalloc_fail(FT_ERR_INVALID, "Q, K and V must be 16-byte aligned");
@@ -179,7 +184,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   int rc = make_f16_map(&h->tmap_q, q, bh * seq, head_dim);
   if (rc == FT_OK) rc = make_f16_map(&h->tmap_k, k, bh * seq, head_dim);
-  if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt, h->vt, bh * head_dim, seq);
+  if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt, h->vt, bh * head_dim, seq, static_cast<unsigned>(head_dim));
   if (rc == FT_OK && opts.exact_prepare == 0) {
     __half* cursor16 = static_cast<__half*>(h->planes);
     h->q_ws = cursor16, cursor16 += ws_elems;
@@ -196,7 +201,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
     err = cudaMemsetAsync(h->report, 0, sizeof(AttnDeviceReport), stream);
     if (err == cudaSuccess) err = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
     if (err == cudaSuccess) err = cudaEventRecord(h->ev0, stream);
-    if (err == cudaSuccess) err = launch_attn_prepare_v(v, h->vt, h->v_sum, h->v_weighted, static_cast<int>(bh), seq, stream);
+    if (err == cudaSuccess) err = launch_attn_prepare_v(v, h->vt, h->v_sum, h->v_weighted, static_cast<int>(bh), seq, head_dim, stream);
     if (err == cudaSuccess) err = launch_band_sums_f16(q, h->q_sums, h->q_mags, bh * seq, head_dim, stream);
     if (err == cudaSuccess) err = launch_band_sums_f16(k, h->k_sums, h->k_mags, bh * seq, head_dim, stream);
     // per head: S = Q K^T is the GEMM A = Q [N, D], B = K [N, D]
@@ -252,6 +257,7 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   params.out = out;
   params.report = h->report;
   params.seq = h->seq;
+  params.dim = h->dim;
   params.score_abs_tol = h->options.score_abs_tol;
   params.score_rel_tol = h->options.score_rel_tol;
   params.pv_abs_tol = h->options.pv_abs_tol;
@@ -293,7 +299,7 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
     const char* choice = std::getenv("FT_ATTENTION_KERNEL");
     return choice != nullptr && std::strcmp(choice, "row") == 0;
   }();
-  if (params.protect_softmax != 0 || force_row) {
+  if (params.protect_softmax != 0 || (force_row && h->dim == 128)) {
     ATTN_CUDA(launch_attention(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
   } else {
     ATTN_CUDA(launch_attention_split(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));

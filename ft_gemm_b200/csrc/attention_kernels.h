@@ -33,6 +33,7 @@ struct AttnParams {
   float* out;               // [B*H][N][D]
   AttnDeviceReport* report;
   int seq;
+  int dim;  // head dimension: 128, or 64 (split-row kernel only)
   float score_abs_tol, score_rel_tol, pv_abs_tol, pv_rel_tol, softmax_abs_tol, softmax_rel_tol;
   int protect_softmax;
   int causal;
@@ -41,7 +42,7 @@ struct AttnParams {
   float fault_value;
 };
 
-cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq,
+cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq, int dim,
                                   cudaStream_t stream);
 cudaError_t launch_generate_f16(void* out, size_t count, uint32_t seed, int dist, float sigma, cudaStream_t stream);
 cudaError_t configure_attention();

@@ -61,33 +61,34 @@ constexpr int kAttnSmemBytes = 6 * kAttnTileBytes + static_cast<int>(sizeof(Attn
 // grid (N/32, B*H), 256 threads.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_prepare_v_kernel(const __half* __restrict__ v, __half* __restrict__ vt,
-                                                             float* __restrict__ v_sum, float* __restrict__ v_weighted, int seq) {
-  __shared__ __half tile[32][kAttnTile + 2];
+                                                             float* __restrict__ v_sum, float* __restrict__ v_weighted, int seq,
+                                                             int dim) {
+  __shared__ __half tile[32][kAttnTile + 2];  // dim <= 128
   const int bh = blockIdx.y;
   const int key0 = blockIdx.x * 32;
-  const __half* src = v + (static_cast<size_t>(bh) * seq + key0) * kAttnTile;
-  for (int i = threadIdx.x; i < 32 * kAttnTile; i += 256) tile[i / kAttnTile][i % kAttnTile] = src[i];
+  const __half* src = v + (static_cast<size_t>(bh) * seq + key0) * dim;
+  for (int i = threadIdx.x; i < 32 * dim; i += 256) tile[i / dim][i % dim] = src[i];
   __syncthreads();
   if (threadIdx.x < 32) {
     float sum = 0.0f, weighted = 0.0f;
-    for (int d = 0; d < kAttnTile; ++d) {
+    for (int d = 0; d < dim; ++d) {
       float value = __half2float(tile[threadIdx.x][d]);
       sum += value;
-      weighted = __fmaf_rn(static_cast<float>(2 * d - (kAttnTile - 1)), value, weighted);
+      weighted = __fmaf_rn(static_cast<float>(2 * d - (dim - 1)), value, weighted);
     }
     v_sum[static_cast<size_t>(bh) * seq + key0 + threadIdx.x] = sum;
     v_weighted[static_cast<size_t>(bh) * seq + key0 + threadIdx.x] = weighted;
   }
-  for (int i = threadIdx.x; i < 32 * kAttnTile; i += 256) {
+  for (int i = threadIdx.x; i < 32 * dim; i += 256) {
     int d = i / 32, key = i % 32;
-    vt[(static_cast<size_t>(bh) * kAttnTile + d) * seq + key0 + key] = tile[key][d];
+    vt[(static_cast<size_t>(bh) * dim + d) * seq + key0 + key] = tile[key][d];
   }
 }
 
-cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq,
+cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq, int dim,
                                   cudaStream_t stream) {
   dim3 grid(seq / 32, batch_heads);
-  attn_prepare_v_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(v), static_cast<__half*>(vt), v_sum, v_weighted, seq);
+  attn_prepare_v_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(v), static_cast<__half*>(vt), v_sum, v_weighted, seq, dim);
   return cudaGetLastError();
 }
 

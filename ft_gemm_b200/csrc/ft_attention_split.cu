@@ -32,7 +32,7 @@ namespace ftg {
 
 namespace {
 
-constexpr int kTile = 128;             // queries per tile, keys per tile, head dimension
+constexpr int kTile = 128;             // queries per tile, keys per tile; the head dimension kDim is 128 or 64
 constexpr int kQTiles = 2;             // query tiles per CTA
 constexpr int kSlabBytes = 128 * 128;  // 128 rows x 64 FP16 (one 128-byte swizzle row each)
 constexpr int kTileBytes = 2 * kSlabBytes;
@@ -91,6 +91,7 @@ __device__ __forceinline__ void reg_acquire() {
 
 }  // namespace
 
+template <int kDim>
 __global__ void __launch_bounds__(kThreads, 1)
 ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
@@ -146,30 +147,37 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
+  constexpr int kDimSlabs = kDim / 64;          // 128-byte slabs of Q and K rows (64 FP16 each)
+  constexpr int kQKBytes = kDimSlabs * kSlabBytes;
+  constexpr int kVSlabBytes = kDim * 128;       // one slab of V^T: kDim rows x 64 keys
+  constexpr int kHalfDim = kDim / 2;            // output dims per thread of a row
 
   if (group == 0) {
     reg_release<40>();
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------- producer
-      mbar_arrive_expect_tx(&sh.q_full, qtiles * kTileBytes);
+      mbar_arrive_expect_tx(&sh.q_full, qtiles * kQKBytes);
       for (int t = 0; t < qtiles; ++t) {
-        tma_load_2d(smem_q + t * kTileBytes, &tmap_q, &sh.q_full, 0, row_base + q0 + t * kTile);
-        tma_load_2d(smem_q + t * kTileBytes + kSlabBytes, &tmap_q, &sh.q_full, 64, row_base + q0 + t * kTile);
+#pragma unroll
+        for (int sl = 0; sl < kDimSlabs; ++sl) {
+          tma_load_2d(smem_q + t * kTileBytes + sl * kSlabBytes, &tmap_q, &sh.q_full, 64 * sl, row_base + q0 + t * kTile);
+        }
       }
       for (int j = 0; j < cta_tiles; ++j) {
         const uint32_t ph = j & 1;
         if (!mbar_wait_bounded(&sh.k_empty, ph ^ 1, abort_flag, kTimeoutNs)) break;
-        mbar_arrive_expect_tx(&sh.k_full, kTileBytes);
-        tma_load_2d(smem_k, &tmap_k, &sh.k_full, 0, row_base + j * kTile);
-        tma_load_2d(smem_k + kSlabBytes, &tmap_k, &sh.k_full, 64, row_base + j * kTile);
+        mbar_arrive_expect_tx(&sh.k_full, kQKBytes);
+#pragma unroll
+        for (int sl = 0; sl < kDimSlabs; ++sl) tma_load_2d(smem_k + sl * kSlabBytes, &tmap_k, &sh.k_full, 64 * sl, row_base + j * kTile);
         if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kTimeoutNs)) break;
-        mbar_arrive_expect_tx(&sh.v_full, kTileBytes);
-        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kTile, bh * kTile);
-        tma_load_2d(smem_v + kSlabBytes, &tmap_vt, &sh.v_full, j * kTile + 64, bh * kTile);
+        mbar_arrive_expect_tx(&sh.v_full, 2 * kVSlabBytes);
+        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kTile, bh * kDim);
+        tma_load_2d(smem_v + kSlabBytes, &tmap_vt, &sh.v_full, j * kTile + 64, bh * kDim);
       }
     } else if (warp == 1 && lane == 0) {
       // ------------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc = make_idesc_f16_f32(kTile, kTile);
+      constexpr uint32_t idesc_s = make_idesc_f16_f32(kTile, kTile);  // S: 128 queries x 128 keys
+      constexpr uint32_t idesc_o = make_idesc_f16_f32(kTile, kDim);   // O: 128 queries x kDim
       bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kTimeoutNs);
       for (int j = 0; j <= cta_tiles && alive; ++j) {
         if (j < cta_tiles) {  // S_A, S_B = Q_{A,B} K_j^T
@@ -183,10 +191,10 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             }
             tcgen05_fence_after();
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
+            for (int kk = 0; kk < kDim / 16; ++kk) {
               uint64_t da = make_smem_desc_sw128(smem_u32(smem_q + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
               uint64_t db = make_smem_desc_sw128(smem_u32(smem_k + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
-              umma_f16(tmem_base + kTmemS + t * kTile, da, db, idesc, kk != 0 ? 1u : 0u);
+              umma_f16(tmem_base + kTmemS + t * kTile, da, db, idesc_s, kk != 0 ? 1u : 0u);
             }
             umma_commit(&sh.s_full[t]);
           }
@@ -207,7 +215,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             for (int kk = 0; kk < 8; ++kk) {
               uint64_t da = make_smem_desc_sw128(smem_u32(smem_p + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
               uint64_t db = make_smem_desc_sw128(smem_u32(smem_v + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
-              umma_f16(tmem_base + kTmemO + t * kTile, da, db, idesc, (i | kk) != 0 ? 1u : 0u);
+              umma_f16(tmem_base + kTmemO + t * kTile, da, db, idesc_o, (i | kk) != 0 ? 1u : 0u);
             }
             umma_commit(&sh.p_empty[t]);
           }
@@ -236,11 +244,11 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const int q_band = q_tile0 / 64 + pair;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t s_addr = lane_addr + kTmemS + t * kTile + c * 64;  // this half's 64 score columns
-      const uint32_t o_addr = lane_addr + kTmemO + t * kTile + c * 64;  // this half's 64 output dims
+      const uint32_t o_addr = lane_addr + kTmemO + t * kTile + c * kHalfDim;  // this half's output dims
       uint8_t* p_row = smem_p + t * kTileBytes + c * kSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
       const bool fault_here = p.fault_bh == bh && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kTile;
       const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE && (p.fault_index % kTile) / 64 == c;
-      const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_index / 64 == c;
+      const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_index / kHalfDim == c;
       const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
       TileScratch& scratch = sh.scratch[t][c][pair];
 
@@ -356,7 +364,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           tcgen05_fence_after();
           if (__any_sync(0xffffffffU, alpha != 1.0f)) {
 #pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {  // this half's 64 output dims
+            for (int cc = 0; cc < kHalfDim / 32; ++cc) {  // this half's output dims
               float o[32];
               tmem_ld_32x32b_x32(o_addr + cc * 32, o);
               tmem_wait_ld();
@@ -447,17 +455,17 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const bool my_fault = output_fault && fault_row == row_in_tile;
         float actual_sum = 0.0f, actual_weighted = 0.0f;
 #pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < kHalfDim / 32; ++cc) {
           float o[32];
           tmem_ld_32x32b_x32(o_addr + cc * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int dim = c * 64 + cc * 32 + i;
+            const int dim = c * kHalfDim + cc * 32 + i;
             float x = o[i] * inv_l;
             if (my_fault && p.fault_index == dim) x += p.fault_value;
             actual_sum += x;
-            actual_weighted = __fmaf_rn(static_cast<float>(2 * dim - (kTile - 1)), x, actual_weighted);
+            actual_weighted = __fmaf_rn(static_cast<float>(2 * dim - (kDim - 1)), x, actual_weighted);
           }
         }
         sh.final_actual[t][c][row_in_tile] = make_float2(actual_sum, actual_weighted);
@@ -475,23 +483,23 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         if (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted) {  // the same in both threads of the row
           if (fabsf(delta_sum) > thr_sum) {
             const float observed_weight = delta_weighted / delta_sum;
-            const int dim = __float2int_rn(0.5f * (observed_weight + static_cast<float>(kTile - 1)));
-            if (dim >= 0 && dim < kTile && fabsf(observed_weight - static_cast<float>(2 * dim - (kTile - 1))) <= 0.25f) recover_dim = dim;
+            const int dim = __float2int_rn(0.5f * (observed_weight + static_cast<float>(kDim - 1)));
+            if (dim >= 0 && dim < kDim && fabsf(observed_weight - static_cast<float>(2 * dim - (kDim - 1))) <= 0.25f) recover_dim = dim;
           }
           if (c == 0) {  // one of the two threads reports
             atomicAdd(&p.report->pv_detected, 1);
             atomicAdd(recover_dim >= 0 ? &p.report->pv_corrected : &p.report->failed_rows, 1);
           }
         }
-        float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kTile + c * 64;
+        float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kDim + c * kHalfDim;
 #pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < kHalfDim / 32; ++cc) {
           float o[32];
           tmem_ld_32x32b_x32(o_addr + cc * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int dim = c * 64 + cc * 32 + i;
+            const int dim = c * kHalfDim + cc * 32 + i;
             float x = o[i] * inv_l;
             if (my_fault && p.fault_index == dim) x += p.fault_value;
             if (recover_dim == dim) x -= delta_sum;
@@ -524,13 +532,19 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 }
 
 cudaError_t configure_attention_split() {
-  return cudaFuncSetAttribute(ft_attention_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t err = cudaFuncSetAttribute(ft_attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (err != cudaSuccess) return err;
+  return cudaFuncSetAttribute(ft_attention_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
 cudaError_t launch_attention_split(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                                    int batch_heads, cudaStream_t stream) {
   dim3 grid((params.seq + kQTiles * kTile - 1) / (kQTiles * kTile), batch_heads);
-  ft_attention_split_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  if (params.dim == 64) {
+    ft_attention_split_kernel<64><<<grid, kThreads, kSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  } else {
+    ft_attention_split_kernel<128><<<grid, kThreads, kSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+  }
   return cudaGetLastError();
 }
 

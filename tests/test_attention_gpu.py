@@ -131,7 +131,9 @@ def test_repeat_runs_are_bit_identical_and_arguments_checked(ftg):
         op.run(first, (2, 0, 0, 0, 0, 1.0))  # a softmax-stage fault needs a handle prepared with protect_softmax
     op.close()
     with pytest.raises(ftg.FtGemmError):
-        ftg.FtAttention(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous())  # D must be 128
+        ftg.FtAttention(q[..., :96].contiguous(), k[..., :96].contiguous(), v[..., :96].contiguous())  # D must be 64 or 128
+    with pytest.raises(ftg.FtGemmError):  # the softmax-stage protection is built for D = 128
+        ftg.FtAttention(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous(), protect_softmax=True)
 
 
 def test_config5_shape_properties(ftg):
@@ -245,4 +247,38 @@ def test_causal_forward_and_faults(ftg, n):
     rep = op.report()
     assert (rep.softmax_detected, rep.softmax_corrected) == (1, 1)
     assert torch.equal(out, protected)
+    op.close()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("exact_prepare", [False, True])
+def test_head_dim_64(ftg, causal, exact_prepare):
+    """The reference's default head dimension (src/ft_flash_attention_a14.cu:114, 267)."""
+    b, h, n, d = 2, 2, 384, 64
+    q, k, v = _qkv(b, h, n, d=d, seed=41)
+    op = ftg.FtAttention(q, k, v, causal=causal, exact_prepare=exact_prepare)
+    clean = op.new_output()
+    op.run(clean)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    want, stats, _ = oa.forward(_np(q), _np(k), _np(v), causal=causal)
+    assert stats.score_detected == 0
+    np.testing.assert_allclose(_np(clean), want, atol=2e-3, rtol=0)
+    np.testing.assert_allclose(_np(clean), oa.truth_fp64(_np(q), _np(k), _np(v), causal=causal), atol=4e-3, rtol=0)
+    out = op.new_output()
+    for head, query, key, value in [(0, 383, 0, 3.0), (1, 200, 130, -4.0), (0, 64, 63, 6.0)]:
+        fault = (ftg.FAULT_SCORE, 1, head, query, key, value)
+        op.run(out, fault)
+        rep = op.report()
+        _, stats, records = oa.forward(_np(q), _np(k), _np(v), causal=causal, fault=fault)
+        assert (rep.score_detected, rep.score_corrected) == (1, 1) == (stats.score_detected, stats.score_corrected)
+        assert (rep.records[0].tile, rep.records[0].bad_row, rep.records[0].bad_col) == (records[0].tile, query % 64, key % 64)
+        np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
+    for query, dim, value in [(5, 0, 0.5), (300, 63, -1.0), (129, 31, 0.25), (383, 32, 2.0)]:  # both dim halves, both tiles
+        fault = (ftg.FAULT_OUTPUT, 0, 1, query, dim, value)
+        op.run(out, fault)
+        rep = op.report()
+        _, stats, _ = oa.forward(_np(q), _np(k), _np(v), causal=causal, fault=fault)
+        assert (rep.pv_detected, rep.pv_corrected, rep.failed_rows) == (1, 1, 0) == (stats.pv_detected, stats.pv_corrected, stats.failed_rows)
+        np.testing.assert_allclose(_np(out), _np(clean), atol=6e-3, rtol=0)
     op.close()

@@ -106,7 +106,10 @@ def test_attention_program():
     assert rep["fault_target"].startswith("batch=0 head=0 query=256 index=128")  # causal default of a14:261
     rc, _, err = run("ft_flash_attention", "--sequence", 256, "--causal", "--fault-stage", "score", "--fault-query", 10, "--fault-index", 20)
     assert rc == 1 and "must not exceed" in err
-    rc, _, err = run("ft_flash_attention", "--head-dim", 64)
+    rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--head-dim", 64, "--repeat", 1, "--fault-stage",
+                     "output", "--fault-value", 0.5)  # the reference's default head dimension (a14:114)
+    assert rc == 0 and rep["shape"].startswith("B=1 H=2 N=512 D=64") and (rep["pv_detected"], rep["pv_corrected"]) == ("1", "1")
+    rc, _, err = run("ft_flash_attention", "--head-dim", 96)
     assert rc == 1 and "Invalid options" in err
 
 
