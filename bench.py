@@ -302,9 +302,9 @@ def main():
         ta = torch.tensor([start.elapsed_time(stop) / attn_steps], device=device, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(ta, op=dist.ReduceOp.MAX)
-        clean = attn.report()
-        attn.run(out, (ftg.FAULT_SCORE, 0, count // 2, seq // 2 + 1, seq - 96, 12.0))
-        faulty = attn.report()
+        clean = ftg.gather_attention_reports(attn.report(), first, batch_heads, seq, device=device)
+        attn.run(out, (ftg.FAULT_SCORE, 0, count // 2, seq // 2 + 1, seq - 96, 12.0))  # one fault per rank
+        faulty = ftg.gather_attention_reports(attn.report(), first, batch_heads, seq, device=device)
         attention = {"workload": f"ft_attention_fwd B*H={batch_heads} N={seq} D={dim} FP16, non-causal, heads sharded over {world} GPU(s)",
                      "ms": float(ta.item()), "tflops": 4.0 * batch_heads * seq * seq * dim / (float(ta.item()) * 1e-3) / 1e12,
                      "prepare_ms": clean.prepare_ms, "clean": [clean.score_detected, clean.pv_detected, clean.failed_rows],

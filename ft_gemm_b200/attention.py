@@ -84,6 +84,43 @@ def shard_heads(batch_heads: int, rank: int, world: int) -> Tuple[int, int]:
     return rank * base + min(rank, extra), count
 
 
+def gather_attention_reports(report: "AttnReport", first_head: int, heads_per_batch: int, seq: int, group=None,
+                             device=None) -> "AttnReport":
+    """All-gathers the counters of head-sharded runs (the reference reads back one DeviceStats per run,
+    src/ft_flash_attention_a14.cu:1437-1440): counters are added, the noise figure is the maximum, tile ids of the records are
+    re-based from the rank's first (batch, head) pair to the whole [B*H] range.  Without a process group: the local report."""
+    import torch.distributed as dist
+    bands = seq // 64
+    per_head = bands * bands
+    counters = [report.status, report.score_detected, report.score_corrected, report.score_uncorrected, report.pv_detected,
+                report.pv_corrected, report.failed_rows, report.softmax_detected, report.softmax_corrected, report.softmax_replayed]
+    mine = torch.zeros(12 + 8 * 16, dtype=torch.float64)
+    mine[:10] = torch.tensor(counters, dtype=torch.float64)
+    mine[10] = report.max_score_noise
+    mine[11] = len(report.records)
+    for i, r in enumerate(report.records[:16]):
+        mine[12 + 8 * i:20 + 8 * i] = torch.tensor([r.tile + first_head * per_head, r.bad_row_count, r.bad_col_count, r.bad_row, r.bad_col,
+                                                    r.row_delta, r.col_delta, r.corrected], dtype=torch.float64)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        if device is not None:
+            mine = mine.to(device)
+        bufs = [torch.empty_like(mine) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(bufs, mine, group=group)
+        bufs = [b.cpu() for b in bufs]
+    else:
+        bufs = [mine]
+    total = torch.stack(bufs)
+    sums = total[:, :10].sum(dim=0)
+    records = []
+    for b in bufs:
+        for i in range(int(b[11].item())):
+            f = b[12 + 8 * i:20 + 8 * i].tolist()
+            records.append(TileRecord(int(f[0]), int(f[1]), int(f[2]), int(f[3]), int(f[4]), f[5], f[6], int(f[7])))
+    records.sort(key=lambda r: r.tile)
+    status = int(total[:, 0].min().item()) if (total[:, 0] != 0).any() else 0  # any rank's error code (they are negative)
+    return AttnReport(status, *(int(x) for x in sums[1:10].tolist()), float(total[:, 10].max().item()), report.prepare_ms, records[:16])
+
+
 class FtAttention:
     """Prepared fault-tolerant attention forward for one (Q, K, V) triple of [B, H, N, D] FP16 tensors."""
 

@@ -76,3 +76,46 @@ def test_gather_without_process_group_is_local():
     rep = Report(0, 1, 1, 0, 0, 0.5, 1.0, 0.5, 0.5, [TileRecord(3, 1, 1, 2, 2, -1.0, -1.0, 1)])
     total = gather_reports(rep, shard)
     assert (total.bad_tiles, total.corrected_tiles, total.records[0].tile) == (1, 1, 3)
+
+
+def test_shard_heads_partition():
+    from ft_gemm_b200 import shard_heads
+    for total, world in [(128, 8), (128, 3), (5, 2), (7, 7), (1, 1)]:
+        parts = [shard_heads(total, r, world) for r in range(world)]
+        assert parts[0][0] == 0 and sum(c for _, c in parts) == total
+        for (f0, c0), (f1, _) in zip(parts, parts[1:]):
+            assert f0 + c0 == f1
+        assert max(c for _, c in parts) - min(c for _, c in parts) <= 1
+
+
+def _attn_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    from ft_gemm_b200 import AttnReport, TileRecord, gather_attention_reports, shard_heads
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    first, count = shard_heads(6, rank, world)  # 6 (batch, head) pairs over 2 ranks
+    seq = 256  # 4 bands: 16 score tiles per head
+    recs = [TileRecord(tile=5 + rank, bad_row_count=1, bad_col_count=1, bad_row=2, bad_col=3, row_delta=-1.0, col_delta=-1.0, corrected=1)]
+    mine = AttnReport(0, 1, 1, 0, rank, rank, 0, 0, 0, 0, 0.01 * (rank + 1), 0.5, recs)
+    total = gather_attention_reports(mine, first, 3, seq)
+    out.put((rank, total.score_detected, total.score_corrected, total.pv_detected, total.max_score_noise, [r.tile for r in total.records]))
+    dist.destroy_process_group()
+
+
+def test_attention_counters_all_gather_gloo_world2():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_attn_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, detected, corrected, pv, noise, tiles in results:
+        assert (detected, corrected, pv) == (2, 2, 1) and noise == pytest.approx(0.02)
+        assert tiles == [5, 3 * 16 + 6]  # rank 1 owns heads 3..5: its local tile 6 is tile 6 of head 3
