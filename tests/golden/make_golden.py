@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the reference's OWN kernels.
 
 Needs a GPU and the harness binaries oracle/_ref/ref_harness_s0,
-oracle/_ref/ref_harness_s4 and oracle/_ref/ref_harness_gs (built by `make -C oracle ref` where the reference
+oracle/_ref/ref_harness_s4, oracle/_ref/ref_harness_gs and oracle/_ref/ref_harness_a0 (built by `make -C oracle ref` where the reference
 checkout is available; they compile the reference's .cu files in place and launch
 its kernels unmodified).  Usage, on a machine with a GPU:
 
@@ -28,6 +28,11 @@ S0_SCENARIOS = ("clean", "inject", "two_rc", "same_row", "cancel")
 # GEMM + softmax cross-nonlinearity check: (M, N, K, fault_row, fault_col, fault_value)
 GS_CASES = [(64, 64, 64, 32, 32, 1.0), (96, 200, 128, 5, 199, -0.75), (128, 1000, 256, 100, 0, 2.5)]
 GS_PHASES = ("clean", "fault", "recovered")
+# attention (the reference's scalar kernel A0): (B, H, N, D, causal, [(stage, query, index, value), ...]); batch 0, head 0
+A0_CASES = [(1, 2, 256, 128, 0, [(0, 0, 0, 0.0), (1, 128, 128, 1.0), (1, 255, 3, -2.5), (2, 128, 128, 0.25), (3, 128, 128, 0.75),
+                                 (4, 128, 64, 0.5), (4, 7, 127, -1.0)]),
+            (1, 2, 256, 64, 1, [(0, 0, 0, 0.0), (1, 200, 100, 1.5), (4, 200, 32, 0.5), (2, 200, 100, 0.25)]),
+            (2, 1, 384, 128, 1, [(0, 0, 0, 0.0), (1, 383, 0, 3.0), (4, 130, 5, 0.75)])]
 
 
 def _read(path, dtype):
@@ -88,6 +93,20 @@ def run_gs(m, n, k, fault_row, fault_col, fault_value, outdir):
         np.savez_compressed(os.path.join(outdir, f"gs_{m}x{n}x{k}.npz"), **data)
 
 
+def run_a0(batch, heads, seq, dim, causal, scenarios, outdir):
+    with tempfile.TemporaryDirectory() as tmp:
+        args = [os.path.join(REF, "ref_harness_a0"), str(batch), str(heads), str(seq), str(dim), str(causal), tmp]
+        args += [f"{s}:{q}:{i}:{v}" for s, q, i, v in scenarios]
+        subprocess.run(args, check=True)
+        data = {name: _read(os.path.join(tmp, name + ".u8"), np.uint8) for name in ("q", "k", "v")}
+        for n in range(len(scenarios)):
+            data[f"out_{n}"] = _read(os.path.join(tmp, f"out_{n}.f32"), np.float32)
+            data[f"stats_{n}"] = _read(os.path.join(tmp, f"stats_{n}.i32"), np.int32)
+        data["shape"] = np.array([batch, heads, seq, dim, causal], dtype=np.int32)
+        data["scenarios"] = np.array(scenarios, dtype=np.float64)
+        np.savez_compressed(os.path.join(outdir, f"a0_{batch}x{heads}x{seq}x{dim}_c{causal}.npz"), **data)
+
+
 def main():
     outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(outdir, exist_ok=True)
@@ -97,6 +116,8 @@ def main():
         run_s0(*case, outdir)
     for case in GS_CASES:
         run_gs(*case, outdir)
+    for case in A0_CASES:
+        run_a0(*case, outdir)
     print("golden fixtures written to", outdir, sorted(os.listdir(outdir)))
 
 
