@@ -15,12 +15,17 @@
  *     carried through the recurrence (a0:585-611), compare, locate by the ratio of
  *     the deltas, correct or count a failed row (a0:613-662).
  *
- * Parity status of this part: UNPINNED.  The reference's attention programs take
- * FP8 inputs and protect the score stage with per-row projections; the FP16 inputs
- * and the 2-D tile checksums used here are the variant this build was asked for,
- * so no output of the reference can be compared bit for bit.  The GEMM checker it
- * reuses is pinned (tests/test_golden_cpu.py); the attention values are checked
- * against an FP64 softmax(QK^T/sqrt(D))V in the tests.
+ * Parity status of this part: PINNED WITHIN TOLERANCE against the reference's own
+ * scalar attention kernel (src/ft_flash_attention_a0.cu:285-667), run unmodified on a
+ * B200 by oracle/ref_harness_a0.cu; fixtures tests/golden/a0_*.npz (head dimensions
+ * 128 and 64, causal and not, every fault stage).  Inputs agree bit for bit (the
+ * reference's grid values are exact in FP16), outputs within 2e-3 (FP16
+ * probabilities here, FP32 there) for clean runs and for every recovered fault, the
+ * per-stage counters are equal.  A bit-for-bit comparison is not possible: the
+ * reference's attention programs take FP8 inputs and protect the score stage with
+ * per-row projections, while the FP16 inputs and the 2-D tile checksums used here
+ * are the variant this build was asked for.  The GEMM checker it reuses is pinned bit
+ * for bit (tests/test_golden_cpu.py).
  */
 #include <math.h>
 #include <stdint.h>

@@ -38,21 +38,27 @@ def test_oracle_against_reference_a0(path):
         np.testing.assert_array_equal(t.ravel()[:4096], grid_values(4096, seed))
     q16, k16, v16 = (t.astype(np.float16) for t in (q, k, v))
     assert all((t16.astype(np.float32) == t).all() for t16, t in ((q16, q), (k16, k), (v16, v)))  # exact in FP16
-    clean = None
+    clean = mine_clean = None
     for i, (stage, query, index, value) in enumerate(g["scenarios"]):
         stage, query, index = int(stage), int(query), int(index)
-        ref_out = g[f"out_{i}"].reshape(shape)
         ref = dict(zip(STATS, (int(x) for x in g[f"stats_{i}"])))
         fault = None if stage == 0 else (stage, 0, 0, query, index, float(value))
         out, stats, _ = oa.forward(q16, k16, v16, causal=bool(causal), protect_softmax=stage in (2, 3), fault=fault)
-        np.testing.assert_allclose(out, ref_out, atol=2e-3, rtol=0, err_msg=f"scenario {i}")
         assert ref["failed_rows"] == 0 == stats.failed_rows
-        if stage == 0:
-            clean = ref_out
+        if stage == 0:  # the reference's clean output in full (stored as FP16)
+            clean = g[f"out_{i}"].astype(np.float32).reshape(shape)
+            np.testing.assert_allclose(out, clean, atol=2e-3, rtol=0)
+            mine_clean = out
             assert all(x == 0 for x in ref.values())
             assert (stats.score_detected, stats.pv_detected, stats.softmax_detected) == (0, 0, 0)
             continue
-        np.testing.assert_allclose(ref_out, clean, atol=2e-3, rtol=0)  # the reference recovered as well
+        # of a fault scenario the fixture holds the faulty query's row and how far any other row moved (nowhere)
+        np.testing.assert_allclose(out[0, 0, query], g[f"row_{i}"], atol=2e-3, rtol=0, err_msg=f"scenario {i}")
+        np.testing.assert_allclose(g[f"row_{i}"], clean[0, 0, query], atol=2e-3, rtol=0)  # the reference recovered as well
+        assert float(g[f"others_{i}"]) == 0.0
+        rest = np.abs(out - mine_clean)
+        rest[0, 0, query] = 0.0
+        assert rest.max() < 1e-6
         if stage == 1:
             assert (ref["score_detected"], ref["score_corrected"] + ref["score_replayed"]) == (1, 1)
             assert (stats.score_detected, stats.score_corrected) == (1, 1)

@@ -282,3 +282,50 @@ def test_head_dim_64(ftg, causal, exact_prepare):
         assert (rep.pv_detected, rep.pv_corrected, rep.failed_rows) == (1, 1, 0) == (stats.pv_detected, stats.pv_corrected, stats.failed_rows)
         np.testing.assert_allclose(_np(out), _np(clean), atol=6e-3, rtol=0)
     op.close()
+
+
+def test_against_reference_a0_fixtures(ftg):
+    """The CUDA path on the inputs of the reference's own scalar attention kernel (tests/golden/a0_*.npz): outputs within
+    2e-3 of the reference's, the same stage counters for every fault scenario."""
+    import glob
+    import os
+    from tests import oracle_lib
+    oracle = oracle_lib.load()
+    paths = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "a0_*.npz")))
+    assert paths
+    for path in paths:
+        g = np.load(path)
+        b, h, n, d, causal = (int(x) for x in g["shape"])
+        q, k, v = (torch.from_numpy(oracle.decode(g[name]).reshape(b, h, n, d)).to(torch.float16).cuda() for name in ("q", "k", "v"))
+        ops = {False: ftg.FtAttention(q, k, v, causal=bool(causal))}
+        if d == 128:
+            ops[True] = ftg.FtAttention(q, k, v, causal=bool(causal), protect_softmax=True)
+        out = ops[False].new_output()
+        clean = None
+        for i, (stage, query, index, value) in enumerate(g["scenarios"]):
+            stage, query, index = int(stage), int(query), int(index)
+            protect = stage in (2, 3)
+            if protect and d != 128:
+                continue
+            op = ops[protect]
+            op.run(out, None if stage == 0 else (stage, 0, 0, query, index, float(value)))
+            rep = op.report()
+            ref = [int(x) for x in g[f"stats_{i}"]]  # score d/c/replayed, softmax d/c/r, pv d/c, failed rows (a0:35-45)
+            assert rep.failed_rows == 0 == ref[8]
+            if stage == 0:
+                clean = g[f"out_{i}"].astype(np.float32).reshape(b, h, n, d)
+                np.testing.assert_allclose(_np(out), clean, atol=2e-3, rtol=0)
+                assert (rep.score_detected, rep.pv_detected, rep.softmax_detected) == (0, 0, 0)
+                continue
+            np.testing.assert_allclose(_np(out)[0, 0, query], g[f"row_{i}"], atol=2e-3, rtol=0)
+            np.testing.assert_allclose(_np(out), clean, atol=2e-3, rtol=0)
+            if stage == 1:
+                assert (rep.score_detected, rep.score_corrected) == (1, 1) == (ref[0], ref[1] + ref[2])
+            elif stage == 2:
+                assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 1, 0) == (ref[3], ref[4], ref[5])
+            elif stage == 3:
+                assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 0, 1) == (ref[3], ref[4], ref[5])
+            else:
+                assert (rep.pv_detected, rep.pv_corrected) == (1, 1) == (ref[6], ref[7])
+        for op in ops.values():
+            op.close()
