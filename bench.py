@@ -252,6 +252,29 @@ def main():
     kernel_ms = elapsed_ms / args.steps  # one kernel launch per step, back to back on one stream
     per_gpu = 2.0 * m_rank * n * k / (kernel_ms * 1e-3) / 1e12
 
+    # ---- A changes on every call (activations of a projection): fused BF16 -> FP8 producer with its band sums, the A-side
+    # of the cache on the tensor cores, then the GEMM; B's band sums and digit planes are reused ----
+    fresh_a = None
+    if rank == 0:
+        src = (torch.randn((m_rank, k), device=device, dtype=torch.float32)).to(torch.bfloat16)
+        for _ in range(3):
+            op.quantize_a(src, 1.0)
+            op.run(c)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            op.quantize_a(src, 1.0)
+            op.run(c)
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+        rep_q = op.report()
+        fresh_a = {"ms_per_call": ms, "tflops": 2.0 * m_rank * n * k / (ms * 1e-3) / 1e12, "bad_tiles": rep_q.bad_tiles,
+                   "note": "per call: quantize A from BF16 with band sums, A-side expected checksums, fused GEMM"}
+        a.copy_(ftg.generate_fp8((m_rank, k), (SEED_A + shard.row_begin * k) & 0xFFFFFFFF, "normal"))  # the A of the other legs again
+        op.refresh(True, False)
+        del src
+
     # ---- end to end through the host-buffer entry point: H2D of A and B, run, D2H of C, report (+ all-gather) ----
     e2e = None
     if not args.no_e2e:
@@ -364,6 +387,8 @@ def main():
             line["e2e"] = e2e
         if attention is not None:
             line["attention"] = attention
+        if fresh_a is not None:
+            line["fresh_a_per_call"] = fresh_a
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = {k_: v for k_, v in cpu_baseline(2048).items() if k_ not in ("seconds", "prepare_seconds")}
         print(json.dumps(line))
