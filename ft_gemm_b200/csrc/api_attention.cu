@@ -56,7 +56,9 @@ int make_f16_map(CUtensorMap* map, const void* base, size_t rows, size_t cols, u
 }  // namespace
 
 struct ft_attn_handle {
-  int batch = 0, heads = 0, seq = 0, dim = 0;
+  int batch = 0, heads = 0, seq = 0, dim = 0;  // seq: rounded up to whole 128-row tiles
+  int valid_seq = 0;                           // the caller's sequence length
+  void* padded[3] = {nullptr, nullptr, nullptr};  // zero-padded copies of Q, K, V when valid_seq != seq
   ft_attn_options options{};
   const void *q = nullptr, *k = nullptr, *v = nullptr;
   void* vt = nullptr;
@@ -97,6 +99,7 @@ int ft_attention_fp16_abft_destroy(ft_attn_handle* h) {
   if (h == nullptr) return FT_OK;
   cudaStreamSynchronize(h->last_stream);
   cudaFree(h->vt);
+  for (void* buffer : h->padded) cudaFree(buffer);
   cudaFree(h->planes);
   cudaFree(h->prepare_status);
   cudaFree(h->cache);
@@ -111,12 +114,16 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
                                    int head_dim, const ft_attn_options* options, void* stream_ptr) {
   if (handle == nullptr || q == nullptr || k == nullptr || v == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or operand pointer");
   *handle = nullptr;
-  if (batch <= 0 || heads <= 0 || seq <= 0 || seq % 128 != 0 || (head_dim != 128 && head_dim != 64)) {
+  if (batch <= 0 || heads <= 0 || seq <= 0 || (head_dim != 128 && head_dim != 64)) {
     return noalloc_fail(FT_ERR_INVALID,
-                        "Invalid options. Require head_dim 64 or 128 (src/ft_flash_attention_a14.cu:267), sequence %% 128 == 0 and positive "
-                        "batch/heads (got B=%d H=%d N=%d D=%d).",
+                        "Invalid options. Require head_dim 64 or 128 (src/ft_flash_attention_a14.cu:267) and positive batch, heads and "
+                        "sequence (got B=%d H=%d N=%d D=%d).",
                         batch, heads, seq, head_dim);
   }
+  // Any sequence length, as in the reference (a14:708, 893 mask by index): the kernels work on whole 128-row tiles, so for
+  // other lengths the handle keeps zero-padded copies of Q, K and V; padded keys are masked, padded queries not stored.
+  const int valid_seq = seq;
+  seq = (seq + 127) / 128 * 128;
   if (head_dim == 64 && options != nullptr && options->protect_softmax != 0) {
     return noalloc_fail(FT_ERR_UNSUPPORTED, "the softmax-stage protection is built for head_dim 128 only");
   }
@@ -145,6 +152,28 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   h->seq = seq;
   h->dim = head_dim;
   h->options = opts;
+  h->valid_seq = valid_seq;
+  if (valid_seq != seq) {
+    const size_t pad_bytes = static_cast<size_t>(batch) * heads * seq * head_dim * 2;
+    const size_t src_pitch = static_cast<size_t>(valid_seq) * head_dim * 2, dst_pitch = static_cast<size_t>(seq) * head_dim * 2;
+    cudaStream_t copy_stream = static_cast<cudaStream_t>(stream_ptr);
+    const void* sources[3] = {q, k, v};
+    for (int i = 0; i < 3; ++i) {
+      cudaError_t perr = cudaMalloc(&h->padded[i], pad_bytes);
+      if (perr == cudaSuccess) perr = cudaMemsetAsync(h->padded[i], 0, pad_bytes, copy_stream);
+      if (perr == cudaSuccess) {
+        perr = cudaMemcpy2DAsync(h->padded[i], dst_pitch, sources[i], src_pitch, src_pitch, static_cast<size_t>(batch) * heads,
+                                 cudaMemcpyDeviceToDevice, copy_stream);
+      }
+      if (perr != cudaSuccess) {
+        ft_attention_fp16_abft_destroy(h);
+        return noalloc_fail(FT_ERR_CUDA, "making the padded copies of Q, K, V failed: %s", cudaGetErrorString(perr));
+      }
+    }
+    q = h->padded[0];
+    k = h->padded[1];
+    v = h->padded[2];
+  }
   h->q = q;
   h->k = k;
   h->v = v;
@@ -257,6 +286,7 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   params.out = out;
   params.report = h->report;
   params.seq = h->seq;
+  params.valid_seq = h->valid_seq;
   params.dim = h->dim;
   params.score_abs_tol = h->options.score_abs_tol;
   params.score_rel_tol = h->options.score_rel_tol;
@@ -277,9 +307,9 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
     if (softmax_stage && h->options.protect_softmax == 0) {
       return noalloc_fail(FT_ERR_INVALID, "the softmax stages can be targeted only by a handle prepared with protect_softmax");
     }
-    int limit = fault->stage == FT_ATTN_FAULT_OUTPUT ? h->dim : h->seq;
+    int limit = fault->stage == FT_ATTN_FAULT_OUTPUT ? h->dim : h->valid_seq;
     if (fault->batch < 0 || fault->batch >= h->batch || fault->head < 0 || fault->head >= h->heads || fault->query < 0 ||
-        fault->query >= h->seq || fault->index < 0 || fault->index >= limit) {
+        fault->query >= h->valid_seq || fault->index < 0 || fault->index >= limit) {
       return noalloc_fail(FT_ERR_INVALID, "fault target is outside the tensor");
     }
     if (h->options.causal != 0 && fault->stage != FT_ATTN_FAULT_OUTPUT && fault->index > fault->query) {

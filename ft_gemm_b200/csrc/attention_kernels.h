@@ -32,7 +32,8 @@ struct AttnParams {
   const float* v_weighted;  // [B*H][N]
   float* out;               // [B*H][N][D]
   AttnDeviceReport* report;
-  int seq;
+  int seq;        // keys and queries per head as the kernels see them: a multiple of 128
+  int valid_seq;  // the caller's sequence length (<= seq): keys past it are masked, queries past it are not stored
   int dim;  // head dimension: 128, or 64 (split-row kernel only)
   float score_abs_tol, score_rel_tol, pv_abs_tol, pv_rel_tol, softmax_abs_tol, softmax_rel_tol;
   int protect_softmax;

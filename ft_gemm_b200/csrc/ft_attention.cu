@@ -353,7 +353,13 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const int my_tiles = tiles_of(t);
       for (int j = 0; j < my_tiles; ++j) {
         const int buf = j & 1;
-        const bool diagonal = causal && j == first_qtile + t;  // keys beyond the query are masked in this tile
+        // Keys of this tile the row may attend to are those with local index <= key_limit: all 128, up to the query in
+        // the causal diagonal tile (src/ft_flash_attention_a14.cu:893), up to the last real key in the last tile of a
+        // sequence that was padded to whole tiles.
+        int key_limit = kAttnTile - 1;
+        if (causal && j == first_qtile + t) key_limit = row_in_tile;
+        if ((j + 1) * kAttnTile > p.valid_seq) key_limit = min(key_limit, p.valid_seq - 1 - j * kAttnTile);
+        const bool diagonal = key_limit < kAttnTile - 1;  // some keys of this tile are masked for this row
         // per-key sums of V for this tile (read in pass 2; published by the barrier inside the wait below)
         sh.v_meta[t][buf][tg] = make_float2(__ldg(p.v_sum + static_cast<size_t>(bh) * seq + j * kAttnTile + tg),
                                             __ldg(p.v_weighted + static_cast<size_t>(bh) * seq + j * kAttnTile + tg));
@@ -396,8 +402,8 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
-              if (i > row_in_tile) v0[i] = -INFINITY;
-              if (64 + i > row_in_tile) v1[i] = -INFINITY;
+              if (i > key_limit) v0[i] = -INFINITY;
+              if (64 + i > key_limit) v1[i] = -INFINITY;
             }
           }
 #pragma unroll
@@ -416,7 +422,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (diagonal) {
 #pragma unroll
               for (int i = 0; i < 64; ++i) {
-                if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+                if (c * 64 + i > key_limit) v[i] = -INFINITY;
               }
             }
 #pragma unroll
@@ -459,7 +465,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              if (!diagonal || c * 32 + i <= row_in_tile) row_max = fmaxf(row_max, v[i]);
+              if (!diagonal || c * 32 + i <= key_limit) row_max = fmaxf(row_max, v[i]);
             }
           }
         }
@@ -523,7 +529,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (diagonal) {  // exp2(-inf) = 0: a masked key gets probability zero in every copy below
 #pragma unroll
               for (int i = 0; i < 64; ++i) {
-                if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+                if (c * 64 + i > key_limit) v[i] = -INFINITY;
               }
             }
             if (!kProtect && c == 1) {  // both halves are in registers: the score buffer can take S of the next key tile
@@ -671,7 +677,8 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         const float thr_sum = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_sum)), p.pv_abs_tol);
         const float thr_weighted = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_weighted)), p.pv_abs_tol);
         int recover_dim = -1;
-        if (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted) {
+        const bool real_row = query < p.valid_seq;  // rows that only pad the sequence to whole tiles are neither checked nor stored
+        if (real_row && (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted)) {
           atomicAdd(&p.report->pv_detected, 1);
           if (fabsf(delta_sum) > thr_sum) {
             const float observed_weight = delta_weighted / delta_sum;
@@ -683,7 +690,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           }
           if (recover_dim < 0) atomicAdd(&p.report->failed_rows, 1);
         }
-        float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kAttnTile;
+        float* out_row = p.out + (static_cast<size_t>(bh) * p.valid_seq + query) * kAttnTile;
 #pragma unroll 1
         for (int cc = 0; cc < 4; ++cc) {
           float o[32];
@@ -696,9 +703,11 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (recover_dim == cc * 32 + i) x -= delta_sum;
             o[i] = x;
           }
+          if (real_row) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+            for (int i = 0; i < 32; i += 4) {
+              __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+            }
           }
         }
       }

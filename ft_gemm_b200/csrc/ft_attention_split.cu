@@ -259,7 +259,13 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       bool drain_skip_first = false;  // ... unless that tile's two barriers were already passed
       for (int j = 0; j < my_tiles; ++j) {
         const int buf = j & 1;
-        const bool diagonal = causal && j == first_qtile + t;  // keys beyond the query are masked in this tile
+        // Keys of this tile the row may attend to are those with local index <= key_limit: all 128, up to the query in
+        // the causal diagonal tile (src/ft_flash_attention_a14.cu:893), up to the last real key in the last tile of a
+        // sequence that was padded to whole tiles.
+        int key_limit = kTile - 1;
+        if (causal && j == first_qtile + t) key_limit = row_in_tile;
+        if ((j + 1) * kTile > p.valid_seq) key_limit = min(key_limit, p.valid_seq - 1 - j * kTile);
+        const bool diagonal = key_limit < kTile - 1;  // some keys of this tile are masked for this row
         // per-key sums of V for this half's 64 keys (read in pass 2; published by the 256-thread barrier of the exchange)
         if (tg < 64) {
           const size_t key = static_cast<size_t>(bh) * seq + j * kTile + c * 64 + tg;
@@ -298,7 +304,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
-              if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+              if (c * 64 + i > key_limit) v[i] = -INFINITY;
             }
           }
 #pragma unroll
@@ -321,7 +327,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
                 tmem_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                  if (!diagonal || c * 64 + cc * 32 + i <= row_in_tile) local_max = fmaxf(local_max, v[i]);
+                  if (!diagonal || c * 64 + cc * 32 + i <= key_limit) local_max = fmaxf(local_max, v[i]);
                 }
               }
             }
@@ -387,7 +393,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           if (diagonal) {  // exp2(-inf) = 0: a masked key gets probability zero
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
-              if (c * 64 + i > row_in_tile) v[i] = -INFINITY;
+              if (c * 64 + i > key_limit) v[i] = -INFINITY;
             }
           }
           // two scores per instruction where the arithmetic allows it (packed FP32 pairs)
@@ -480,7 +486,8 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const float thr_sum = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_sum)), p.pv_abs_tol);
         const float thr_weighted = __fmaf_rn(p.pv_rel_tol, fmaxf(1.0f, fabsf(expected_weighted)), p.pv_abs_tol);
         int recover_dim = -1;
-        if (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted) {  // the same in both threads of the row
+        const bool real_row = query < p.valid_seq;  // rows that only pad the sequence to whole tiles are neither checked nor stored
+        if (real_row && (fabsf(delta_sum) > thr_sum || fabsf(delta_weighted) > thr_weighted)) {  // the same in both threads of the row
           if (fabsf(delta_sum) > thr_sum) {
             const float observed_weight = delta_weighted / delta_sum;
             const int dim = __float2int_rn(0.5f * (observed_weight + static_cast<float>(kDim - 1)));
@@ -491,7 +498,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             atomicAdd(recover_dim >= 0 ? &p.report->pv_corrected : &p.report->failed_rows, 1);
           }
         }
-        float* out_row = p.out + (static_cast<size_t>(row_base) + query) * kDim + c * kHalfDim;
+        float* out_row = p.out + (static_cast<size_t>(bh) * p.valid_seq + query) * kDim + c * kHalfDim;
 #pragma unroll 1
         for (int cc = 0; cc < kHalfDim / 32; ++cc) {
           float o[32];
@@ -505,9 +512,11 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             if (recover_dim == dim) x -= delta_sum;
             o[i] = x;
           }
+          if (real_row) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+            for (int i = 0; i < 32; i += 4) {
+              __stcs(reinterpret_cast<float4*>(out_row + cc * 32 + i), make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+            }
           }
         }
       }

@@ -9,10 +9,12 @@
  * nine counters back (DeviceStats, a14:98-108).  The entry points below are that
  * launch interface.
  *
- * Operator: O[b,h,q,:] = softmax(Q K^T / sqrt(D)) V, non-causal, for
+ * Operator: O[b,h,q,:] = softmax(Q K^T / sqrt(D)) V, causal (ft_attn_options.causal,
+ * a14:708, 893) or not, for
  *   Q, K, V  [B, H, N, D]  FP16, D contiguous       (the reference uses FP8 E4M3)
  *   O        [B, H, N, D]  FP32
- *   D == 128, N % 128 == 0
+ *   D == 64 or 128 (a14:267), any N >= 1 (the handle keeps zero-padded copies of
+ *   Q, K, V when N is not a multiple of the 128-row tile; O keeps the caller's N)
  * Protection:
  *   - score stage: every 64x64 tile of S = Q K^T is checked with the SAME row /
  *     column checksum verifier as the GEMM (expected_row = Q rowsum(K-tile),

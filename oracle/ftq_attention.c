@@ -135,10 +135,14 @@ static void band_sums_f32(const float* x, int rows, int d, float* sums, float* m
  * (src/ft_flash_attention_a14.cu:964-1099): verifier probabilities, the moments
  * sum p, sum w p, sum w^2 p of the FP16-rounded probabilities, single-point
  * replacement or replay of the row, and a duplicate of the running state.
+ * seq is a multiple of 128; valid_seq <= seq is the real sequence length: the rows
+ * valid_seq..seq-1 of q, k, v are zero padding, their keys are masked like the
+ * causal ones (a14:893 masks by index) and their queries leave no output row and
+ * no output-stage counters; out is [batch_heads, valid_seq, dim].
  * records (may be NULL): score tiles whose checker fired, tile id =
  * ((bh * N/64) + q_band) * N/64 + key_band, sorted by tile id.
  */
-void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint16_t* v16, int batch_heads, int seq, int dim,
+void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint16_t* v16, int batch_heads, int seq, int valid_seq, int dim,
                            float score_abs, float score_rel, float pv_abs, float pv_rel, float softmax_abs, float softmax_rel,
                            int protect_softmax, int causal, int fault_stage, int fault_bh,
                            int fault_query, int fault_index, float fault_value, float* out, ftq_attn_stats* stats,
@@ -269,6 +273,10 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
           for (int r = 0; r < 64; ++r)
             for (int c = 0; c < 128; ++c)
               if (j * 128 + c > qb * 64 + r) s[r * 128 + c] = -INFINITY;
+        if ((j + 1) * 128 > valid_seq)
+          for (int r = 0; r < 64; ++r)
+            for (int c = 0; c < 128; ++c)
+              if (j * 128 + c >= valid_seq) s[r * 128 + c] = -INFINITY;
         /* online softmax, FP16 probabilities, P V and the expected projections */
         for (int r = 0; r < 64; ++r) {
           float row_max = -INFINITY;
@@ -363,6 +371,7 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
       /* output stage (a0:613-662) */
       for (int r = 0; r < 64; ++r) {
         int query = qb * 64 + r;
+        if (query >= valid_seq) continue;
         float inv_l = 1.0f / l_run[r];
         float* o = acc + (size_t)r * dim;
         float actual_sum = 0.0f, actual_weighted = 0.0f;
@@ -390,7 +399,7 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
             ++failed_rows;
           }
         }
-        memcpy(out + head + (size_t)query * dim, o, (size_t)dim * sizeof(float));
+        memcpy(out + (size_t)bh * valid_seq * dim + (size_t)query * dim, o, (size_t)dim * sizeof(float));
       }
     }
     free(qf);

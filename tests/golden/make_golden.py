@@ -32,7 +32,10 @@ GS_PHASES = ("clean", "fault", "recovered")
 A0_CASES = [(1, 2, 256, 128, 0, [(0, 0, 0, 0.0), (1, 128, 128, 1.0), (1, 255, 3, -2.5), (2, 128, 128, 0.25), (3, 128, 128, 0.75),
                                  (4, 128, 64, 0.5), (4, 7, 127, -1.0)]),
             (1, 2, 256, 64, 1, [(0, 0, 0, 0.0), (1, 200, 100, 1.5), (4, 200, 32, 0.5), (2, 200, 100, 0.25)]),
-            (2, 1, 384, 128, 1, [(0, 0, 0, 0.0), (1, 383, 0, 3.0), (4, 130, 5, 0.75)])]
+            (2, 1, 384, 128, 1, [(0, 0, 0, 0.0), (1, 383, 0, 3.0), (4, 130, 5, 0.75)]),
+            # sequence lengths that are not whole tiles
+            (1, 2, 200, 128, 0, [(0, 0, 0, 0.0), (1, 199, 150, 2.0), (4, 199, 64, 0.5), (2, 130, 199, 0.25), (3, 64, 10, 0.75)]),
+            (1, 2, 333, 64, 1, [(0, 0, 0, 0.0), (1, 332, 300, 1.5), (4, 260, 10, 0.5)])]
 
 
 def _read(path, dtype):
@@ -118,15 +121,12 @@ def run_a0(batch, heads, seq, dim, causal, scenarios, outdir):
 
 def main():
     outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
+    only = sys.argv[2].split(",") if len(sys.argv) > 2 else ["s4", "s0", "gs", "a0"]  # optional: which families to regenerate
     os.makedirs(outdir, exist_ok=True)
-    for case in S4_CASES:
-        run_s4(*case, outdir)
-    for case in S0_CASES:
-        run_s0(*case, outdir)
-    for case in GS_CASES:
-        run_gs(*case, outdir)
-    for case in A0_CASES:
-        run_a0(*case, outdir)
+    for family, cases, run in (("s4", S4_CASES, run_s4), ("s0", S0_CASES, run_s0), ("gs", GS_CASES, run_gs), ("a0", A0_CASES, run_a0)):
+        if family in only:
+            for case in cases:
+                run(*case, outdir)
     print("golden fixtures written to", outdir, sorted(os.listdir(outdir)))
 
 

@@ -16,19 +16,22 @@ class AttnStats(ctypes.Structure):
 
 def forward(q, k, v, score_abs=1e-2, score_rel=2e-5, pv_abs=2e-3, pv_rel=2e-3, fault=None, max_records=64, protect_softmax=False,
             softmax_abs=2e-5, softmax_rel=2e-5, causal=False):
-    """q, k, v: numpy float16 arrays [B, H, N, D].  fault = (stage, batch, head, query, index, value).
-    Returns (out float32 [B,H,N,D], stats, records)."""
+    """q, k, v: numpy float16 arrays [B, H, N, D], any N (zero-padded here to whole 128-row tiles).
+    fault = (stage, batch, head, query, index, value).  Returns (out float32 [B,H,N,D], stats, records)."""
     lib = oracle_lib.load().lib
-    b, h, n, d = q.shape
+    b, h, valid, d = q.shape
+    n = (valid + 127) // 128 * 128
+    if n != valid:
+        q, k, v = (np.pad(np.asarray(x, dtype=np.float16), ((0, 0), (0, 0), (0, n - valid), (0, 0))) for x in (q, k, v))
     q16 = np.ascontiguousarray(q, dtype=np.float16).view(np.uint16)
     k16 = np.ascontiguousarray(k, dtype=np.float16).view(np.uint16)
     v16 = np.ascontiguousarray(v, dtype=np.float16).view(np.uint16)
-    out = np.empty((b, h, n, d), dtype=np.float32)
+    out = np.empty((b, h, valid, d), dtype=np.float32)
     stats = AttnStats()
     records = (oracle_lib.TileRecord * max_records)()
     stage, fb, fh, fq, fi, fv = fault if fault is not None else (0, 0, 0, 0, 0, 0.0)
     ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
-    lib.ftq_attention_forward(ptr(q16), ptr(k16), ptr(v16), b * h, n, d, ctypes.c_float(score_abs), ctypes.c_float(score_rel),
+    lib.ftq_attention_forward(ptr(q16), ptr(k16), ptr(v16), b * h, n, valid, d, ctypes.c_float(score_abs), ctypes.c_float(score_rel),
                               ctypes.c_float(pv_abs), ctypes.c_float(pv_rel), ctypes.c_float(softmax_abs), ctypes.c_float(softmax_rel),
                               int(bool(protect_softmax)), int(bool(causal)), int(stage), int(fb * h + fh), int(fq), int(fi),
                               ctypes.c_float(fv), ptr(out), ctypes.byref(stats), records, max_records)

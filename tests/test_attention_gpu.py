@@ -284,6 +284,50 @@ def test_head_dim_64(ftg, causal, exact_prepare):
     op.close()
 
 
+@pytest.mark.parametrize("n,d,causal", [(200, 128, False), (333, 64, True), (1, 64, False), (129, 128, True), (2100, 128, False),
+                                        (77, 128, True)])
+def test_sequence_lengths_that_are_not_whole_tiles(ftg, n, d, causal):
+    """Any sequence length (the reference masks by index, src/ft_flash_attention_a14.cu:893): the handle pads Q, K, V to whole
+    tiles, padded keys carry no weight, padded queries leave no output row and no counters."""
+    b, h = 1, 2
+    q, k, v = _qkv(b, h, n, d=d, seed=70 + n)
+    op = ftg.FtAttention(q, k, v, causal=causal)
+    guard = torch.full((b, h, n + 1, d), 7.0, device="cuda")  # one spare row per head pair: nothing may be written past N
+    out = guard.view(-1)[: b * h * n * d].view(b, h, n, d)
+    op.run(out)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    assert torch.all(guard.view(-1)[b * h * n * d:] == 7.0)
+    want, stats, _ = oa.forward(_np(q), _np(k), _np(v), causal=causal)
+    np.testing.assert_allclose(_np(out), want, atol=2e-3, rtol=0)
+    np.testing.assert_allclose(_np(out), oa.truth_fp64(_np(q), _np(k), _np(v), causal=causal), atol=4e-3, rtol=0)
+    clean = out.clone()
+    last = n - 1
+    key = last if causal else max(0, n - 3)
+    fault = (ftg.FAULT_SCORE, 0, 1, last, key // 2 if causal else key, 3.0)
+    op.run(out, fault)
+    rep = op.report()
+    _, stats, records = oa.forward(_np(q), _np(k), _np(v), causal=causal, fault=fault)
+    assert (rep.score_detected, rep.score_corrected) == (1, 1) == (stats.score_detected, stats.score_corrected)
+    assert (rep.records[0].tile, rep.records[0].bad_row, rep.records[0].bad_col) == (records[0].tile, records[0].bad_row, records[0].bad_col)
+    np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
+    fault = (ftg.FAULT_OUTPUT, 0, 0, last, d - 1, 0.5)
+    op.run(out, fault)
+    rep = op.report()
+    assert (rep.pv_detected, rep.pv_corrected, rep.failed_rows) == (1, 1, 0)
+    np.testing.assert_allclose(_np(out), _np(clean), atol=6e-3, rtol=0)
+    with pytest.raises(ftg.FtGemmError):
+        op.run(out, (ftg.FAULT_SCORE, 0, 0, n, 0, 1.0))  # a query in the padding
+    op.close()
+    if d == 128:
+        op = ftg.FtAttention(q, k, v, causal=causal, protect_softmax=True)
+        op.run(out, (2, 0, 0, last, key // 2 if causal else key, 0.25))
+        rep = op.report()
+        assert (rep.softmax_detected, rep.softmax_corrected) == (1, 1)
+        np.testing.assert_allclose(_np(out), _np(clean), atol=1e-5, rtol=0)
+        op.close()
+
+
 def test_against_reference_a0_fixtures(ftg):
     """The CUDA path on the inputs of the reference's own scalar attention kernel (tests/golden/a0_*.npz): outputs within
     2e-3 of the reference's, the same stage counters for every fault scenario."""

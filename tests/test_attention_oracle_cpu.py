@@ -112,3 +112,26 @@ def test_causal_forward():
     np.testing.assert_allclose(got, out, atol=1e-6, rtol=0)
     got, stats, _ = oa.forward(q, k, v, causal=True, fault=(4, 0, 1, 50, 99, 0.75))
     assert (stats.pv_detected, stats.pv_corrected, stats.failed_rows) == (1, 1, 0)
+
+
+def test_sequence_lengths_that_are_not_whole_tiles():
+    """Any sequence length (the reference masks by index, src/ft_flash_attention_a14.cu:893): padded keys carry no weight,
+    padded queries leave no row, and faults near the ragged edge are still located."""
+    for n, d, causal in [(200, 128, False), (333, 64, True), (1, 64, False), (129, 128, True)]:
+        q, k, v = _qkv(1, 2, n, d, seed=50 + n)
+        out, stats, records = oa.forward(q, k, v, causal=causal)
+        assert out.shape == (1, 2, n, d)
+        assert (stats.score_detected, stats.pv_detected, stats.failed_rows) == (0, 0, 0) and not records
+        np.testing.assert_allclose(out, oa.truth_fp64(q, k, v, causal=causal), atol=3e-3, rtol=0)
+    q, k, v = _qkv(1, 2, 200, 128, seed=61)
+    clean, _, _ = oa.forward(q, k, v)
+    got, stats, records = oa.forward(q, k, v, fault=(1, 0, 1, 199, 150, 3.0))
+    assert (stats.score_detected, stats.score_corrected) == (1, 1)
+    assert (records[0].bad_row, records[0].bad_col) == (199 % 64, 150 % 64)
+    np.testing.assert_allclose(got, clean, atol=5e-4, rtol=0)
+    got, stats, _ = oa.forward(q, k, v, fault=(4, 0, 0, 199, 127, 0.5))
+    assert (stats.pv_detected, stats.pv_corrected, stats.failed_rows) == (1, 1, 0)
+    np.testing.assert_allclose(got, clean, atol=6e-3, rtol=0)
+    got, stats, _ = oa.forward(q, k, v, protect_softmax=True, fault=(2, 0, 0, 130, 199, 0.25))
+    assert (stats.softmax_detected, stats.softmax_corrected) == (1, 1)
+    np.testing.assert_allclose(got, clean, atol=1e-6, rtol=0)
