@@ -180,7 +180,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
-    if (lane == 0) {
+    if (elect_one()) {
       int s = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -220,7 +220,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (the leader only, in the pair form)
-    if (lane == 0 && rank == 0) {
+    if (rank == 0 && elect_one()) {
       constexpr uint32_t idesc = make_idesc_e4m3_f32(Cfg::kTileM, kBlockN);
       int s = 0;
       uint32_t phase = 0;

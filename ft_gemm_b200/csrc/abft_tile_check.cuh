@@ -3,7 +3,7 @@
 // checker of the reference's epilogue (src/s4_cluster_multicast_abft_fp8_gemm.cu:
 // 456-499) in register form.
 //
-//   row checksum    serial sum of the thread's 64 values (the reference's order)
+//   row checksum    sum of the thread's 64 values (four interleaved partial sums)
 //   column checksum transpose-reduce butterfly over the warp's 32 rows, combined
 //                   with the partner warp (the other 32 rows of the tile) through
 //                   shared memory; the caller synchronises the two warps
@@ -46,9 +46,17 @@ struct TileDecision {
 // again before both warps have finished abft_tile_decide().
 __device__ __forceinline__ void abft_tile_sums(const float (&v)[64], int lane, int half, TileScratch& sc, float exp_row, float scale_row,
                                                float abs_tol, float rel_tol, float& max_ratio) {
-  float row_sum = 0.0f;
+  // Four interleaved partial sums in two packed FP32 pairs: 32 dependent additions become two chains of 15.  (The score
+  // products come from the tensor core, whose own summation order is not defined, so no particular order is owed here.)
+  unsigned long long sum_a = pack_f32x2(v[0], v[1]), sum_b = pack_f32x2(v[2], v[3]);
 #pragma unroll
-  for (int c = 0; c < 64; ++c) row_sum += v[c];
+  for (int c = 4; c < 64; c += 4) {
+    sum_a = add_f32x2(sum_a, pack_f32x2(v[c], v[c + 1]));
+    sum_b = add_f32x2(sum_b, pack_f32x2(v[c + 2], v[c + 3]));
+  }
+  float sum_lo, sum_hi;
+  unpack_f32x2(add_f32x2(sum_a, sum_b), sum_lo, sum_hi);
+  const float row_sum = sum_lo + sum_hi;
   const float row_delta = exp_row - row_sum;
   const float row_thr = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_row), abs_tol);
   const bool row_bad = fabsf(row_delta) > row_thr;

@@ -5,7 +5,7 @@
 // src/ft_flash_attention_a14.cu:659-1201) and its metadata kernels (a14:303-316,
 // 571-621).  One CTA owns 256 queries of one (batch, head) as two 128-query tiles
 // A and B that share every 128-key K / V^T tile:
-//   warpgroup 0  warp 0: TMA producer (Q once, K and V^T tiles); warp 1: one thread
+//   warpgroup 0  warp 0: TMA producer of Q (once) and the K tiles, warp 2: of the V^T tiles; warp 1: one thread
 //                issues tcgen05.mma kind::f16 -- S_A, S_B = Q_{A,B} K_j^T into two
 //                128-column TMEM buffers, O_{A,B} += P_{A,B} V_j into two more;
 //                the group gives most of its registers away (setmaxnreg);
@@ -251,7 +251,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 
   if (group == 0) {
     reg_release<40>();
-    if (warp == 0 && lane == 0) {
+    if (warp == 0 && elect_one()) {
       // ------------------------------------------------------------- producer
       mbar_arrive_expect_tx(&sh.q_full, qtiles * kAttnTileBytes);
       for (int t = 0; t < qtiles; ++t) {
@@ -264,12 +264,18 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         mbar_arrive_expect_tx(&sh.k_full, kAttnTileBytes);
         tma_load_2d(smem_k, &tmap_k, &sh.k_full, 0, row_base + j * kAttnTile);
         tma_load_2d(smem_k + kAttnSlabBytes, &tmap_k, &sh.k_full, 64, row_base + j * kAttnTile);
+      }
+    } else if (warp == 2 && elect_one()) {
+      // ------------------------------------------------------------- producer of V^T: its own thread, so that the load of
+      // K_{j+1} (free as soon as both score products of tile j are done) never queues behind the wait for the V buffer
+      for (int j = 0; j < cta_tiles; ++j) {
+        const uint32_t ph = j & 1;
         if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
         mbar_arrive_expect_tx(&sh.v_full, kAttnTileBytes);
         tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kAttnTile, bh * kAttnTile);
         tma_load_2d(smem_v + kAttnSlabBytes, &tmap_vt, &sh.v_full, j * kAttnTile + 64, bh * kAttnTile);
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1 && elect_one()) {
       // ------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc = make_idesc_f16_f32(kAttnTile, kAttnTile);
       bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kAttnTimeoutNs);
@@ -407,7 +413,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             }
           }
 #pragma unroll
-          for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, fmaxf(v0[i], v1[i]));
+          for (int i = 0; i < 64; ++i) row_max = max3_f32(row_max, v0[i], v1[i]);
           asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
         }
         bool reload_row = false;
@@ -426,7 +432,7 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
               }
             }
 #pragma unroll
-            for (int i = 0; i < 64; ++i) row_max = fmaxf(row_max, v[i]);
+            for (int i = 0; i < 64; i += 2) row_max = max3_f32(row_max, v[i], v[i + 1]);
             asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
           }
           const TileDecision d = abft_tile_decide(lane, sh.scratch[t][pair][c], exp_col0[c], exp_col1[c], scale_col0[c], scale_col1[c],

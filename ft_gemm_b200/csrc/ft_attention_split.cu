@@ -7,7 +7,7 @@
 // O live in TMEM, P goes through shared memory -- but every query row is worked on
 // by TWO threads: the softmax / verifier warpgroup (t, c) takes the key half c
 // (64 columns = exactly one 64x64 ABFT tile per 64-row band) of query tile t.
-//   warpgroup 0        warp 0 TMA producer, warp 1 MMA issuer (as before)
+//   warpgroup 0        warp 0 TMA producer of Q and K, warp 2 of V^T, warp 1 MMA issuer
 //   warpgroups 1..4    (t, c) = (A,0), (A,1), (B,0), (B,1); 16 softmax warps per SM
 //                      instead of 8: the kernel is bound by latency (barriers, TMEM
 //                      loads, dependent FP32 chains), not by a pipe, and the second
@@ -154,7 +154,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 
   if (group == 0) {
     reg_release<40>();
-    if (warp == 0 && lane == 0) {
+    if (warp == 0 && elect_one()) {
       // ------------------------------------------------------------- producer
       mbar_arrive_expect_tx(&sh.q_full, qtiles * kQKBytes);
       for (int t = 0; t < qtiles; ++t) {
@@ -169,12 +169,18 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         mbar_arrive_expect_tx(&sh.k_full, kQKBytes);
 #pragma unroll
         for (int sl = 0; sl < kDimSlabs; ++sl) tma_load_2d(smem_k + sl * kSlabBytes, &tmap_k, &sh.k_full, 64 * sl, row_base + j * kTile);
+      }
+    } else if (warp == 2 && elect_one()) {
+      // ------------------------------------------------------------- producer of V^T: its own thread, so that the load of
+      // K_{j+1} (free as soon as both score products of tile j are done) never queues behind the wait for the V buffer
+      for (int j = 0; j < cta_tiles; ++j) {
+        const uint32_t ph = j & 1;
         if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kTimeoutNs)) break;
         mbar_arrive_expect_tx(&sh.v_full, 2 * kVSlabBytes);
         tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kTile, bh * kDim);
         tma_load_2d(smem_v + kSlabBytes, &tmap_vt, &sh.v_full, j * kTile + 64, bh * kDim);
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1 && elect_one()) {
       // ------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_s = make_idesc_f16_f32(kTile, kTile);  // S: 128 queries x 128 keys
       constexpr uint32_t idesc_o = make_idesc_f16_f32(kTile, kDim);   // O: 128 queries x kDim
@@ -307,8 +313,15 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               if (c * 64 + i > key_limit) v[i] = -INFINITY;
             }
           }
+          {  // two chains of three-input maxima instead of one chain of 64
+            float max_a = v[0], max_b = v[1];
 #pragma unroll
-          for (int i = 0; i < 64; ++i) local_max = fmaxf(local_max, v[i]);
+            for (int i = 2; i < 62; i += 4) {
+              max_a = max3_f32(max_a, v[i], v[i + 1]);
+              max_b = max3_f32(max_b, v[i + 2], v[i + 3]);
+            }
+            local_max = max3_f32(max_a, max_b, fmaxf(v[62], v[63]));
+          }
         }
         asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
         {
@@ -374,8 +387,9 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               float o[32];
               tmem_ld_32x32b_x32(o_addr + cc * 32, o);
               tmem_wait_ld();
+              const unsigned long long alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              for (int i = 0; i < 32; i += 2) unpack_f32x2(mul_f32x2(pack_f32x2(o[i], o[i + 1]), alpha2), o[i], o[i + 1]);
               tmem_st_32x32b_x32(o_addr + cc * 32, o);
             }
             tmem_wait_st();

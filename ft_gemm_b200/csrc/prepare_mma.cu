@@ -216,7 +216,7 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   const uint32_t tmem_base = tail.tmem_base;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       // ------------------------------------------------------------- producer
       int s = 0;
       uint32_t phase = 0;
@@ -243,7 +243,7 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {
       // ------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_s = Cfg::kHalf ? make_idesc_f16_f32(kPmRows, L::kSumCols) : make_idesc_e4m3_f32(kPmRows, L::kSumCols);
       constexpr uint32_t idesc_m = Cfg::kHalf ? make_idesc_f16_f32(kPmRows, L::kMagCols) : make_idesc_e4m3_f32(kPmRows, L::kMagCols);
