@@ -125,6 +125,25 @@ def cpu_baseline(sample_rows):
             "seconds": steady, "prepare_seconds": secs[0]}
 
 
+def cpu_table():
+    """The CPU port on the host cores at the two smaller configurations in full (1024^3 and 4096^3), with all threads and,
+    in a child process with OMP_NUM_THREADS=1, on one core; one JSON line per run with the prepare / GEMM / check split the
+    reference's first stage prints (src/s0_tiled_abft_fp8_gemm.cu:412-417)."""
+    from tests import oracle_lib
+    oracle = oracle_lib.load()
+    for size in (1024, 4096):
+        a = oracle.generate_uniform(size * size, SEED_A)
+        b = oracle.generate_uniform(size * size, SEED_B)
+        _, secs, summary = oracle.full_pass(a, b, size, size, size)
+        flops = 2.0 * size ** 3
+        print(json.dumps({"cpu_port": f"M=N=K={size}", "cores": oracle.num_threads(), "prepare_s": round(secs[0], 4),
+                          "gemm_s": round(secs[1], 4), "check_s": round(secs[2], 4),
+                          "steady_gflops": round(flops / (secs[1] + secs[2]) / 1e9, 2),
+                          "first_call_gflops": round(flops / sum(secs) / 1e9, 2), "bad_tiles": summary.bad_tiles}), flush=True)
+    if os.environ.get("OMP_NUM_THREADS") != "1":
+        subprocess.run([sys.executable, os.path.abspath(__file__), "--cpu-table"], env=dict(os.environ, OMP_NUM_THREADS="1"), check=True)
+
+
 def run_reference(args):
     """The reference has no CPU implementation of its own and its S1-S4 kernels are sm_90a-only; its arm is the
     oracle port on all host cores, each step a bounded row band of the same workload."""
@@ -155,7 +174,6 @@ def _reference_gpu_program():
     """For the record beside the CPU arm: the one stage of the reference that runs on this GPU generation, its scalar
     first stage, built unmodified from the reference's source (oracle/_ref/ref_program_s0), at 4096^3.  None when the
     binary or a GPU is missing."""
-    import subprocess
     exe = os.path.join(ROOT, "oracle", "_ref", "ref_program_s0")
     if not os.path.exists(exe):
         return None
@@ -189,8 +207,12 @@ def main():
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-attention", action="store_true")
     parser.add_argument("--m", type=int, default=M_PER_RANK, help="rows of A per rank (default: the 8192 of the headline shape)")
+    parser.add_argument("--cpu-table", action="store_true", help="only time the CPU port at 1024^3 and 4096^3 (all cores, one core)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.cpu_table:
+        cpu_table()
+        return
     if args.impl == "reference":
         run_reference(args)
         return
