@@ -21,12 +21,15 @@
 // The result equals the reference's value up to FP32 accumulation order, not bit
 // for bit; the CUDA-core kernel remains for that.
 //
-// One CTA (192 threads) per SM, persistent over tiles of 128 rows of X x 32 bands:
+// One CTA (320 threads) per SM, persistent over tiles of 128 rows of X x 32 bands:
 //   warp 0      TMA producer: X tile 128 rows x 128 B, plane tiles of sums and of
 //               magnitudes, 3 stages;
 //   warp 1      one thread issues, per 32 B of K, X * Ws^T and |X| * Wm^T into two
 //               column ranges of one TMEM accumulator (M128, N = planes x 32);
-//   warps 2-5   |X| tiles during the main loop, then the epilogue: thread = row.
+//   warps 2-5   the epilogue: thread = row; the accumulator is handed back as soon as it is in registers, so the
+//               stores of tile i run beside the main loop of tile i+1;
+//   warps 6-9   the |X| tiles of the main loop (a group of their own: with short K, as for the attention heads, the
+//               epilogue of one tile must not hold up the |X| tiles of the next).
 // `batch` independent problems of the same shape (attention heads) are laid out back
 // to back in X, in the planes and in the outputs.
 // Every wait is bounded; on expiry the kernel sets *status and leaves.
@@ -47,7 +50,7 @@ constexpr int kPmRows = 128;   // rows of X per tile
 constexpr int kPmBands = 32;   // bands per tile
 constexpr int kPmStages = 3;
 constexpr int kPmXBytes = kPmRows * 128;  // 16 KiB: 128 rows x one 128-byte swizzle row of K
-constexpr int kPmThreads = 192;
+constexpr int kPmThreads = 320;
 constexpr uint32_t kPmTmemColumns = 512;
 constexpr uint64_t kPmTimeoutNs = 2000000000ull;
 
@@ -85,15 +88,15 @@ constexpr int pm_smem_bytes() {
   return kPmStages * PmLayout<Cfg>::kStageBytes + static_cast<int>(sizeof(PmTail));
 }
 
-__device__ __forceinline__ bool pm_any(bool flag) {  // OR over the 128 threads of warps 2-5
+__device__ __forceinline__ bool pm_any(bool flag, int barrier_id) {  // OR over the 128 threads of one helper warpgroup
   uint32_t out;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %1, 0;\n\t"
-      "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+      "barrier.cta.red.or.pred q, %2, 128, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(out)
-      : "r"(static_cast<uint32_t>(flag))
+      : "r"(static_cast<uint32_t>(flag)), "r"(barrier_id)
       : "memory");
   return out != 0;
 }
@@ -285,23 +288,17 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         acc_phase ^= 1;
       }
     }
-  } else {
-    // ------------------------------------------------------------- |X| tiles, then the epilogue
-    const int tid = threadIdx.x - 64;  // 0..127
-    const int quarter = warp & 3;      // TMEM lanes [32 * quarter, +32) belong to this warp
-    const int row_in_block = quarter * 32 + lane;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int rows64 = (rows + 63) >> 6;
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------- |X| tiles
+    const int tid = threadIdx.x - 192;  // 0..127
     int s = 0;
-    uint32_t phase = 0, acc_phase = 0;
+    uint32_t phase = 0;
     bool alive = true;
     for (int t = worker; t < num_tiles && alive; t += workers) {
-      const int problem = t / tiles_per_problem, local = t % tiles_per_problem;
-      const int group = local % groups, row_block = local / groups;
       for (int kb = 0; kb < num_kb; ++kb) {
         bool ok = true;
         if (tid == 0) ok = mbar_wait_bounded(&tail.full[s], phase, abort_flag, kPmTimeoutNs);
-        if (pm_any(!ok)) {  // uniform over the 128 threads
+        if (pm_any(!ok, 2)) {  // uniform over the 128 threads
           alive = false;
           break;
         }
@@ -323,10 +320,21 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           phase ^= 1;
         }
       }
-      if (!alive) break;
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int tid = threadIdx.x - 64;  // 0..127
+    const int quarter = warp & 3;      // TMEM lanes [32 * quarter, +32) belong to this warp
+    const int row_in_block = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int rows64 = (rows + 63) >> 6;
+    uint32_t acc_phase = 0;
+    for (int t = worker; t < num_tiles; t += workers) {
+      const int problem = t / tiles_per_problem, local = t % tiles_per_problem;
+      const int group = local % groups, row_block = local / groups;
       bool ok = true;
       if (tid == 0) ok = mbar_wait_bounded(&tail.acc_full, acc_phase, abort_flag, kPmTimeoutNs);
-      if (pm_any(!ok)) break;
+      if (pm_any(!ok, 1)) break;
       acc_phase ^= 1;
       tcgen05_fence_after();
       // recombination, last plane first: FP8 digits by Horner (value = 2^-9 * sum_d 32^d * acc_d), FP16 pieces lo + mid + hi
