@@ -58,18 +58,26 @@ constexpr int kAttnSmemBytes = 6 * kAttnTileBytes + static_cast<int>(sizeof(Attn
 // V metadata and transpose (src/ft_flash_attention_a14.cu:303-316, 600-620):
 // v_sum[key] = sum_d V[key,d] (ascending d), v_weighted[key] = sum_d (2d-(D-1)) V[key,d]
 // (one fma per step), V^T[d][key] so that the keys are contiguous for the PV MMA.
-// grid (N/32, B*H), 256 threads.
+// grid (N/64, B*H), 256 threads: 64 keys per CTA, read as 16-byte pieces, written back as 128-byte runs of keys.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_prepare_v_kernel(const __half* __restrict__ v, __half* __restrict__ vt,
                                                              float* __restrict__ v_sum, float* __restrict__ v_weighted, int seq,
                                                              int dim) {
-  __shared__ __half tile[32][kAttnTile + 2];  // dim <= 128
+  __shared__ __half tile[64][kAttnTile + 2];  // dim <= 128; the odd word stride keeps column reads free of bank conflicts
   const int bh = blockIdx.y;
-  const int key0 = blockIdx.x * 32;
-  const __half* src = v + (static_cast<size_t>(bh) * seq + key0) * dim;
-  for (int i = threadIdx.x; i < 32 * dim; i += 256) tile[i / dim][i % dim] = src[i];
+  const int key0 = blockIdx.x * 64;
+  const uint4* src = reinterpret_cast<const uint4*>(v + (static_cast<size_t>(bh) * seq + key0) * dim);  // 16-byte aligned: dim % 8 == 0
+  for (int i = threadIdx.x; i < 64 * dim / 8; i += 256) {
+    const uint4 piece = __ldg(src + i);
+    const int key = (i * 8) / dim, d = (i * 8) % dim;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[key][d]);  // rows start on 4-byte boundaries
+    dst[0] = piece.x;
+    dst[1] = piece.y;
+    dst[2] = piece.z;
+    dst[3] = piece.w;
+  }
   __syncthreads();
-  if (threadIdx.x < 32) {
+  if (threadIdx.x < 64) {
     float sum = 0.0f, weighted = 0.0f;
     for (int d = 0; d < dim; ++d) {
       float value = __half2float(tile[threadIdx.x][d]);
@@ -79,15 +87,16 @@ __global__ void __launch_bounds__(256) attn_prepare_v_kernel(const __half* __res
     v_sum[static_cast<size_t>(bh) * seq + key0 + threadIdx.x] = sum;
     v_weighted[static_cast<size_t>(bh) * seq + key0 + threadIdx.x] = weighted;
   }
-  for (int i = threadIdx.x; i < 32 * dim; i += 256) {
-    int d = i / 32, key = i % 32;
-    vt[(static_cast<size_t>(bh) * dim + d) * seq + key0 + key] = tile[key][d];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int d = warp; d < dim; d += 8) {
+    const __half2 pair = __halves2half2(tile[2 * lane][d], tile[2 * lane + 1][d]);
+    *reinterpret_cast<__half2*>(vt + (static_cast<size_t>(bh) * dim + d) * seq + key0 + 2 * lane) = pair;
   }
 }
 
 cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq, int dim,
                                   cudaStream_t stream) {
-  dim3 grid(seq / 32, batch_heads);
+  dim3 grid(seq / 64, batch_heads);
   attn_prepare_v_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(v), static_cast<__half*>(vt), v_sum, v_weighted, seq, dim);
   return cudaGetLastError();
 }

@@ -21,14 +21,14 @@
 // The result equals the reference's value up to FP32 accumulation order, not bit
 // for bit; the CUDA-core kernel remains for that.
 //
-// One CTA (320 threads) per SM, persistent over tiles of 128 rows of X x 32 bands:
+// One CTA (448 threads) per SM, persistent over tiles of 128 rows of X x 32 bands:
 //   warp 0      TMA producer: X tile 128 rows x 128 B, plane tiles of sums and of
 //               magnitudes, 3 stages;
 //   warp 1      one thread issues, per 32 B of K, X * Ws^T and |X| * Wm^T into two
 //               column ranges of one TMEM accumulator (M128, N = planes x 32);
-//   warps 2-5   the epilogue: thread = row; the accumulator is handed back as soon as it is in registers, so the
-//               stores of tile i run beside the main loop of tile i+1;
-//   warps 6-9   the |X| tiles of the main loop (a group of their own: with short K, as for the attention heads, the
+//   warps 2-9   the epilogue: two threads per row, 16 bands each; the accumulator is handed back as soon as it is in
+//               registers, so the stores of tile i run beside the main loop of tile i+1;
+//   warps 10-13 the |X| tiles of the main loop (a group of their own: with short K, as for the attention heads, the
 //               epilogue of one tile must not hold up the |X| tiles of the next).
 // `batch` independent problems of the same shape (attention heads) are laid out back
 // to back in X, in the planes and in the outputs.
@@ -50,7 +50,7 @@ constexpr int kPmRows = 128;   // rows of X per tile
 constexpr int kPmBands = 32;   // bands per tile
 constexpr int kPmStages = 3;
 constexpr int kPmXBytes = kPmRows * 128;  // 16 KiB: 128 rows x one 128-byte swizzle row of K
-constexpr int kPmThreads = 320;
+constexpr int kPmThreads = 448;
 constexpr uint32_t kPmTmemColumns = 512;
 constexpr uint64_t kPmTimeoutNs = 2000000000ull;
 
@@ -72,13 +72,15 @@ struct PmLayout {
   static constexpr int kSumCols = Cfg::kSumPlanes * kPmBands, kMagCols = Cfg::kMagPlanes * kPmBands;
   static constexpr int kWsBytes = kSumCols * 128, kWmBytes = kMagCols * 128;
   static constexpr int kStageBytes = 2 * kPmXBytes + kWsBytes + kWmBytes;
+  static constexpr int kAccCols = kSumCols + kMagCols;                      // TMEM columns of one accumulator
+  static constexpr int kAccBuffers = 2 * kAccCols <= 512 ? 2 : 1;           // FP16: two (epilogue beside the next main loop); FP8: one
 };
 
 struct PmTail {
   uint64_t full[kPmStages];      // TMA data landed
   uint64_t abs_full[kPmStages];  // |X| written
   uint64_t empty[kPmStages];     // MMAs have read the stage
-  uint64_t acc_full, acc_empty;
+  uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -88,15 +90,16 @@ constexpr int pm_smem_bytes() {
   return kPmStages * PmLayout<Cfg>::kStageBytes + static_cast<int>(sizeof(PmTail));
 }
 
-__device__ __forceinline__ bool pm_any(bool flag, int barrier_id) {  // OR over the 128 threads of one helper warpgroup
+template <int kCount>
+__device__ __forceinline__ bool pm_any(bool flag, int barrier_id) {  // OR over the kCount threads of one helper group
   uint32_t out;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %1, 0;\n\t"
-      "barrier.cta.red.or.pred q, %2, 128, p;\n\t"
+      "barrier.cta.red.or.pred q, %2, %3, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(out)
-      : "r"(static_cast<uint32_t>(flag)), "r"(barrier_id)
+      : "r"(static_cast<uint32_t>(flag)), "r"(barrier_id), "n"(kCount)
       : "memory");
   return out != 0;
 }
@@ -201,8 +204,10 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       mbar_init(&tail.abs_full[s], 128);
       mbar_init(&tail.empty[s], 1);
     }
-    mbar_init(&tail.acc_full, 1);
-    mbar_init(&tail.acc_empty, 128);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tail.acc_full[a], 1);
+      mbar_init(&tail.acc_empty[a], 256);
+    }
     tail.abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_x);
@@ -251,10 +256,14 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       constexpr uint32_t idesc_s = Cfg::kHalf ? make_idesc_f16_f32(kPmRows, L::kSumCols) : make_idesc_e4m3_f32(kPmRows, L::kSumCols);
       constexpr uint32_t idesc_m = Cfg::kHalf ? make_idesc_f16_f32(kPmRows, L::kMagCols) : make_idesc_e4m3_f32(kPmRows, L::kMagCols);
       int s = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t phase = 0;
+      int done = 0;  // tiles issued by this CTA: accumulator done % kAccBuffers, in its use number done / kAccBuffers
       bool alive = true;
-      for (int t = worker; t < num_tiles && alive; t += workers) {
-        if (!mbar_wait_bounded(&tail.acc_empty, acc_phase ^ 1, abort_flag, kPmTimeoutNs)) break;
+      for (int t = worker; t < num_tiles && alive; t += workers, ++done) {
+        const int acc = done % L::kAccBuffers;
+        const uint32_t acc_phase = (done / L::kAccBuffers) & 1;
+        const uint32_t tmem_acc = tmem_base + acc * L::kAccCols;
+        if (!mbar_wait_bounded(&tail.acc_empty[acc], acc_phase ^ 1, abort_flag, kPmTimeoutNs)) break;
         tcgen05_fence_after();
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&tail.full[s], phase, abort_flag, kPmTimeoutNs) ||
@@ -271,11 +280,11 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           for (int kk = 0; kk < 4; ++kk) {  // one MMA consumes 32 bytes of K; +32 bytes inside the swizzle row = +2 in the address field
             const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
             if (Cfg::kHalf) {
-              umma_f16(tmem_base, desc_x + 2 * kk, desc_ws + 2 * kk, idesc_s, accumulate);
-              umma_f16(tmem_base + L::kSumCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc_m, accumulate);
+              umma_f16(tmem_acc, desc_x + 2 * kk, desc_ws + 2 * kk, idesc_s, accumulate);
+              umma_f16(tmem_acc + L::kSumCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc_m, accumulate);
             } else {
-              umma_f8f6f4(tmem_base, desc_x + 2 * kk, desc_ws + 2 * kk, idesc_s, accumulate);
-              umma_f8f6f4(tmem_base + L::kSumCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc_m, accumulate);
+              umma_f8f6f4(tmem_acc, desc_x + 2 * kk, desc_ws + 2 * kk, idesc_s, accumulate);
+              umma_f8f6f4(tmem_acc + L::kSumCols, desc_ax + 2 * kk, desc_wm + 2 * kk, idesc_m, accumulate);
             }
           }
           umma_commit(&tail.empty[s]);
@@ -284,13 +293,12 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
             phase ^= 1;
           }
         }
-        if (alive) umma_commit(&tail.acc_full);
-        acc_phase ^= 1;
+        if (alive) umma_commit(&tail.acc_full[acc]);
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 10) {
     // ------------------------------------------------------------- |X| tiles
-    const int tid = threadIdx.x - 192;  // 0..127
+    const int tid = threadIdx.x - 320;  // 0..127
     int s = 0;
     uint32_t phase = 0;
     bool alive = true;
@@ -298,7 +306,7 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       for (int kb = 0; kb < num_kb; ++kb) {
         bool ok = true;
         if (tid == 0) ok = mbar_wait_bounded(&tail.full[s], phase, abort_flag, kPmTimeoutNs);
-        if (pm_any(!ok, 2)) {  // uniform over the 128 threads
+        if (pm_any<128>(!ok, 2)) {  // uniform over the 128 threads
           alive = false;
           break;
         }
@@ -323,29 +331,30 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     }
   } else {
     // ------------------------------------------------------------- epilogue
-    const int tid = threadIdx.x - 64;  // 0..127
+    const int tid = threadIdx.x - 64;  // 0..255
+    const int half = (warp - 2) >> 2;  // which 16 of the tile's 32 bands this thread recombines and stores
     const int quarter = warp & 3;      // TMEM lanes [32 * quarter, +32) belong to this warp
     const int row_in_block = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const int rows64 = (rows + 63) >> 6;
-    uint32_t acc_phase = 0;
-    for (int t = worker; t < num_tiles; t += workers) {
+    int done = 0;
+    for (int t = worker; t < num_tiles; t += workers, ++done) {
       const int problem = t / tiles_per_problem, local = t % tiles_per_problem;
       const int group = local % groups, row_block = local / groups;
+      const int acc = done % L::kAccBuffers;
+      const uint32_t acc_phase = (done / L::kAccBuffers) & 1;
       bool ok = true;
-      if (tid == 0) ok = mbar_wait_bounded(&tail.acc_full, acc_phase, abort_flag, kPmTimeoutNs);
-      if (pm_any(!ok, 1)) break;
-      acc_phase ^= 1;
+      if (tid == 0) ok = mbar_wait_bounded(&tail.acc_full[acc], acc_phase, abort_flag, kPmTimeoutNs);
+      if (pm_any<256>(!ok, 1)) break;
       tcgen05_fence_after();
       // recombination, last plane first: FP8 digits by Horner (value = 2^-9 * sum_d 32^d * acc_d), FP16 pieces lo + mid + hi
-      float e[2][2][16];  // [sums | magnitudes][band half][band]
+      float e[2][16];  // [sums | magnitudes][band]
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const int planes = which == 0 ? Cfg::kSumPlanes : Cfg::kMagPlanes;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const uint32_t base = lane_addr + which * L::kSumCols + half * 16;
-          tmem_ld_32x32b_x16(base + (planes - 1) * kPmBands, e[which][half]);
+        {
+          const uint32_t base = lane_addr + acc * L::kAccCols + which * L::kSumCols + half * 16;
+          tmem_ld_32x32b_x16(base + (planes - 1) * kPmBands, e[which]);
           tmem_wait_ld();
 #pragma unroll
           for (int d = planes - 2; d >= 0; --d) {
@@ -353,27 +362,27 @@ expected_checksums_mma_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
             tmem_ld_32x32b_x16(base + d * kPmBands, a);
             tmem_wait_ld();
 #pragma unroll
-            for (int b = 0; b < 16; ++b) e[which][half][b] = Cfg::kHalf ? e[which][half][b] + a[b] : __fmaf_rn(e[which][half][b], 32.0f, a[b]);
+            for (int b = 0; b < 16; ++b) e[which][b] = Cfg::kHalf ? e[which][b] + a[b] : __fmaf_rn(e[which][b], 32.0f, a[b]);
           }
         }
       }
       tcgen05_fence_before();
-      mbar_arrive(&tail.acc_empty);  // the accumulators are in registers: the next tile may start
+      mbar_arrive(&tail.acc_empty[acc]);  // the accumulators are in registers: this buffer may take another tile
       const float unit = Cfg::kHalf ? 128.0f : 0.001953125f;  // undo the 2^-7 of the FP16 pieces / the 2^9 of the FP8 digits
       const int row = row_block * kPmRows + row_in_block;
       if (row < rows64 * 64) {  // rows of the last 64-row group past `rows` were zero-filled by the copy: their checksums are zeros
         const size_t problem_base = static_cast<size_t>(problem) * rows64 * nbands * 64;
+        // consecutive bands of one row lie a fixed distance apart in both layouts
+        const int band0 = group * kPmBands + half * 16;
+        const size_t first = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band0 : static_cast<size_t>(band0) * rows64 + (row >> 6);
+        const size_t step = mode == 0 ? 64 : static_cast<size_t>(rows64) * 64;
+        float* out_e = expected + problem_base + first * 64 + (row & 63);
+        float* out_s = scales + problem_base + first * 64 + (row & 63);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll
-          for (int b = 0; b < 16; ++b) {
-            const int band = group * kPmBands + half * 16 + b;
-            if (band < nbands) {
-              const size_t tile = mode == 0 ? static_cast<size_t>(row >> 6) * nbands + band : static_cast<size_t>(band) * rows64 + (row >> 6);
-              const size_t out = problem_base + tile * 64 + (row & 63);
-              expected[out] = e[0][half][b] * unit;
-              scales[out] = e[1][half][b] * unit;
-            }
+        for (int b = 0; b < 16; ++b) {
+          if (band0 + b < nbands) {
+            out_e[b * step] = e[0][b] * unit;
+            out_s[b * step] = e[1][b] * unit;
           }
         }
       }
