@@ -204,17 +204,18 @@ __global__ void __launch_bounds__(kBandThreads) quantize_band_sums_kernel(const 
   mo[1] = make_float4(m[4], m[5], m[6], m[7]);
 }
 
-// FP16 operands (attention): one thread owns 8 consecutive k.
+// FP16 operands (attention): one thread owns 8 consecutive k of one band, rows in ascending order.  With a short k (a head
+// dimension) `per` = k / 8 threads cover a band and a CTA takes kBandThreads / per bands, so that no thread is idle.
 __global__ void __launch_bounds__(kBandThreads) band_sums_f16_kernel(const __half* __restrict__ x, float* __restrict__ sums,
-                                                                     float* __restrict__ mags, int k) {
-  int band = blockIdx.y;
-  int k0 = (blockIdx.x * kBandThreads + threadIdx.x) * 8;
-  if (k0 >= k) return;
+                                                                     float* __restrict__ mags, int k, int per, int nbands) {
+  int band = blockIdx.y * (kBandThreads / per) + threadIdx.x / per;
+  int k0 = (blockIdx.x * per + threadIdx.x % per) * 8;
+  if (k0 >= k || band >= nbands) return;
   const __half* base = x + static_cast<size_t>(band) * 64 * k + k0;
   float s[8], m[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) s[i] = m[i] = 0.0f;
-#pragma unroll 8
+#pragma unroll 16
   for (int row = 0; row < 64; ++row) {
     uint4 packed = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(row) * k));
     const __half2* h2 = reinterpret_cast<const __half2*>(&packed);
@@ -437,9 +438,12 @@ cudaError_t launch_band_sums_f16(const void* x, float* sums, float* mags, size_t
   size_t bands = rows / 64;
   for (size_t first = 0; first < bands; first += 65535) {  // grid.y limit
     unsigned count = static_cast<unsigned>(bands - first < 65535 ? bands - first : 65535);
-    dim3 grid((k / 8 + kBandThreads - 1) / kBandThreads, count);
+    const int chunks = k / 8;
+    const int per = chunks < kBandThreads && kBandThreads % chunks == 0 ? chunks : kBandThreads;  // threads per band in a CTA
+    const unsigned bands_per_cta = kBandThreads / per;
+    dim3 grid((chunks + per - 1) / per, (count + bands_per_cta - 1) / bands_per_cta);
     band_sums_f16_kernel<<<grid, kBandThreads, 0, stream>>>(static_cast<const __half*>(x) + first * 64 * k, sums + first * k,
-                                                            mags + first * k, k);
+                                                            mags + first * k, k, per, static_cast<int>(count));
   }
   return cudaGetLastError();
 }
