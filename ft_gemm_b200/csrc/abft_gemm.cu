@@ -178,6 +178,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   tcgen05_fence_after();
   const uint32_t tmem_base = tail.tmem_base;
 
+  if (p.clear_counters != nullptr && blockIdx.x == 0 && threadIdx.x >= 64 && threadIdx.x < 72) p.clear_counters[threadIdx.x - 64] = 0;
+
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (elect_one()) {

@@ -96,7 +96,9 @@ struct ft_gemm_handle {
   size_t cache_bytes = 0;
   float *a_sums = nullptr, *a_mags = nullptr, *b_sums = nullptr, *b_mags = nullptr;
   float *expected_rows = nullptr, *expected_cols = nullptr, *row_scales = nullptr, *col_scales = nullptr;
-  DeviceReport* report = nullptr;
+  DeviceReport* report = nullptr;          // the buffer of the current (last started) report: report_pair[report_index]
+  DeviceReport* report_pair = nullptr;     // two buffers, used alternately (see GemmParams::clear_counters)
+  int report_index = 0;
   CUtensorMap tmap_a{}, tmap_b{};
   // tensor-core prepare: digit planes of the band sums (in the cache allocation) and their maps
   uint8_t *planes_as = nullptr, *planes_am = nullptr, *planes_bs = nullptr, *planes_bm = nullptr;
@@ -351,7 +353,8 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   h->cache_bytes = floats * sizeof(float) + 2 * planes_a + 2 * planes_b;
   cudaError_t err = opts.exact_prepare != 0 ? cudaSuccess : configure_prepare_mma();
   if (err == cudaSuccess) err = cudaMalloc(&h->cache_base, h->cache_bytes);
-  if (err == cudaSuccess) err = cudaMalloc(&h->report, sizeof(DeviceReport));
+  if (err == cudaSuccess) err = cudaMalloc(&h->report_pair, 2 * sizeof(DeviceReport));
+  h->report = h->report_pair;
   if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->prepare_status), sizeof(int));
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev0);
   if (err == cudaSuccess) err = cudaEventCreate(&h->ev_mid);
@@ -390,7 +393,7 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (rc == FT_OK) {
-    cudaError_t merr = cudaMemsetAsync(h->report, 0, sizeof(DeviceReport), stream);
+    cudaError_t merr = cudaMemsetAsync(h->report_pair, 0, 2 * sizeof(DeviceReport), stream);
     if (merr == cudaSuccess) merr = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
     if (merr != cudaSuccess) rc = fail(FT_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(merr));
   }
@@ -474,8 +477,14 @@ int ft_gemm_fp8_abft_run_window(ft_gemm_handle* h, float* c, const ft_fault* fau
     params.faults.col[i] = faults[i].col;
     params.faults.value[i] = faults[i].value;
   }
-  // one small memset in place of the reference's two counter memsets
-  if (zero_report) FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
+  // In place of the reference's two counter memsets (src/s4:693-694): a new report goes to the other buffer, whose
+  // counters the previous such launch (or the prepare) has cleared, and this launch clears the one it leaves.
+  if (zero_report) {
+    h->report_index ^= 1;
+    h->report = h->report_pair + h->report_index;
+    params.report = h->report;
+    params.clear_counters = reinterpret_cast<int*>(h->report_pair + (h->report_index ^ 1));
+  }
   int tiles = ((rows + tile_m - 1) / tile_m) * ((cols + 255) / 256);
   int grid = h->pair ? std::min(h->grid, 2 * tiles) : std::min(h->grid, tiles);
   FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, grid, h->pair, stream));
@@ -565,7 +574,7 @@ int ft_gemm_fp8_abft_destroy(ft_gemm_handle* h) {
   if (h == nullptr) return FT_OK;
   if (h->last_stream != nullptr || h->cache_base != nullptr) cudaStreamSynchronize(h->last_stream);
   cudaFree(h->cache_base);
-  cudaFree(h->report);
+  cudaFree(h->report_pair);
   cudaFree(h->prepare_status);
   if (h->ev0) cudaEventDestroy(h->ev0);
   if (h->ev_mid) cudaEventDestroy(h->ev_mid);

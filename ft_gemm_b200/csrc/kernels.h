@@ -35,6 +35,10 @@ struct GemmParams {
   const float* col_scales;
   float* c;
   DeviceReport* report;
+  // The handle keeps two report buffers and alternates between them: a launch that starts a new report also clears the
+  // counters (the first 32 bytes) of the buffer the NEXT call will use, so no separate memset sits between two calls.
+  // nullptr: nothing to clear (window launches that add to the current report).
+  int* clear_counters;
   int m, n, k;
   // window of C this launch computes (rows a multiple of the tile height, cols of 256); the whole product by default
   int row0, rows, col0, cols;
