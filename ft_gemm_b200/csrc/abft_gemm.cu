@@ -302,6 +302,22 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       tile_coords(t, num_m, num_n, kGroupM, mb, nb);
       mb += first_mb;
       nb += first_nb;
+      {
+        // The cached expected checksums of this tile's (up to) four ABFT tiles are asked for while the main loop still runs:
+        // with few tiles per CTA nothing else hides their latency.  Lines of row blocks or column groups past the
+        // matrix are not touched.
+        const int pf_row = (mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM) / kGroupCols + pair;
+        if (pf_row * kGroupCols < p.m) {
+          const int pf_groups = min(kGroups, (p.n - nb * kBlockN + kGroupCols - 1) / kGroupCols);
+          for (int g = 0; g < pf_groups; ++g) {
+            const size_t cache = static_cast<size_t>(pf_row * tile_cols + nb * kGroups + g) * kGroupCols;
+            prefetch_l1(p.expected_rows + cache + r_local);
+            prefetch_l1(p.row_scales + cache + r_local);
+            prefetch_l1(p.expected_cols + cache + 2 * lane);
+            prefetch_l1(p.col_scales + cache + 2 * lane);
+          }
+        }
+      }
       const long long t0 = profiling ? clock64() : 0;
       // one thread polls the barrier; the other 127 sleep in the hardware barrier below until it has seen the phase
       bool ok = true;

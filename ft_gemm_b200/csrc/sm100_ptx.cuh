@@ -59,6 +59,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+__device__ __forceinline__ void prefetch_l1(const void* ptr) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+}
+
 // One lane of a converged warp, chosen by the hardware.  Unlike a test of the lane index, the compiler knows that the
 // code under it runs in a single thread and keeps the descriptors of tcgen05.mma and of the tensor copies in uniform registers.
 __device__ __forceinline__ bool elect_one() {
