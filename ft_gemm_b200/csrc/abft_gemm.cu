@@ -46,7 +46,6 @@ constexpr int kEpilogueThreads = 128;
 constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
 constexpr int kGroups = kBlockN / kGroupCols;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
-constexpr int kTileGroupRows = 2048;  // rows walked together so that concurrent tiles share A and B in L2
 constexpr int kMaxStages = 7;
 
 template <bool kPair>
@@ -143,7 +142,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int first_nb = p.col0 / kBlockN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.k + kBlockK - 1) / kBlockK;    // a short last K block is zero-filled by the copy engine
-  constexpr int kGroupM = kTileGroupRows / Cfg::kTileM;
+  const int kGroupM = max(1, p.group_rows / Cfg::kTileM);  // row blocks walked together (see GemmParams::group_rows)
   constexpr bool profiling = kProfile;
 
   if (threadIdx.x == 0) {

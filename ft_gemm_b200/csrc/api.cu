@@ -200,6 +200,8 @@ void fill_params(const ft_gemm_handle* h, float* c, GemmParams* params) {
   params->cols = h->n;
   params->abs_tol = h->options.abs_tol;
   params->rel_tol = h->options.rel_tol;
+  const long long panel_rows = (32ll << 20) / h->k;  // rows of A whose K bytes fill 32 MiB
+  params->group_rows = static_cast<int>(std::min<long long>(std::max<long long>(panel_rows / 256 * 256, 1024), 8192));
 }
 
 // Largest chunk count g <= kMaxPipeChunks for which M/g and N/g are whole tiles; 1 = no pipelining.
