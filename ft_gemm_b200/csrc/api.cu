@@ -201,7 +201,11 @@ void fill_params(const ft_gemm_handle* h, float* c, GemmParams* params) {
   params->abs_tol = h->options.abs_tol;
   params->rel_tol = h->options.rel_tol;
   const long long panel_rows = (32ll << 20) / h->k;  // rows of A whose K bytes fill 32 MiB
-  params->group_rows = static_cast<int>(std::min<long long>(std::max<long long>(panel_rows / 256 * 256, 1024), 8192));
+  const int tile_m = h->pair ? 256 : 128;
+  const int per_group = static_cast<int>(std::min<long long>(std::max<long long>(panel_rows, 1024), 8192)) / tile_m;
+  const int row_blocks = (h->m + tile_m - 1) / tile_m;
+  const int groups = (row_blocks + per_group - 1) / per_group;
+  params->group_rows = (row_blocks + groups - 1) / groups * tile_m;  // groups of equal height
 }
 
 // Largest chunk count g <= kMaxPipeChunks for which M/g and N/g are whole tiles; 1 = no pipelining.
