@@ -11,11 +11,17 @@ LIB       := ft_gemm_b200/lib/libft_gemm_b200.so
 OBJS      := build/obj/prepare.o build/obj/prepare_mma.o build/obj/abft_gemm.o build/obj/api.o build/obj/noalloc.o build/obj/ft_attention.o build/obj/ft_attention_split.o build/obj/api_attention.o build/obj/gemm_softmax.o
 HDRS      := include/ft_gemm.h include/ft_attention.h include/ft_gemm_softmax.h $(CSRC)/kernels.h $(CSRC)/attention_kernels.h $(CSRC)/abft_tile_check.cuh $(CSRC)/sm100_ptx.cuh
 
-FAULT_TRIALS    ?= 100
+# the campaign the 100 % single-fault correction claim is quoted on: 8192^3, N(0,1) inputs, 1000 single faults U[1,256]
+# with random sign + 50 double faults, relative tolerance 2e-6 (the reference's default 2e-5 puts the threshold near 6.7
+# at K = 8192 with these inputs, above ~2 % of the injected magnitudes; FAULT_REL_TOL=0.00002 runs that configuration)
+FAULT_SIZE      ?= 8192
+FAULT_DIST      ?= normal
+FAULT_TRIALS    ?= 1000
+FAULT_DOUBLES   ?= 50
 FAULT_MIN_VALUE ?= 1
 FAULT_MAX_VALUE ?= 256
 FAULT_SEED      ?= 12345
-FAULT_REL_TOL   ?= 0.00002
+FAULT_REL_TOL   ?= 0.000002
 
 all: lib cli oracle
 
@@ -32,7 +38,7 @@ $(LIB): $(OBJS)
 cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench build/ft_flash_attention build/gemm_softmax_abft
 
 build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(LIB)
-	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -lnccl -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
@@ -50,8 +56,9 @@ oracle:
 	$(MAKE) -C oracle
 
 fault_campaign: build/fault_campaign
-	./build/fault_campaign --m 4096 --n 4096 --k 4096 --warmup 1 --repeat 1 --rel-tol $(FAULT_REL_TOL) \
-	  --fault-min-value $(FAULT_MIN_VALUE) --fault-max-value $(FAULT_MAX_VALUE) --fault-trials $(FAULT_TRIALS) --fault-seed $(FAULT_SEED)
+	./build/fault_campaign --m $(FAULT_SIZE) --n $(FAULT_SIZE) --k $(FAULT_SIZE) --dist $(FAULT_DIST) --warmup 1 --repeat 1 \
+	  --rel-tol $(FAULT_REL_TOL) --fault-min-value $(FAULT_MIN_VALUE) --fault-max-value $(FAULT_MAX_VALUE) \
+	  --fault-trials $(FAULT_TRIALS) --double-trials $(FAULT_DOUBLES) --fault-seed $(FAULT_SEED)
 
 clean:
 	rm -rf build/obj

@@ -21,7 +21,8 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libf
 
 class FtOptions(ctypes.Structure):
     _fields_ = [("abs_tol", ctypes.c_float), ("rel_tol", ctypes.c_float), ("sm_limit", ctypes.c_int),
-                ("single_cta", ctypes.c_int), ("exact_prepare", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
+                ("single_cta", ctypes.c_int), ("exact_prepare", ctypes.c_int), ("wait_limit_us", ctypes.c_int),
+                ("reserved", ctypes.c_int * 2)]
 
 
 class FtFault(ctypes.Structure):
@@ -82,6 +83,12 @@ def load():
     lib.ft_gemm_fp8_abft_expected_noalloc.argtypes = [vp, vp, ci, ci, ci, vp, vp, vp, vp, vp]
     lib.ft_gemm_fp8_abft_expected_noalloc.restype = ci
     lib.ft_gemm_generate_fp8.argtypes = [vp, ctypes.c_size_t, ctypes.c_uint32, ci, cf, cf, vp]
+    lib.ft_gemm_report_rebase.argtypes = [ctypes.POINTER(FtReport), ci, ci]
+    lib.ft_gemm_report_rebase.restype = ci
+    lib.ft_gemm_report_merge.argtypes = [ctypes.POINTER(FtReport), ci, ctypes.POINTER(FtReport)]
+    lib.ft_gemm_report_merge.restype = ci
+    lib.ft_gemm_fp8_abft_selftest_wait.argtypes = [vp, ci, vp]
+    lib.ft_gemm_fp8_abft_selftest_wait.restype = ci
     lib.ft_gemm_last_error.argtypes = []
     lib.ft_gemm_last_error.restype = ctypes.c_char_p
     lib.ft_gemm_abi_version.argtypes = []

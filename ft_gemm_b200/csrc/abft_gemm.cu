@@ -45,7 +45,6 @@ constexpr int kThreads = 192;
 constexpr int kEpilogueThreads = 128;
 constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
 constexpr int kGroups = kBlockN / kGroupCols;
-constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
 constexpr int kMaxStages = 7;
 
 template <bool kPair>
@@ -195,7 +194,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int b_row = nb * kBlockN + static_cast<int>(rank) * Cfg::kBRows;
         for (int kb = 0; kb < num_kb; ++kb) {
           const long long t0 = profiling ? clock64() : 0;
-          if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, kWaitTimeoutNs)) {
+          if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, p.wait_timeout_ns)) {
             alive = false;
             break;
           }
@@ -232,13 +231,13 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const long long role_start = profiling ? clock64() : 0;
       for (int t = worker; t < num_tiles && alive; t += workers) {
         long long t0 = profiling ? clock64() : 0;
-        if (!mbar_wait_bounded(&tail.tmem_empty[acc], acc_phase ^ 1, abort_flag, kWaitTimeoutNs)) break;
+        if (!mbar_wait_bounded(&tail.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.wait_timeout_ns)) break;
         if (profiling) wait_tmem += clock64() - t0;
         tcgen05_fence_after();
         uint32_t tmem_d = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < num_kb; ++kb) {
           t0 = profiling ? clock64() : 0;
-          if (!mbar_wait_bounded(&tail.full[s], phase, abort_flag, kWaitTimeoutNs)) {
+          if (!mbar_wait_bounded(&tail.full[s], phase, abort_flag, p.wait_timeout_ns)) {
             alive = false;
             break;
           }
@@ -320,7 +319,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const long long t0 = profiling ? clock64() : 0;
       // one thread polls the barrier; the other 127 sleep in the hardware barrier below until it has seen the phase
       bool ok = true;
-      if (warp == 2 && lane == 0) ok = mbar_wait_bounded(&tail.tmem_full[acc], acc_phase, abort_flag, kWaitTimeoutNs);
+      if (warp == 2 && lane == 0) ok = mbar_wait_bounded(&tail.tmem_full[acc], acc_phase, abort_flag, p.wait_timeout_ns);
       if (any_over_epilogue(!ok)) break;
       if (profiling) {
         epi_wait += clock64() - t0;
@@ -551,6 +550,28 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       tmem_dealloc(tmem_base, kTmemColumns);
     }
   }
+}
+
+// The failure path of every kernel here, in isolation: a bounded wait that nothing satisfies, then the same status
+// write as the teardown above.  One warp, no tensor memory, no copies, no MMA.
+__global__ void selftest_wait_kernel(DeviceReport* report, unsigned long long limit_ns) {
+  __shared__ uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&barrier, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_bounded(&barrier, 0, &abort_flag, limit_ns);  // phase 0 never completes
+    if (!ok && abort_flag != 0) atomicExch(&report->status, 1);
+  }
+}
+
+cudaError_t launch_selftest_wait(DeviceReport* report, unsigned long long limit_ns, cudaStream_t stream) {
+  selftest_wait_kernel<<<1, 32, 0, stream>>>(report, limit_ns);
+  return cudaGetLastError();
 }
 
 int abft_gemm_smem_bytes(bool pair) { return pair ? smem_bytes<true>() : smem_bytes<false>(); }

@@ -172,6 +172,8 @@ int copy_padded(ft_gemm_handle* h, int which, cudaStream_t stream) {
 }
 
 int fill_cache(ft_gemm_handle* h, int which, cudaStream_t stream) {
+  // the status of the prepare kernels describes the latest fill: a handle whose earlier fill timed out recovers here
+  FT_CUDA(cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream));
   FT_CUDA(cudaEventRecord(h->ev0, stream));
   if (which & 1) FT_CUDA(launch_band_sums(h->a, h->a_sums, h->a_mags, h->m, h->k, stream));
   if (which & 2) FT_CUDA(launch_band_sums(h->b, h->b_sums, h->b_mags, h->n, h->k, stream));
@@ -200,6 +202,7 @@ void fill_params(const ft_gemm_handle* h, float* c, GemmParams* params) {
   params->cols = h->n;
   params->abs_tol = h->options.abs_tol;
   params->rel_tol = h->options.rel_tol;
+  params->wait_timeout_ns = h->options.wait_limit_us > 0 ? 1000ull * static_cast<unsigned long long>(h->options.wait_limit_us) : 2000000000ull;
   const long long panel_rows = (32ll << 20) / h->k;  // rows of A whose K bytes fill 32 MiB
   const int tile_m = h->pair ? 256 : 128;
   const int per_group = static_cast<int>(std::min<long long>(std::max<long long>(panel_rows, 1024), 8192)) / tile_m;
@@ -305,7 +308,9 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   ft_options opts;
   ft_options_default(&opts);
   if (options != nullptr) opts = *options;
-  if (opts.abs_tol < 0.0f || opts.rel_tol < 0.0f || opts.sm_limit < 0) return fail(FT_ERR_INVALID, "negative tolerance or sm_limit");
+  if (opts.abs_tol < 0.0f || opts.rel_tol < 0.0f || opts.sm_limit < 0 || opts.wait_limit_us < 0) {
+    return fail(FT_ERR_INVALID, "negative tolerance, sm_limit or wait_limit_us");
+  }
 
   int device = 0;
   FT_CUDA(cudaGetDevice(&device));
@@ -427,6 +432,7 @@ int ft_gemm_fp8_abft_quantize_a(ft_gemm_handle* h, const void* src, int src_dtyp
   if (!(scale == scale) || scale == 0.0f) return fail(FT_ERR_INVALID, "scale must be a non-zero number");
   if (h->pad_a != nullptr) return fail(FT_ERR_UNSUPPORTED, "the fused producer of A needs K %% 16 == 0 and a 16-byte aligned A");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  FT_CUDA(cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream));
   FT_CUDA(cudaEventRecord(h->ev0, stream));
   // A and its band sums in one pass over the source; the caller's A buffer is written here
   FT_CUDA(launch_quantize_band_sums(src, src_dtype, const_cast<void*>(h->a), h->a_sums, h->a_mags, h->m, h->k, scale, stream));
@@ -505,11 +511,11 @@ int ft_gemm_fp8_abft_run_profiled(ft_gemm_handle* h, float* c, unsigned long lon
   unsigned long long* dev = nullptr;
   size_t bytes = static_cast<size_t>(h->grid) * 8 * sizeof(unsigned long long);
   FT_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), bytes));
-  FT_CUDA(cudaMemsetAsync(dev, 0, bytes, stream));
   GemmParams params{};
   fill_params(h, c, &params);
   params.profile = dev;
-  cudaError_t err = cudaMemsetAsync(h->report, 0, 32, stream);
+  cudaError_t err = cudaMemsetAsync(dev, 0, bytes, stream);  // every failure below still reaches the cudaFree
+  if (err == cudaSuccess) err = cudaMemsetAsync(h->report, 0, 32, stream);
   if (err == cudaSuccess) err = launch_abft_gemm(h->tmap_a, h->tmap_b, params, h->grid, h->pair, stream);
   if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
   int n = std::min(h->grid, max_ctas);
@@ -546,7 +552,53 @@ int ft_gemm_fp8_abft_report(ft_gemm_handle* h, ft_report* out) {
     if (cudaEventElapsedTime(&ms, h->ev0, h->ev_mid) == cudaSuccess) out->prepare_input_ms = ms;
     if (cudaEventElapsedTime(&ms, h->ev_mid, h->ev1) == cudaSuccess) out->prepare_expected_ms = ms;
   }
-  if (dev.status != 0) return fail(FT_ERR_TIMEOUT, "a device-side wait expired; the output of this run is not valid");
+  if (dev.status != 0) {
+    return fail(FT_ERR_TIMEOUT, "a device-side wait expired; the output of this run is not valid (after a prepare time-out, "
+                                "_refresh the handle)");
+  }
+  return FT_OK;
+}
+
+int ft_gemm_fp8_abft_selftest_wait(ft_gemm_handle* h, int limit_us, void* stream_ptr) {
+  if (h == nullptr || limit_us <= 0 || limit_us > 1000000) return fail(FT_ERR_INVALID, "null handle, or limit_us outside [1, 1000000]");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  FT_CUDA(cudaMemsetAsync(h->report, 0, 32, stream));
+  FT_CUDA(launch_selftest_wait(h->report, 1000ull * static_cast<unsigned long long>(limit_us), stream));
+  h->last_stream = stream;
+  return FT_OK;
+}
+
+int ft_gemm_report_rebase(ft_report* report, int tile_cols, int first_tile_row) {
+  if (report == nullptr || tile_cols <= 0 || first_tile_row < 0) return fail(FT_ERR_INVALID, "null report, or bad tile_cols / first_tile_row");
+  for (int i = 0; i < report->n_records && i < FT_MAX_RECORDS; ++i) report->records[i].tile += first_tile_row * tile_cols;
+  return FT_OK;
+}
+
+int ft_gemm_report_merge(const ft_report* shards, int n, ft_report* out) {
+  if (shards == nullptr || out == nullptr || n <= 0) return fail(FT_ERR_INVALID, "null report pointer or no shards");
+  ft_report merged;
+  std::memset(&merged, 0, sizeof(merged));
+  for (int s = 0; s < n; ++s) {
+    const ft_report& r = shards[s];
+    if (merged.status == FT_OK) merged.status = r.status;
+    merged.bad_tiles += r.bad_tiles;
+    merged.corrected_tiles += r.corrected_tiles;
+    merged.multi_fault_tiles += r.multi_fault_tiles;
+    merged.records_dropped += r.records_dropped;
+    merged.max_clean_ratio = std::max(merged.max_clean_ratio, r.max_clean_ratio);
+    merged.prepare_ms = std::max(merged.prepare_ms, r.prepare_ms);
+    merged.prepare_input_ms = std::max(merged.prepare_input_ms, r.prepare_input_ms);
+    merged.prepare_expected_ms = std::max(merged.prepare_expected_ms, r.prepare_expected_ms);
+    const int count = std::max(0, std::min(r.n_records, FT_MAX_RECORDS));
+    for (int i = 0; i < count; ++i) {
+      if (merged.n_records < FT_MAX_RECORDS) {
+        merged.records[merged.n_records++] = r.records[i];
+      } else {
+        ++merged.records_dropped;
+      }
+    }
+  }
+  *out = merged;
   return FT_OK;
 }
 
@@ -676,6 +728,13 @@ int ft_gemm_fp8_abft_host(ft_gemm_handle** reuse, const void* a_host, const void
       err = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream);
       if (err != cudaSuccess) rc = fail(FT_ERR_CUDA, "device-to-host copy failed: %s", cudaGetErrorString(err));
     }
+  }
+  if (h == nullptr) {  // a fresh call whose copies failed before a handle existed: the error text stays, nothing leaks
+    cudaFree(da);
+    cudaFree(db);
+    cudaFree(dc);
+    cudaStreamDestroy(stream);
+    return rc;
   }
   int report_rc = ft_gemm_fp8_abft_report(h, report);
   if (rc == FT_OK) rc = report_rc;

@@ -71,6 +71,22 @@ int main(int argc, char** argv) {
   float input_metadata_ms = report.prepare_input_ms, expected_metadata_ms = report.prepare_expected_ms;
   ft_cache_view cache;
   CLI_FT(ft_gemm_fp8_abft_cache(handle, &cache));
+  // The largest detection threshold of the run, abs + rel * max(1, scale) over every cached row and column scale
+  // (src/s4_cluster_multicast_abft_fp8_gemm.cu:467, 480): a fault below it may pass the reference's checker by design.
+  float threshold_max = 0.0f, threshold_min = 0.0f;
+  {
+    std::vector<float> scales(static_cast<size_t>(tile_count) * 64);
+    float largest = 1.0f, smallest = 3.0e38f;
+    for (int which = 6; which <= 7; ++which) {
+      CLI_FT(ft_gemm_fp8_abft_cache_read(handle, which, scales.data(), scales.size()));
+      for (float v : scales) {
+        largest = std::fmax(largest, v);
+        if (v > 0.0f) smallest = std::fmin(smallest, v);  // zeros pad the boundary tiles
+      }
+    }
+    threshold_max = o.abft_abs_tolerance + o.abft_rel_tolerance * largest;
+    threshold_min = o.abft_abs_tolerance + o.abft_rel_tolerance * std::fmax(1.0f, smallest);
+  }
 
   StageTimings timing = time_stage(handle, d_clean, o, stream);
   // clean reference output and clean counters (src/s4_random_fault_campaign.cu keeps h_c of the clean run)
@@ -92,6 +108,7 @@ int main(int argc, char** argv) {
   };
   std::vector<FaultFailure> failures;
   int double_reported = 0, double_silently_corrected = 0, double_missed = 0;
+  float max_missed_magnitude = 0.0f, min_detected_magnitude = 3.0e38f;
 
   uint32_t state = static_cast<uint32_t>(fault_seed);
   for (int trial = 0; trial < fault_trials + double_trials; ++trial) {
@@ -150,6 +167,8 @@ int main(int argc, char** argv) {
     campaign_correction_attempts += attempted;
     campaign_corrected += recovered;
     campaign_missed += !detected;
+    if (!detected) max_missed_magnitude = std::fmax(max_missed_magnitude, fault_magnitude);
+    if (detected) min_detected_magnitude = std::fmin(min_detected_magnitude, fault_magnitude);
     campaign_detected_not_corrected += detected && !attempted;
     campaign_miscorrected += attempted && !recovered;
     campaign_max_residual = std::fmax(campaign_max_residual, residual);
@@ -204,6 +223,9 @@ int main(int argc, char** argv) {
   std::printf("fault_campaign_detection_rate_percent: %.3f\n", detection_rate);
   std::printf("fault_campaign_correction_rate_percent: %.3f\n", correction_rate);
   std::printf("fault_campaign_max_post_correction_residual: %.6e\n", campaign_max_residual);
+  std::printf("abft_threshold_range: min=%.6e max=%.6e\n", threshold_min, threshold_max);
+  std::printf("fault_campaign_max_missed_magnitude: %.6e\n", max_missed_magnitude);
+  std::printf("fault_campaign_min_detected_magnitude: %.6e\n", campaign_detected > 0 ? min_detected_magnitude : 0.0f);
   float bin_width = (fault_max_value - fault_min_value) / kMagnitudeBins;
   for (int bin = 0; bin < kMagnitudeBins; ++bin) {
     float lower = fault_min_value + bin * bin_width;

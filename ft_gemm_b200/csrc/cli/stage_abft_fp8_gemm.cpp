@@ -9,7 +9,11 @@
 // input seeds), --fault2 (a second fault in the same ABFT tile: the tile must then
 // be reported and left uncorrected), --json (the report once more as one JSON
 // line), --gpus G (rows of A and of C split into G equal bands, one device each,
-// B replicated: no data is exchanged, the counters are added on the host).
+// B replicated: the kernels read local memory only; the one exchange is a single
+// ncclAllGather of the fixed-size per-band report, after which every device holds
+// all G reports with tile ids re-based to the whole product, merged in rank order).
+#include <nccl.h>
+
 #include <cstdarg>
 #include <string>
 #include <utility>
@@ -53,6 +57,15 @@ struct Report {
     std::printf("}\n");
   }
 };
+
+#define CLI_NCCL(call)                                                                              \
+  do {                                                                                              \
+    ncclResult_t result_ = (call);                                                                  \
+    if (result_ != ncclSuccess) {                                                                   \
+      std::fprintf(stderr, "NCCL error %s:%d: %s\n", __FILE__, __LINE__, ncclGetErrorString(result_)); \
+      std::exit(EXIT_FAILURE);                                                                      \
+    }                                                                                               \
+  } while (0)
 
 struct Device {
   int id = 0;
@@ -193,14 +206,51 @@ int main(int argc, char** argv) {
     }
     CLI_FT(ft_gemm_fp8_abft_run(d.handle, d.c, n_faults ? faults : nullptr, n_faults, d.stream));
   }
+  std::vector<ft_report> shards(gpus);
   for (Device& d : devices) {
     CLI_CUDA(cudaSetDevice(d.id));
-    ft_report report;
-    CLI_FT(ft_gemm_fp8_abft_report(d.handle, &report));
-    total.bad_tiles += report.bad_tiles;
-    total.corrected_tiles += report.corrected_tiles;
-    total.multi_fault_tiles += report.multi_fault_tiles;
-    total.max_clean_ratio = std::max(total.max_clean_ratio, report.max_clean_ratio);
+    CLI_FT(ft_gemm_fp8_abft_report(d.handle, &shards[d.id]));
+    CLI_FT(ft_gemm_report_rebase(&shards[d.id], tile_cols, d.row_begin / 64));  // band-local tile ids -> ids of the whole product
+  }
+  float report_gather_ms = 0.0f;
+  if (gpus == 1) {
+    total = shards[0];
+  } else {
+    // One all-gather of the fixed-size report: afterwards every device holds the G reports in rank order.
+    std::vector<ncclComm_t> comms(gpus);
+    std::vector<int> ids(gpus);
+    for (int g = 0; g < gpus; ++g) ids[g] = g;
+    CLI_NCCL(ncclCommInitAll(comms.data(), gpus, ids.data()));
+    std::vector<ft_report*> send(gpus), recv(gpus);
+    for (Device& d : devices) {
+      CLI_CUDA(cudaSetDevice(d.id));
+      CLI_CUDA(cudaMalloc(reinterpret_cast<void**>(&send[d.id]), sizeof(ft_report)));
+      CLI_CUDA(cudaMalloc(reinterpret_cast<void**>(&recv[d.id]), sizeof(ft_report) * gpus));
+      CLI_CUDA(cudaMemcpyAsync(send[d.id], &shards[d.id], sizeof(ft_report), cudaMemcpyHostToDevice, d.stream));
+      CLI_CUDA(cudaEventRecord(d.start, d.stream));
+    }
+    CLI_NCCL(ncclGroupStart());
+    for (Device& d : devices) CLI_NCCL(ncclAllGather(send[d.id], recv[d.id], sizeof(ft_report), ncclChar, comms[d.id], d.stream));
+    CLI_NCCL(ncclGroupEnd());
+    for (Device& d : devices) {
+      CLI_CUDA(cudaSetDevice(d.id));
+      CLI_CUDA(cudaEventRecord(d.stop, d.stream));
+      CLI_CUDA(cudaStreamSynchronize(d.stream));
+      float ms = 0.0f;
+      CLI_CUDA(cudaEventElapsedTime(&ms, d.start, d.stop));
+      report_gather_ms = std::max(report_gather_ms, ms);
+    }
+    // every rank holds the same union; the last device's copy is the one printed (it proves the data travelled)
+    std::vector<ft_report> gathered(gpus);
+    CLI_CUDA(cudaSetDevice(gpus - 1));
+    CLI_CUDA(cudaMemcpy(gathered.data(), recv[gpus - 1], sizeof(ft_report) * gpus, cudaMemcpyDeviceToHost));
+    CLI_FT(ft_gemm_report_merge(gathered.data(), gpus, &total));
+    for (Device& d : devices) {
+      CLI_CUDA(cudaSetDevice(d.id));
+      CLI_CUDA(cudaFree(send[d.id]));
+      CLI_CUDA(cudaFree(recv[d.id]));
+      CLI_NCCL(ncclCommDestroy(comms[d.id]));
+    }
   }
 
   float first_call_total_ms = metadata_prepare_ms + timing.first_ms;
@@ -246,6 +296,14 @@ int main(int argc, char** argv) {
   out.add("bad_tiles", "%d", total.bad_tiles);
   out.add("corrected_tiles", "%d", total.corrected_tiles);
   out.add("multi_fault_tiles", "%d", total.multi_fault_tiles);
+  if (gpus > 1) out.add("report_gather", "ncclAllGather of %zu bytes per device, %.3f ms", sizeof(ft_report), report_gather_ms);
+  for (int i = 0; i < total.n_records; ++i) {  // tile ids of the whole product, rank order
+    const ft_tile_record& r = total.records[i];
+    char key[32];
+    std::snprintf(key, sizeof(key), "fault_record_%d", i);
+    out.add(key, "tile=%d gpu=%d bad_rows=%d bad_cols=%d row=%d col=%d row_delta=%.6e col_delta=%.6e corrected=%d", r.tile,
+            (r.tile / tile_cols) * 64 / rows, r.bad_row_count, r.bad_col_count, r.bad_row, r.bad_col, r.row_delta, r.col_delta, r.corrected);
+  }
   out.add("verification_samples", "%d", verification.checked);
   out.add("sampled_max_absolute_error", "%.6e", verification.max_absolute_error);
   out.add("sampled_max_tolerance_ratio", "%.6e", verification.max_tolerance_ratio);

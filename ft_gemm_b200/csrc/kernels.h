@@ -43,6 +43,8 @@ struct GemmParams {
   // window of C this launch computes (rows a multiple of the tile height, cols of 256); the whole product by default
   int row0, rows, col0, cols;
   float abs_tol, rel_tol;
+  // limit of every device-side wait of this launch, nanoseconds (ft_options::wait_limit_us; 2 s by default)
+  unsigned long long wait_timeout_ns;
   // Tiles are walked in groups of group_rows rows of C, column block by column block inside a group, so that the A panel of
   // a group (group_rows x K bytes) stays in L2 while B streams past it once per group.  The host sizes the panel to 32 MiB,
   // a quarter of the L2, between 1024 and 8192 rows: at K = 8192 that is 4096 rows (measured at 8192^3: 2048 rows -1.6 %,
@@ -96,5 +98,7 @@ cudaError_t configure_abft_gemm();
 cudaError_t launch_abft_gemm(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmParams& params, int grid, bool pair,
                              cudaStream_t stream);
 int abft_gemm_smem_bytes(bool pair);
+// Test hook: one thread waits with mbar_wait_bounded on a barrier nobody arrives on and records the time-out in `report`.
+cudaError_t launch_selftest_wait(DeviceReport* report, unsigned long long limit_ns, cudaStream_t stream);
 
 }  // namespace ftg

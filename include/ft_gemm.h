@@ -30,7 +30,11 @@
  *
  * Every function returns FT_OK (0) or a negative FT_ERR_* code; the text of the
  * last error of the calling thread is available from ft_gemm_last_error().
- * A handle may be used by one host thread at a time.
+ * A handle may be used by one host thread at a time, and its _run / _run_window /
+ * _refresh / _report calls belong to ONE stream at a time: the handle keeps two
+ * report buffers that successive launches use alternately, and _report waits for
+ * the stream of the last launch only.  Launch on another stream only after the
+ * previous stream's work on the handle has finished (an event or _report).
  */
 #ifndef FT_GEMM_H
 #define FT_GEMM_H
@@ -64,7 +68,10 @@ typedef struct {
   int exact_prepare; /* 0 (default): the expected checksums are computed on the tensor cores (band sums split into exact
                         E4M3 digits; equal to the reference's values up to FP32 accumulation order); 1: on the CUDA
                         cores in the reference's summation order (src/s4:264-282), bit-identical to its cache, ~10x slower */
-  int reserved[3];
+  int wait_limit_us; /* 0 (default): a device-side wait of the fused GEMM kernel gives up after 2 s; >0: after this many
+                        microseconds.  A kernel whose wait gave up leaves through its normal teardown and the run is
+                        reported as FT_ERR_TIMEOUT; nothing traps or spins without limit. */
+  int reserved[2];
 } ft_options;
 
 /* A test fault: `value` is added to the accumulator element (row, col) of ABFT
@@ -183,6 +190,30 @@ int ft_gemm_fp8_abft_run_profiled(ft_gemm_handle* handle, float* c, unsigned lon
  * sets out->status) when a device-side wait gave up. */
 int ft_gemm_fp8_abft_report(ft_gemm_handle* handle, ft_report* out);
 
+/* Multi-GPU reports (the reference is single-GPU, src/s4:558; its two counters
+ * become one report per row band).  _report_rebase turns the band-local tile ids of
+ * a shard's report into ids of the whole product: the band starts at tile row
+ * first_tile_row (= first row of the band / 64) of a product with tile_cols =
+ * ceil(N/64) tile columns.  _report_merge forms the union of n re-based reports in
+ * the order given (rank order): counters added, records concatenated up to
+ * FT_MAX_RECORDS (the rest counted in records_dropped), status = the first
+ * non-zero status, max_clean_ratio / prepare times = the maximum.  Both are plain
+ * host functions: whoever moves the fixed-size ft_report between ranks (one
+ * ncclAllGather in the stage program, torch.distributed in the Python host) calls
+ * them on the gathered array. */
+int ft_gemm_report_rebase(ft_report* report, int tile_cols, int first_tile_row);
+int ft_gemm_report_merge(const ft_report* shards, int n, ft_report* out);
+
+/* Test hook for the failure path (no counterpart in the reference, whose kernels
+ * wait without limit): launches a one-thread kernel that waits, with the same
+ * bounded-wait routine every kernel of this library uses, on a barrier nobody
+ * arrives on.  After limit_us microseconds the wait gives up and the kernel
+ * records the time-out in the handle's current report exactly as the fused
+ * kernel's teardown does, so the next _report returns FT_ERR_TIMEOUT.  The kernel
+ * touches no tensor memory, issues no copy and no MMA; the context stays usable
+ * and the next _run starts a clean report. */
+int ft_gemm_fp8_abft_selftest_wait(ft_gemm_handle* handle, int limit_us, void* stream);
+
 /* Frees the cache (the reference's cudaFree block, src/s4:771-783). */
 int ft_gemm_fp8_abft_destroy(ft_gemm_handle* handle);
 
@@ -220,16 +251,24 @@ int ft_gemm_generate_fp8(void* out_e4m3, size_t count, uint32_t seed, int dist, 
 /* No counterpart in the reference (its programs allocate everything up front in
  * main()).  Fills the four expected-checksum arrays for A[M,K], B[N,K] exactly as
  * ft_gemm_fp8_abft_prepare does, but allocates nothing: the caller passes the
- * outputs (each (M/64)*(N/64)*64 floats of device memory) and the intermediate
- * band sums are kept in an array built into the library, 16 MiB on every GPU that
- * loads it.  It exists for callers that cannot call cudaMalloc where they need
- * new checksums -- a serving loop that refreshes them whenever A changes while
- * the framework's allocator owns the device memory, or that cannot take the
- * device-wide stall cudaMalloc causes.
- *   - Shapes with 2*(M/64 + N/64)*K*4 bytes > FT_NOALLOC_MAX_SCRATCH_BYTES are
- *     rejected with FT_ERR_INVALID (8192^3 fits exactly); use _prepare for them.
+ * outputs and the intermediate band sums are kept in an array built into the
+ * library, 16 MiB on every GPU that loads it.  It exists for callers that cannot
+ * call cudaMalloc where they need new checksums -- a serving loop that refreshes
+ * them whenever A changes while the framework's allocator owns the device memory,
+ * or that cannot take the device-wide stall cudaMalloc causes.
+ *   - Any positive M and N, K % 16 == 0, A and B 16-byte aligned.  Each of the
+ *     four outputs holds ceil(M/64) * ceil(N/64) * 64 floats of device memory
+ *     (boundary tiles count in full; entries past the last valid column are
+ *     written as zeros): M = 100, N = 256 needs 2 * 4 * 64 = 512 floats each.
+ *   - Shapes with 2*(ceil(M/64) + ceil(N/64))*K*4 bytes > FT_NOALLOC_MAX_SCRATCH_BYTES
+ *     are rejected with FT_ERR_INVALID (8192^3 fits exactly); use _prepare for them.
  *   - The first call on each device looks the array's device address up (with
- *     that device current); make that first call before any stream capture.
+ *     that device current).  Under lazy module loading that lookup is also the
+ *     moment the 16 MiB are reserved on the device, and it can fail with
+ *     FT_ERR_CUDA when no memory is left: make the first call at start-up, before
+ *     the framework's allocator takes the device memory and before any stream
+ *     capture (a call on a tiny shape will do).  The address is kept per device for
+ *     the life of the process and does not survive cudaDeviceReset.
  *   - All calls on a device share the array, which keeps the previous call's
  *     contents: every used element is rewritten before it is read, but two calls
  *     whose kernels overlap on the GPU (different streams) race on it. */

@@ -517,6 +517,15 @@ int ftq_num_threads(void) {
 #endif
 }
 
+/* Number of OpenMP threads of the following calls (a launcher may have set OMP_NUM_THREADS=1 for its children). */
+void ftq_set_num_threads(int threads) {
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+#else
+  (void)threads;
+#endif
+}
+
 void ftq_full_pass(const uint8_t* a, const uint8_t* b, float* c, int m_rows, int n, int k, int tile, float abs_tol,
                    float rel_tol, double* seconds3, ftq_check_summary* summary) {
   int tile_rows = m_rows / tile, tile_cols = (n + tile - 1) / tile;

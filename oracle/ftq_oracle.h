@@ -124,6 +124,7 @@ void ftq_verify_samples(const uint8_t* a, const uint8_t* b, const float* c, int 
 void ftq_full_pass(const uint8_t* a, const uint8_t* b, float* c, int m_rows, int n, int k, int tile, float abs_tol,
                    float rel_tol, double* seconds3, ftq_check_summary* summary);
 int ftq_num_threads(void);
+void ftq_set_num_threads(int threads);
 
 #ifdef __cplusplus
 }

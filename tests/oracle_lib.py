@@ -168,6 +168,9 @@ class Oracle:
     def num_threads(self):
         return int(self.lib.ftq_num_threads())
 
+    def set_num_threads(self, threads):
+        self.lib.ftq_set_num_threads(int(threads))
+
 
 _oracle = None
 

@@ -82,3 +82,32 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_abi, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _abi.load()
+
+
+def test_report_rebase_and_merge_are_host_functions():
+    """The multi-GPU report plumbing of the C-ABI needs no device: tile ids of a band become ids of the whole product,
+    the union keeps rank order, adds the counters and counts what does not fit."""
+    import ft_gemm_b200 as ftg
+    from ft_gemm_b200 import _abi
+    lib = ftg.load()
+    tile_cols = 8
+    shards = (_abi.FtReport * 3)()
+    for rank in range(3):
+        r = shards[rank]
+        r.bad_tiles, r.corrected_tiles, r.multi_fault_tiles = rank + 1, rank, 1
+        r.n_records = 30
+        r.max_clean_ratio = 0.1 * (rank + 1)
+        r.prepare_ms = 1.0 + rank
+        for i in range(30):
+            r.records[i] = _abi.FtTileRecord(i, 1, 1, i, i + 1, 0.5, 0.25, 1)
+        assert lib.ft_gemm_report_rebase(ctypes.byref(r), tile_cols, 4 * rank) == ftg.FT_OK
+        assert [r.records[i].tile for i in range(3)] == [32 * rank + i for i in range(3)]
+    shards[1].status = ftg.FT_ERR_TIMEOUT
+    total = _abi.FtReport()
+    assert lib.ft_gemm_report_merge(shards, 3, ctypes.byref(total)) == ftg.FT_OK
+    assert (total.status, total.bad_tiles, total.corrected_tiles, total.multi_fault_tiles) == (ftg.FT_ERR_TIMEOUT, 6, 3, 3)
+    assert total.n_records == _abi.FT_MAX_RECORDS and total.records_dropped == 90 - _abi.FT_MAX_RECORDS
+    assert [total.records[i].tile for i in (0, 29, 30, 59, 60, 63)] == [0, 29, 32, 61, 64, 67]
+    assert abs(total.max_clean_ratio - 0.3) < 1e-6 and total.prepare_ms == 3.0
+    assert lib.ft_gemm_report_merge(shards, 0, ctypes.byref(total)) == ftg.FT_ERR_INVALID
+    assert lib.ft_gemm_report_rebase(None, tile_cols, 0) == ftg.FT_ERR_INVALID
