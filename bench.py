@@ -444,16 +444,18 @@ def main():
         c_pin = torch.empty((n, m_rank), dtype=torch.float32).pin_memory()
         # plain pinned copies alone, one at a time: the floor the call cannot beat on this host at this rank count
         d_tmp = torch.empty_like(c)
-        barrier()
-        t0 = time.perf_counter()
-        a.copy_(a_pin, non_blocking=True)
-        b.copy_(b_pin, non_blocking=True)
-        barrier()
-        h2d_s = max_over_ranks(time.perf_counter() - t0)
-        t0 = time.perf_counter()
-        c_pin.copy_(d_tmp, non_blocking=True)
-        barrier()
-        d2h_s = max_over_ranks(time.perf_counter() - t0)
+        h2d_s = d2h_s = float("inf")
+        for _ in range(3):  # the first pass also pays for mapping the pinned pages; the best of three is the floor
+            barrier()
+            t0 = time.perf_counter()
+            a.copy_(a_pin, non_blocking=True)
+            b.copy_(b_pin, non_blocking=True)
+            barrier()
+            h2d_s = min(h2d_s, max_over_ranks(time.perf_counter() - t0))
+            t0 = time.perf_counter()
+            c_pin.copy_(d_tmp, non_blocking=True)
+            barrier()
+            d2h_s = min(d2h_s, max_over_ranks(time.perf_counter() - t0))
         del d_tmp
         host = ftg.HostAbftGemm(m_rank, n, k)
         host(a_pin, b_pin, c_pin)  # creates device buffers and the cache
