@@ -4,9 +4,11 @@
 // 456-499) in register form.
 //
 //   row checksum    sum of the thread's 64 values (four interleaved partial sums)
-//   column checksum transpose-reduce butterfly over the warp's 32 rows, combined
-//                   with the partner warp (the other 32 rows of the tile) through
-//                   shared memory; the caller synchronises the two warps
+//   column checksum transpose-reduce butterfly over the warp's 32 rows (from the row
+//                   registers, or from a second read of tensor memory in the
+//                   fragment layout), combined with the partner warp (the other 32
+//                   rows of the tile) through shared memory; the caller
+//                   synchronises the two warps
 //   decision        bad <=> |expected - actual| > abs + rel * max(1, scale)
 //   correction      iff exactly one bad row and one bad column:
 //                   v[row][col] += 0.5 * (row_delta + col_delta), applied by the caller
@@ -40,11 +42,14 @@ struct TileDecision {
   bool corrected;
 };
 
-// The check is split in two so that a caller can overlap the partner exchange with other work (a second tile, the
-// row maximum): abft_tile_sums() by each of the two warps (64 threads) that own the tile's rows, then a barrier over
-// those 64 threads, then abft_tile_decide().  `half` says which 32 rows this warp holds.  `sc` must not be written
-// again before both warps have finished abft_tile_decide().
-__device__ __forceinline__ void abft_tile_sums(const float (&v)[64], int lane, int half, TileScratch& sc, float exp_row, float scale_row,
+// The check is split so that a caller can overlap the partner exchange with other work (a second tile, the row
+// maximum): the row part and the column part by each of the two warps (64 threads) that own the tile's rows, then a
+// barrier over those 64 threads, then abft_tile_decide().  `half` says which 32 rows this warp holds.  `sc` must not
+// be written again before both warps have finished abft_tile_decide().
+
+// Row part: the thread's row checksum against its cached expectation; publishes the warp's bad-row count, its lowest
+// bad row and that row's delta.
+__device__ __forceinline__ void abft_tile_rows(const float (&v)[64], int lane, int half, TileScratch& sc, float exp_row, float scale_row,
                                                float abs_tol, float rel_tol, float& max_ratio) {
   // Four interleaved partial sums in two packed FP32 pairs: 32 dependent additions become two chains of 15.  (The score
   // products come from the tensor core, whose own summation order is not defined, so no particular order is owed here.)
@@ -61,7 +66,18 @@ __device__ __forceinline__ void abft_tile_sums(const float (&v)[64], int lane, i
   const float row_thr = __fmaf_rn(rel_tol, fmaxf(1.0f, scale_row), abs_tol);
   const bool row_bad = fabsf(row_delta) > row_thr;
   if (!row_bad) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(row_delta), row_thr));
+  const uint32_t row_mask = __ballot_sync(0xffffffffU, row_bad);
+  const int first_lane = row_mask != 0 ? __ffs(row_mask) - 1 : 0;
+  const float first_delta = __shfl_sync(0xffffffffU, row_delta, first_lane);
+  if (lane == 0) {
+    sc.rows[half].count = __popc(row_mask);
+    sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
+    sc.rows[half].delta = first_delta;
+  }
+}
 
+// Column part from registers (one thread = one row): transpose-reduce butterfly over the warp's 32 rows, 63 shuffles.
+__device__ __forceinline__ void abft_tile_cols_from_rows(const float (&v)[64], int lane, int half, TileScratch& sc) {
   float w[32];
   {
     const bool upper = (lane & 16) != 0;
@@ -85,14 +101,47 @@ __device__ __forceinline__ void abft_tile_sums(const float (&v)[64], int lane, i
     }
   }
   *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(w[0], w[1]);
-  const uint32_t row_mask = __ballot_sync(0xffffffffU, row_bad);
-  const int first_lane = row_mask != 0 ? __ffs(row_mask) - 1 : 0;
-  const float first_delta = __shfl_sync(0xffffffffU, row_delta, first_lane);
-  if (lane == 0) {
-    sc.rows[half].count = __popc(row_mask);
-    sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
-    sc.rows[half].delta = first_delta;
+}
+
+// Column part straight from tensor memory: the warp's 32 lanes x 64 columns at `taddr` (lane field = first lane of the
+// warp's quarter) are read a second time in the 16-lane x 256-bit fragment layout, in which a thread holds two adjacent
+// columns of four rows per 8-column block.  Three packed additions per block fold the four rows, then a
+// transpose-reduce over the eight row groups (lane bits 2..4) leaves the sums of columns 2*lane and 2*lane+1 in each
+// thread: 14 shuffles instead of 63, and the additions work on FP32 pairs.
+__device__ __forceinline__ void abft_tile_cols_from_tmem(uint32_t taddr, int lane, int half, TileScratch& sc) {
+  float a[32], b[32];
+  tmem_ld_16x256b_x8(taddr, a);                // lanes +0 .. +15
+  tmem_ld_16x256b_x8(taddr + (16u << 16), b);  // lanes +16 .. +31
+  tmem_wait_ld();
+  unsigned long long s[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    s[k] = add_f32x2(add_f32x2(pack_f32x2(a[4 * k], a[4 * k + 1]), pack_f32x2(a[4 * k + 2], a[4 * k + 3])),
+                     add_f32x2(pack_f32x2(b[4 * k], b[4 * k + 1]), pack_f32x2(b[4 * k + 2], b[4 * k + 3])));
   }
+  int n = 4;
+#pragma unroll
+  for (int off = 16; off >= 4; off >>= 1) {
+    const bool up = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      const unsigned long long send = up ? s[i] : s[i + n];
+      const unsigned long long keep = up ? s[i + n] : s[i];
+      s[i] = add_f32x2(keep, shfl_xor_f32x2(send, off));
+    }
+    n >>= 1;
+  }
+  // block index kept = lane >> 2, columns 8*(lane>>2) + 2*(lane&3) + {0,1} = 2*lane + {0,1}
+  float c0, c1;
+  unpack_f32x2(s[0], c0, c1);
+  *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(c0, c1);
+}
+
+// Row and column parts from registers (the form the kernels with one thread per whole row use).
+__device__ __forceinline__ void abft_tile_sums(const float (&v)[64], int lane, int half, TileScratch& sc, float exp_row, float scale_row,
+                                               float abs_tol, float rel_tol, float& max_ratio) {
+  abft_tile_rows(v, lane, half, sc, exp_row, scale_row, abs_tol, rel_tol, max_ratio);
+  abft_tile_cols_from_rows(v, lane, half, sc);
 }
 
 // The decision is the same in all 64 threads.  Nothing is corrected here: the caller applies

@@ -302,11 +302,12 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         // ---- pass 1: verify this thread's 64x64 score tile, take the half's row maximum
         float local_max = -INFINITY;
         {
+          abft_tile_cols_from_tmem(s_addr, lane, half, scratch);
           float v[64];
           tmem_ld_32x32b_x32(s_addr, v);
           tmem_ld_32x32b_x32(s_addr + 32, v + 32);
           tmem_wait_ld();
-          abft_tile_sums(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
+          abft_tile_rows(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
           if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
