@@ -26,14 +26,16 @@ class FtAttnOptions(ctypes.Structure):
 
 class FtAttnFault(ctypes.Structure):
     _fields_ = [("stage", ctypes.c_int), ("batch", ctypes.c_int), ("head", ctypes.c_int), ("query", ctypes.c_int),
-                ("index", ctypes.c_int), ("value", ctypes.c_float)]
+                ("index", ctypes.c_int), ("value", ctypes.c_float), ("query2", ctypes.c_int), ("index2", ctypes.c_int),
+                ("value2", ctypes.c_float)]
 
 
 class FtAttnReport(ctypes.Structure):
     _fields_ = [("status", ctypes.c_int), ("score_detected", ctypes.c_int), ("score_corrected", ctypes.c_int),
                 ("score_uncorrected", ctypes.c_int), ("pv_detected", ctypes.c_int), ("pv_corrected", ctypes.c_int),
                 ("failed_rows", ctypes.c_int), ("softmax_detected", ctypes.c_int), ("softmax_corrected", ctypes.c_int),
-                ("softmax_replayed", ctypes.c_int), ("n_records", ctypes.c_int), ("max_score_noise", ctypes.c_float),
+                ("softmax_replayed", ctypes.c_int), ("score_replayed", ctypes.c_int), ("n_records", ctypes.c_int),
+                ("max_score_noise", ctypes.c_float),
                 ("prepare_ms", ctypes.c_float), ("records", _abi.FtTileRecord * 16)]
 
 
@@ -52,6 +54,7 @@ class AttnReport:
     max_score_noise: float
     prepare_ms: float
     records: List[TileRecord] = field(default_factory=list)
+    score_replayed: int = 0
 
 
 _bound = False
@@ -93,13 +96,15 @@ def gather_attention_reports(report: "AttnReport", first_head: int, heads_per_ba
     bands = seq // 64
     per_head = bands * bands
     counters = [report.status, report.score_detected, report.score_corrected, report.score_uncorrected, report.pv_detected,
-                report.pv_corrected, report.failed_rows, report.softmax_detected, report.softmax_corrected, report.softmax_replayed]
-    mine = torch.zeros(12 + 8 * 16, dtype=torch.float64)
-    mine[:10] = torch.tensor(counters, dtype=torch.float64)
-    mine[10] = report.max_score_noise
-    mine[11] = len(report.records)
+                report.pv_corrected, report.failed_rows, report.softmax_detected, report.softmax_corrected, report.softmax_replayed,
+                report.score_replayed]
+    head = len(counters) + 2
+    mine = torch.zeros(head + 8 * 16, dtype=torch.float64)
+    mine[:11] = torch.tensor(counters, dtype=torch.float64)
+    mine[11] = report.max_score_noise
+    mine[12] = len(report.records)
     for i, r in enumerate(report.records[:16]):
-        mine[12 + 8 * i:20 + 8 * i] = torch.tensor([r.tile + first_head * per_head, r.bad_row_count, r.bad_col_count, r.bad_row, r.bad_col,
+        mine[head + 8 * i:head + 8 + 8 * i] = torch.tensor([r.tile + first_head * per_head, r.bad_row_count, r.bad_col_count, r.bad_row, r.bad_col,
                                                     r.row_delta, r.col_delta, r.corrected], dtype=torch.float64)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         if device is not None:
@@ -110,15 +115,16 @@ def gather_attention_reports(report: "AttnReport", first_head: int, heads_per_ba
     else:
         bufs = [mine]
     total = torch.stack(bufs)
-    sums = total[:, :10].sum(dim=0)
+    sums = total[:, :11].sum(dim=0)
     records = []
     for b in bufs:
-        for i in range(int(b[11].item())):
-            f = b[12 + 8 * i:20 + 8 * i].tolist()
+        for i in range(int(b[12].item())):
+            f = b[head + 8 * i:head + 8 + 8 * i].tolist()
             records.append(TileRecord(int(f[0]), int(f[1]), int(f[2]), int(f[3]), int(f[4]), f[5], f[6], int(f[7])))
     records.sort(key=lambda r: r.tile)
     status = int(total[:, 0].min().item()) if (total[:, 0] != 0).any() else 0  # any rank's error code (they are negative)
-    return AttnReport(status, *(int(x) for x in sums[1:10].tolist()), float(total[:, 10].max().item()), report.prepare_ms, records[:16])
+    return AttnReport(status, *(int(x) for x in sums[1:10].tolist()), float(total[:, 11].max().item()), report.prepare_ms, records[:16],
+                      int(sums[10].item()))
 
 
 class FtAttention:
@@ -151,9 +157,9 @@ class FtAttention:
     def new_output(self) -> torch.Tensor:
         return torch.empty(self.q.shape, dtype=torch.float32, device=self.q.device)
 
-    def run(self, out: torch.Tensor, fault: Optional[Tuple[int, int, int, int, int, float]] = None,
-            stream: Optional[torch.cuda.Stream] = None):
-        """fault = (stage, batch, head, query, index, value) with the reference's stage numbers (1 score, 4 output)."""
+    def run(self, out: torch.Tensor, fault: Optional[Tuple] = None, stream: Optional[torch.cuda.Stream] = None):
+        """fault = (stage, batch, head, query, index, value) with the reference's stage numbers (1 score, 4 output); a score
+        fault may carry a second one in the same head as three more entries (query2, index2, value2)."""
         if not out.is_cuda or out.dtype != torch.float32 or not out.is_contiguous() or out.shape != self.q.shape:
             raise ValueError("out must be a contiguous float32 CUDA tensor shaped like Q")
         cf = FtAttnFault(*fault) if fault is not None else None
@@ -171,7 +177,7 @@ class FtAttention:
                               r.corrected) for r in rep.records[:rep.n_records]]
         return AttnReport(rep.status, rep.score_detected, rep.score_corrected, rep.score_uncorrected, rep.pv_detected,
                           rep.pv_corrected, rep.failed_rows, rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed,
-                          rep.max_score_noise, rep.prepare_ms, records)
+                          rep.max_score_noise, rep.prepare_ms, records, rep.score_replayed)
 
     def close(self):
         if getattr(self, "handle", None) is not None and self.handle.value:

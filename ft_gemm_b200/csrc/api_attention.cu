@@ -68,7 +68,8 @@ struct ft_attn_handle {
   float *expected_rows = nullptr, *expected_cols = nullptr, *row_scales = nullptr, *col_scales = nullptr;
   float *v_sum = nullptr, *v_weighted = nullptr;
   AttnDeviceReport* report = nullptr;
-  CUtensorMap tmap_q{}, tmap_k{}, tmap_vt{};
+  CUtensorMap tmap_q{}, tmap_k{}, tmap_vt{};  // tmap_vt: boxes of D rows (whole-row kernel)
+  CUtensorMap tmap_vt_ext{};                  // boxes of D + kAttnVExtra rows: V^T with its checksum rows (split-row kernel)
   // tensor-core prepare: FP16 pieces of the band sums (one allocation) and their maps
   void* planes = nullptr;
   void *q_ws = nullptr, *q_wm = nullptr, *k_ws = nullptr, *k_wm = nullptr;
@@ -186,7 +187,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   const size_t floats = 4 * band_floats + 4 * checks + 2 * key_floats;
   h->cache_bytes = floats * sizeof(float);
   cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&h->cache), h->cache_bytes);
-  if (err == cudaSuccess) err = cudaMalloc(&h->vt, bh * seq * head_dim * 2);
+  if (err == cudaSuccess) err = cudaMalloc(&h->vt, bh * seq * (head_dim + kAttnVExtra) * 2);
   if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->report), sizeof(AttnDeviceReport));
   if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&h->prepare_status), sizeof(int));
   const int nbands = seq / 64;
@@ -213,7 +214,8 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   int rc = make_f16_map(&h->tmap_q, q, bh * seq, head_dim);
   if (rc == FT_OK) rc = make_f16_map(&h->tmap_k, k, bh * seq, head_dim);
-  if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt, h->vt, bh * head_dim, seq, static_cast<unsigned>(head_dim));
+  if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt, h->vt, bh * (head_dim + kAttnVExtra), seq, static_cast<unsigned>(head_dim));
+  if (rc == FT_OK) rc = make_f16_map(&h->tmap_vt_ext, h->vt, bh * (head_dim + kAttnVExtra), seq, static_cast<unsigned>(head_dim + kAttnVExtra));
   if (rc == FT_OK && opts.exact_prepare == 0) {
     __half* cursor16 = static_cast<__half*>(h->planes);
     h->q_ws = cursor16, cursor16 += ws_elems;
@@ -281,6 +283,8 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   params.expected_cols = h->expected_cols;
   params.row_scales = h->row_scales;
   params.col_scales = h->col_scales;
+  params.q = h->q;
+  params.k = h->k;
   params.v_sum = h->v_sum;
   params.v_weighted = h->v_weighted;
   params.out = out;
@@ -320,9 +324,18 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
     params.fault_query = fault->query;
     params.fault_index = fault->index;
     params.fault_value = fault->value;
+    if (fault->stage == FT_ATTN_FAULT_SCORE && fault->value2 != 0.0f) {
+      if (fault->query2 < 0 || fault->query2 >= h->valid_seq || fault->index2 < 0 || fault->index2 >= h->valid_seq ||
+          (h->options.causal != 0 && fault->index2 > fault->query2)) {
+        return noalloc_fail(FT_ERR_INVALID, "the second fault target is outside the tensor (or beyond the causal diagonal)");
+      }
+      params.fault2_query = fault->query2;
+      params.fault2_index = fault->index2;
+      params.fault2_value = fault->value2;
+    }
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  ATTN_CUDA(cudaMemsetAsync(h->report, 0, 48, stream));
+  ATTN_CUDA(cudaMemsetAsync(h->report, 0, 64, stream));  // the counters; the records are guarded by record_count
   // The split-row kernel (two threads per query row) is the default; the whole-row kernel carries the softmax-stage
   // protection and can be selected for comparison with FT_ATTENTION_KERNEL=row in the environment.
   static const bool force_row = [] {
@@ -332,7 +345,7 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   if (params.protect_softmax != 0 || (force_row && h->dim == 128)) {
     ATTN_CUDA(launch_attention(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
   } else {
-    ATTN_CUDA(launch_attention_split(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
+    ATTN_CUDA(launch_attention_split(h->tmap_q, h->tmap_k, h->tmap_vt_ext, params, h->batch * h->heads, stream));
   }
   h->last_stream = stream;
   return FT_OK;
@@ -357,6 +370,7 @@ int ft_attention_fp16_abft_report(ft_attn_handle* h, ft_attn_report* out) {
   out->softmax_detected = dev.softmax_detected;
   out->softmax_corrected = dev.softmax_corrected;
   out->softmax_replayed = dev.softmax_replayed;
+  out->score_replayed = dev.score_replayed;
   out->n_records = std::min(dev.record_count, 16);
   std::memcpy(&out->max_score_noise, &dev.max_noise_bits, sizeof(float));
   std::copy(dev.records, dev.records + out->n_records, out->records);

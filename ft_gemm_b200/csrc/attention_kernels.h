@@ -7,6 +7,13 @@
 
 namespace ftg {
 
+// V^T carries, below the D rows of a head, kAttnVExtra rows of per-key constants for the output-stage check:
+// row D: ones; D+1, D+2: FP16 hi and lo pieces of sum_d V[key, d]; D+3, D+4: hi and lo pieces of
+// sum_d w_d V[key, d] / kAttnVWeightScale (w_d = 2d - (D-1); the division keeps the value inside the FP16 range);
+// the rest zeros.  As extra columns of the PV product they give l and the two expected output projections.
+constexpr int kAttnVExtra = 16;
+constexpr float kAttnVWeightScale = 128.0f;
+
 struct AttnDeviceReport {
   int status;
   int score_detected;
@@ -20,6 +27,8 @@ struct AttnDeviceReport {
   int softmax_detected;
   int softmax_corrected;
   int softmax_replayed;
+  int score_replayed;
+  int pad[3];  // the counters above (64 bytes with this padding) are cleared before every run
   ft_tile_record records[16];
 };
 
@@ -28,6 +37,8 @@ struct AttnParams {
   const float* expected_cols;
   const float* row_scales;
   const float* col_scales;
+  const void* q;  // [B*H][N][D] FP16: read directly only when a score tile is replayed on the CUDA cores
+  const void* k;
   const float* v_sum;       // [B*H][N]
   const float* v_weighted;  // [B*H][N]
   float* out;               // [B*H][N][D]
@@ -41,6 +52,8 @@ struct AttnParams {
   float scale_log2;  // log2(e) / sqrt(D)
   int fault_stage, fault_bh, fault_query, fault_index;
   float fault_value;
+  int fault2_query, fault2_index;  // a second score fault in the same (batch, head); active when fault2_value != 0
+  float fault2_value;
 };
 
 cudaError_t launch_attn_prepare_v(const void* v, void* vt, float* v_sum, float* v_weighted, int batch_heads, int seq, int dim,

@@ -189,6 +189,7 @@ int main(int argc, char** argv) {
   std::printf("fault_target: batch=%d head=%d query=%d index=%d delta=%+.6e\n", fault_batch, fault_head, fault_query, fault_index, fault_value);
   std::printf("score_detected: %d\n", report.score_detected);
   std::printf("score_corrected: %d\n", report.score_corrected);
+  std::printf("score_replayed: %d\n", report.score_replayed);
   std::printf("score_uncorrected: %d\n", report.score_uncorrected);
   std::printf("score_checksum_noise_ratio: %.6e\n", report.max_score_noise);
   std::printf("softmax_protection: %s\n", opt.protect_softmax ? "on" : "off");

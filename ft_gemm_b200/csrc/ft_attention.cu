@@ -27,6 +27,7 @@
 #include <stdint.h>
 
 #include "abft_tile_check.cuh"
+#include "attention_device.cuh"
 #include "attention_kernels.h"
 #include "sm100_ptx.cuh"
 
@@ -49,6 +50,7 @@ struct AttnShared {
   int abort_flag;
   float2 v_meta[kAttnQTiles][2][kAttnTile];  // [query tile][parity][key]: {sum_d V, sum_d w_d V}
   TileScratch scratch[kAttnQTiles][2][2];    // [query tile][row pair][parity]
+  TileScratch replay_scratch[kAttnQTiles][2];  // [query tile][row pair]: second check of a replayed score tile
 };
 
 // Q (2 tiles), K, V^T, P (2 tiles)
@@ -86,11 +88,27 @@ __global__ void __launch_bounds__(256) attn_prepare_v_kernel(const __half* __res
     }
     v_sum[static_cast<size_t>(bh) * seq + key0 + threadIdx.x] = sum;
     v_weighted[static_cast<size_t>(bh) * seq + key0 + threadIdx.x] = weighted;
+    // The checksum rows below the head's D rows of V^T (see kAttnVExtra): ones, then hi and lo FP16 pieces of the two
+    // sums, so that the PV product accumulates l and both expected projections.  hi + lo carries 22 bits of the FP32
+    // value; values beyond the FP16 range saturate (the check then reports the rows instead of passing them).
+    __half* extra = vt + (static_cast<size_t>(bh) * (dim + kAttnVExtra) + dim) * seq + key0 + threadIdx.x;
+    const float scaled = weighted * (1.0f / kAttnVWeightScale);
+    const float clamp = 65504.0f;
+    const __half sum_hi = __float2half_rn(fminf(fmaxf(sum, -clamp), clamp));
+    const __half sum_lo = __float2half_rn(sum - __half2float(sum_hi));
+    const __half weighted_hi = __float2half_rn(fminf(fmaxf(scaled, -clamp), clamp));
+    const __half weighted_lo = __float2half_rn(scaled - __half2float(weighted_hi));
+    extra[0] = __float2half_rn(1.0f);
+    extra[static_cast<size_t>(1) * seq] = sum_hi;
+    extra[static_cast<size_t>(2) * seq] = sum_lo;
+    extra[static_cast<size_t>(3) * seq] = weighted_hi;
+    extra[static_cast<size_t>(4) * seq] = weighted_lo;
+    for (int e = 5; e < kAttnVExtra; ++e) extra[static_cast<size_t>(e) * seq] = __float2half_rn(0.0f);
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int d = warp; d < dim; d += 8) {
     const __half2 pair = __halves2half2(tile[2 * lane][d], tile[2 * lane + 1][d]);
-    *reinterpret_cast<__half2*>(vt + (static_cast<size_t>(bh) * dim + d) * seq + key0 + 2 * lane) = pair;
+    *reinterpret_cast<__half2*>(vt + (static_cast<size_t>(bh) * (dim + kAttnVExtra) + d) * seq + key0 + 2 * lane) = pair;
   }
 }
 
@@ -281,8 +299,8 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         const uint32_t ph = j & 1;
         if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kAttnTimeoutNs)) break;
         mbar_arrive_expect_tx(&sh.v_full, kAttnTileBytes);
-        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kAttnTile, bh * kAttnTile);
-        tma_load_2d(smem_v + kAttnSlabBytes, &tmap_vt, &sh.v_full, j * kAttnTile + 64, bh * kAttnTile);
+        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kAttnTile, bh * (kAttnTile + kAttnVExtra));  // the D rows of the head; its checksum rows are skipped
+        tma_load_2d(smem_v + kAttnSlabBytes, &tmap_vt, &sh.v_full, j * kAttnTile + 64, bh * (kAttnTile + kAttnVExtra));
       }
     } else if (warp == 1 && elect_one()) {
       // ------------------------------------------------------------- MMA issuer
@@ -357,6 +375,8 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       uint8_t* p_tile = smem_p + t * kAttnTileBytes;
       const bool fault_here = p.fault_bh == bh && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kAttnTile;
       const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE;
+      const bool score_fault2 = p.fault_bh == bh && p.fault_stage == FT_ATTN_FAULT_SCORE && p.fault2_value != 0.0f &&
+                                p.fault2_query >= q_tile0 && p.fault2_query < q_tile0 + kAttnTile;
       const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT;
       const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
 
@@ -399,6 +419,9 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         // test hook: the fault enters the accumulator itself, before any checksum
         if (score_fault && p.fault_index / kAttnTile == j && fault_row / 32 == quarter) {
           tmem_add_to_element(s_addr + p.fault_index % kAttnTile, lane, fault_row % 32, p.fault_value);
+        }
+        if (score_fault2 && p.fault2_index / kAttnTile == j && (p.fault2_query - q_tile0) / 32 == quarter) {
+          tmem_add_to_element(s_addr + p.fault2_index % kAttnTile, lane, (p.fault2_query - q_tile0) % 32, p.fault2_value);
         }
 
         // ---- pass 1: verify both 64x64 score tiles of this thread's band, track the row maximum.  Both halves are
@@ -447,14 +470,37 @@ ft_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           const TileDecision d = abft_tile_decide(lane, sh.scratch[t][pair][c], exp_col0[c], exp_col1[c], scale_col0[c], scale_col1[c],
                                                   p.score_abs_tol, p.score_rel_tol, max_ratio);
           if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps of the band
+            bool replayed = false;
             if (d.corrected && d.bad_row / 32 == half) {
               // src/s4:493-497 on the accumulator itself: pass 2 reads the corrected score back
               tmem_add_to_element(s_addr + c * 64 + d.bad_col, lane, d.bad_row % 32, 0.5f * (d.row_delta + d.col_delta));
               reload_row = true;
             }
+            if (!d.corrected) {
+              // The fault cannot be located: the band's 64 x 64 scores are recomputed without the tensor core
+              // (src/ft_flash_attention_a14.cu:935-959), checked again and put back into the accumulator for pass 2.
+              // Waits of this kernel are abandoned by whole warpgroups, so the two warps of the band can meet at their
+              // named barrier here as well.
+              float rv[64];
+              const __half* q_row = static_cast<const __half*>(p.q) + (static_cast<size_t>(row_base) + q_tile0 + row_in_tile) * kAttnTile;
+              const __half* k_tile = static_cast<const __half*>(p.k) + (static_cast<size_t>(row_base) + j * kAttnTile + c * 64) * kAttnTile;
+              replay_score_row<kAttnTile>(q_row, k_tile, rv);
+              TileScratch& again = sh.replay_scratch[t][pair];
+              float ignored = 0.0f;
+              abft_tile_sums(rv, lane, half, again, exp_row[c], scale_row[c], p.score_abs_tol, p.score_rel_tol, ignored);
+              asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+              const TileDecision d2 = abft_tile_decide(lane, again, exp_col0[c], exp_col1[c], scale_col0[c], scale_col1[c], p.score_abs_tol,
+                                                       p.score_rel_tol, ignored);
+              replayed = (d2.bad_rows | d2.bad_cols) == 0;
+              asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");  // `again` may be written again for the other half
+              tmem_st_32x32b_x32(s_addr + c * 64, rv);
+              tmem_st_32x32b_x32(s_addr + c * 64 + 32, rv + 32);
+              tmem_wait_st();
+              reload_row = true;
+            }
             if (half == 0 && lane == 0) {
               atomicAdd(&p.report->score_detected, 1);
-              atomicAdd(d.corrected ? &p.report->score_corrected : &p.report->score_uncorrected, 1);
+              atomicAdd(d.corrected ? &p.report->score_corrected : (replayed ? &p.report->score_replayed : &p.report->score_uncorrected), 1);
               int slot = atomicAdd(&p.report->record_count, 1);
               if (slot < 16) {
                 ft_tile_record rec;

@@ -2,22 +2,35 @@
 // form with one thread per whole row in ft_attention.cu serves the softmax-stage
 // protection).
 //
-// Same data flow as ft_attention.cu -- one CTA owns 256 queries of one (batch,
-// head) as two 128-query tiles A and B that share every 128-key K / V^T tile, S and
-// O live in TMEM, P goes through shared memory -- but every query row is worked on
-// by TWO threads: the softmax / verifier warpgroup (t, c) takes the key half c
-// (64 columns = exactly one 64x64 ABFT tile per 64-row band) of query tile t.
-//   warpgroup 0        warp 0 TMA producer of Q and K, warp 2 of V^T, warp 1 MMA issuer
+// One CTA owns 256 queries of one (batch, head) as two 128-query tiles A and B that
+// share every 128-key K / V^T tile.  Every query row is worked on by TWO threads:
+// the softmax / verifier warpgroup (t, c) takes the key half c (64 columns =
+// exactly one 64x64 ABFT tile per 64-row band) of query tile t.
+//   warpgroup 0        warp 0 TMA producer of Q and K, warp 2 of V^T, warp 1 issues the score MMAs, warp 3 the PV MMAs
 //   warpgroups 1..4    (t, c) = (A,0), (A,1), (B,0), (B,1); 16 softmax warps per SM
-//                      instead of 8: the kernel is bound by latency (barriers, TMEM
-//                      loads, dependent FP32 chains), not by a pipe, and the second
-//                      set of warps fills the idle issue slots.
+//
+// Tensor memory: ONE score buffer S (128 columns) serves both query tiles in turn,
+// because a thread reads its 64 scores exactly once: the column checksums come from
+// a read in the 16x256b fragment layout, then the row's 64 values are loaded into
+// registers, the buffer is handed back, and everything else (row checksum, row
+// maximum, correction, exponentials) works on the registers.  The columns this
+// frees hold 16 extra columns per output accumulator: V^T carries, below its D rows,
+// a row of ones and FP16 hi/lo pieces of the per-key sums sum_d V and sum_d w_d V
+// (attn_prepare_v_kernel), so the PV product of the tensor core also accumulates
+//   l = sum_j p_j,  sum_j p_j vsum_j,  sum_j p_j vweighted_j
+// -- the softmax denominator and the two expected output projections of the
+// reference's output-stage check (src/ft_flash_attention_a0.cu:585-662) -- from the
+// very FP16 probabilities it multiplies by V; the rescaling of O when a row maximum
+// moves covers them like any other column.
+//
 // Per key tile the two threads of a row exchange one number, their row maxima
-// (shared memory + one 256-thread barrier); the running sums l, sum p*vsum,
-// sum p*vweighted stay per half and are added once at the end, where the output
-// projection check (src/ft_flash_attention_a0.cu:613-662) needs two more exchanges.
-// The ABFT check of a score tile still pairs the two warps that hold rows 0-31 and
-// 32-63 of the band (abft_tile_check.cuh); both belong to the same warpgroup.
+// (shared memory + one 256-thread barrier).  The ABFT check of a score tile pairs
+// the two warps that hold rows 0-31 and 32-63 of the band (abft_tile_check.cuh);
+// both belong to the same warpgroup.  A tile whose fault cannot be located (not
+// exactly one bad row and one bad column) is replayed on the CUDA cores from Q and
+// K in global memory (src/ft_flash_attention_a14.cu:935-959), verified again and
+// counted as replayed, or as uncorrected when the replayed tile still disagrees
+// with the cached checksums.
 // Every wait is bounded; on expiry the kernel reports status and leaves.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -25,6 +38,7 @@
 #include <stdint.h>
 
 #include "abft_tile_check.cuh"
+#include "attention_device.cuh"
 #include "attention_kernels.h"
 #include "sm100_ptx.cuh"
 
@@ -37,24 +51,39 @@ constexpr int kQTiles = 2;             // query tiles per CTA
 constexpr int kSlabBytes = 128 * 128;  // 128 rows x 64 FP16 (one 128-byte swizzle row each)
 constexpr int kTileBytes = 2 * kSlabBytes;
 constexpr int kThreads = 640;
+// Register budget.  The CTA is launched with kLaunchRegs registers per thread (what the compiler reports for 640 threads
+// per SM); warpgroup 0 then gives registers back and the four softmax warpgroups take more.  setmaxnreg.inc WAITS until
+// the CTA's pool holds what it asks for, so the two numbers must fit the pool the launch allocated -- not the register
+// file: 128 * 32 + 512 * 112 = 61440 = 640 * 96 (with 40 registers left to warpgroup 0 the softmax warps would wait for ever).
+constexpr int kLaunchRegs = 96;
+constexpr int kProducerRegs = 32;
+constexpr int kSoftmaxRegs = 112;
+static_assert(128 * kProducerRegs + 512 * kSoftmaxRegs <= kThreads * kLaunchRegs, "setmaxnreg.inc would wait for registers the CTA does not own");
 constexpr uint64_t kTimeoutNs = 2000000000ull;
-constexpr uint32_t kTmemS = 0;    // score buffers of tile A, B at columns 0, 128
-constexpr uint32_t kTmemO = 256;  // output accumulators of tile A, B at columns 256, 384
+constexpr uint32_t kTmemS = 0;    // the score buffer, shared by the two query tiles
+constexpr uint32_t kTmemO = 128;  // output accumulators of tile A, B: kDim + kAttnVExtra columns each
 
 struct SplitShared {
   uint64_t q_full, k_full, k_empty, v_full, v_empty;
-  uint64_t s_full[kQTiles], s_empty[kQTiles];
+  uint64_t s_full[kQTiles], s_free;
   uint64_t p_full[kQTiles], p_empty[kQTiles];
+  uint64_t replay_bar[kQTiles][2][2];      // [query tile][key half][row pair]: the two warps of a band in the replay path
   uint32_t tmem_base;
   int abort_flag;
-  float4 v_meta[kQTiles][2][kTile / 2];    // [query tile][parity][key pair]: {sum_d V of both keys, sum_d w_d V of both keys}
   TileScratch scratch[kQTiles][2][2];      // [query tile][key half][row pair]
+  TileScratch replay_scratch[kQTiles][2][2];
   float row_max[kQTiles][2][2][kTile];     // [query tile][parity][key half][row]: the half's row maximum of this key tile
-  float4 final_sums[kQTiles][2][kTile];    // [query tile][key half][row]: {l, sum p*vsum, sum p*vweighted, -}
-  float2 final_actual[kQTiles][2][kTile];  // [query tile][dim half][row]: {sum_d o, sum_d w_d o} over the half's 64 dims
+  float2 final_actual[kQTiles][2][kTile];  // [query tile][dim half][row]: {sum_d o, sum_d w_d o} over the half's dims
 };
 
-constexpr int kSmemBytes = 6 * kTileBytes + static_cast<int>(sizeof(SplitShared)) + 1024;
+template <int kDim>
+constexpr int v_slab_bytes() {
+  return (kDim + kAttnVExtra) * 128;  // one slab of V^T: kDim + extra rows x 64 keys
+}
+template <int kDim>
+constexpr int smem_bytes() {
+  return 3 * kTileBytes + 2 * v_slab_bytes<kDim>() + 2 * kTileBytes + static_cast<int>(sizeof(SplitShared)) + 1024;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -89,19 +118,46 @@ __device__ __forceinline__ void reg_acquire() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Regs));
 }
 
+// Row maximum over the keys of this half a row may attend to (all 64 unless the tile is masked for the row).
+__device__ __forceinline__ float masked_row_max(const float (&v)[64], bool masked, int first_key, int key_limit) {
+  if (masked) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      if (first_key + i <= key_limit) m = fmaxf(m, v[i]);
+    }
+    return m;
+  }
+  // two chains of three-input maxima instead of one chain of 64
+  float max_a = v[0], max_b = v[1];
+#pragma unroll
+  for (int i = 2; i < 62; i += 4) {
+    max_a = max3_f32(max_a, v[i], v[i + 1]);
+    max_b = max3_f32(max_b, v[i + 2], v[i + 3]);
+  }
+  return max3_f32(max_a, max_b, fmaxf(v[62], v[63]));
+}
+
 }  // namespace
 
 template <int kDim>
 __global__ void __launch_bounds__(kThreads, 1)
 ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
+  constexpr int kDimSlabs = kDim / 64;             // 128-byte slabs of Q and K rows (64 FP16 each)
+  constexpr int kQKBytes = kDimSlabs * kSlabBytes;
+  constexpr int kVRows = kDim + kAttnVExtra;       // rows of a V^T tile: the head dimension and the checksum rows
+  constexpr int kVSlabBytes = (kDim + kAttnVExtra) * 128;  // one slab of V^T: kVRows rows x 64 keys
+  constexpr int kHalfDim = kDim / 2;               // output dims per thread of a row
+  constexpr uint32_t kOCols = kDim + kAttnVExtra;  // TMEM columns of one output accumulator
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* smem_q = smem;                   // 2 query tiles
-  uint8_t* smem_k = smem + 2 * kTileBytes;  // 1 stage
-  uint8_t* smem_v = smem + 3 * kTileBytes;  // 1 stage
-  uint8_t* smem_p = smem + 4 * kTileBytes;  // 2 query tiles
-  SplitShared& sh = *reinterpret_cast<SplitShared*>(smem + 6 * kTileBytes);
+  uint8_t* smem_q = smem;                      // 2 query tiles
+  uint8_t* smem_k = smem + 2 * kTileBytes;     // 1 stage
+  uint8_t* smem_v = smem + 3 * kTileBytes;     // 1 stage: two slabs of kVRows x 64 keys
+  uint8_t* smem_p = smem_v + 2 * kVSlabBytes;  // 2 query tiles
+  SplitShared& sh = *reinterpret_cast<SplitShared*>(smem_p + 2 * kTileBytes);
   volatile int* abort_flag = &sh.abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -127,11 +183,12 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     mbar_init(&sh.k_empty, 1);
     mbar_init(&sh.v_full, 1);
     mbar_init(&sh.v_empty, 1);
+    mbar_init(&sh.s_free, 256);  // both key halves of the tile that used the buffer hold their scores in registers
     for (int t = 0; t < kQTiles; ++t) {
       mbar_init(&sh.s_full[t], 1);
-      mbar_init(&sh.s_empty[t], 256);  // both key halves have read S
-      mbar_init(&sh.p_full[t], 256);   // both halves of P are written
+      mbar_init(&sh.p_full[t], 256);  // both halves of P are written
       mbar_init(&sh.p_empty[t], 1);
+      for (int i = 0; i < 4; ++i) mbar_init(&sh.replay_bar[t][i >> 1][i & 1], 64);
     }
     sh.abort_flag = 0;
     fence_barrier_init();
@@ -147,13 +204,9 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
-  constexpr int kDimSlabs = kDim / 64;          // 128-byte slabs of Q and K rows (64 FP16 each)
-  constexpr int kQKBytes = kDimSlabs * kSlabBytes;
-  constexpr int kVSlabBytes = kDim * 128;       // one slab of V^T: kDim rows x 64 keys
-  constexpr int kHalfDim = kDim / 2;            // output dims per thread of a row
 
   if (group == 0) {
-    reg_release<40>();
+    reg_release<kProducerRegs>();
     if (warp == 0 && elect_one()) {
       // ------------------------------------------------------------- producer
       mbar_arrive_expect_tx(&sh.q_full, qtiles * kQKBytes);
@@ -172,66 +225,78 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       }
     } else if (warp == 2 && elect_one()) {
       // ------------------------------------------------------------- producer of V^T: its own thread, so that the load of
-      // K_{j+1} (free as soon as both score products of tile j are done) never queues behind the wait for the V buffer
+      // K_{j+1} never queues behind the wait for the V buffer
       for (int j = 0; j < cta_tiles; ++j) {
         const uint32_t ph = j & 1;
         if (!mbar_wait_bounded(&sh.v_empty, ph ^ 1, abort_flag, kTimeoutNs)) break;
         mbar_arrive_expect_tx(&sh.v_full, 2 * kVSlabBytes);
-        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kTile, bh * kDim);
-        tma_load_2d(smem_v + kSlabBytes, &tmap_vt, &sh.v_full, j * kTile + 64, bh * kDim);
+        tma_load_2d(smem_v, &tmap_vt, &sh.v_full, j * kTile, bh * kVRows);
+        tma_load_2d(smem_v + kVSlabBytes, &tmap_vt, &sh.v_full, j * kTile + 64, bh * kVRows);
       }
-    } else if (warp == 1 && elect_one()) {
-      // ------------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc_s = make_idesc_f16_f32(kTile, kTile);  // S: 128 queries x 128 keys
-      constexpr uint32_t idesc_o = make_idesc_f16_f32(kTile, kDim);   // O: 128 queries x kDim
-      bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kTimeoutNs);
-      for (int j = 0; j <= cta_tiles && alive; ++j) {
-        if (j < cta_tiles) {  // S_A, S_B = Q_{A,B} K_j^T
-          if (!mbar_wait_bounded(&sh.k_full, j & 1, abort_flag, kTimeoutNs)) break;
-          for (int t = 0; t < qtiles && alive; ++t) {
-            if (j >= tiles_of(t)) continue;
-            // the score buffer of tile t is free once both key halves have read S_{j-1} for the second time
-            if (!mbar_wait_bounded(&sh.s_empty[t], (j & 1) ^ 1, abort_flag, kTimeoutNs)) {
-              alive = false;
-              break;
-            }
-            tcgen05_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < kDim / 16; ++kk) {
-              uint64_t da = make_smem_desc_sw128(smem_u32(smem_q + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
-              uint64_t db = make_smem_desc_sw128(smem_u32(smem_k + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
-              umma_f16(tmem_base + kTmemS + t * kTile, da, db, idesc_s, kk != 0 ? 1u : 0u);
-            }
-            umma_commit(&sh.s_full[t]);
+    } else if ((warp == 1 || warp == 3) && elect_one()) {
+      // ------------------------------------------------------------- MMA issuers: warp 1 the score products, warp 3 the PV
+      // products.  Two threads, so that neither chain queues behind a wait of the other (a score product never waits for
+      // probabilities, a PV product never for a free score buffer) and each loop keeps only a handful of registers.
+      // The score buffer is used in the order (key tile 0: A, B), (key tile 1: A, B), ...; use n may start when the
+      // softmax threads of use n-1 hold their scores in registers.  The PV products follow the same order.
+      auto advance = [&](int& j, int& t) {  // next (key tile, query tile) in use order; j == cta_tiles at the end
+        do {
+          if (++t == qtiles) {
+            t = 0;
+            ++j;
           }
-          if (!alive) break;
-          umma_commit(&sh.k_empty);
+        } while (j < cta_tiles && j >= tiles_of(t));
+      };
+      int j = 0, t = 0;
+      if (warp == 1) {
+        constexpr uint32_t idesc_s = make_idesc_f16_f32(kTile, kTile);  // S: 128 queries x 128 keys
+        bool alive = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kTimeoutNs);
+        int k_waited = -1;
+        uint32_t uses = 0;
+        while (alive && j < cta_tiles) {
+          if (k_waited != j) {
+            if (!mbar_wait_bounded(&sh.k_full, j & 1, abort_flag, kTimeoutNs)) break;
+            k_waited = j;
+          }
+          if (uses > 0 && !mbar_wait_bounded(&sh.s_free, (uses - 1) & 1, abort_flag, kTimeoutNs)) break;
+          tcgen05_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kDim / 16; ++kk) {
+            uint64_t da = make_smem_desc_sw128(smem_u32(smem_q + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+            uint64_t db = make_smem_desc_sw128(smem_u32(smem_k + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+            umma_f16(tmem_base + kTmemS, da, db, idesc_s, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(&sh.s_full[t]);
+          const int before = j;
+          advance(j, t);
+          if (j != before) umma_commit(&sh.k_empty);  // that was the last product that reads K_j
+          ++uses;
         }
-        if (j > 0) {  // O_{A,B} += P_i V_i for the previous key tile
-          const int i = j - 1;
-          if (!mbar_wait_bounded(&sh.v_full, i & 1, abort_flag, kTimeoutNs)) break;
-          for (int t = 0; t < qtiles && alive; ++t) {
-            if (i >= tiles_of(t)) continue;
-            if (!mbar_wait_bounded(&sh.p_full[t], i & 1, abort_flag, kTimeoutNs)) {
-              alive = false;
-              break;
-            }
-            tcgen05_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-              uint64_t da = make_smem_desc_sw128(smem_u32(smem_p + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
-              uint64_t db = make_smem_desc_sw128(smem_u32(smem_v + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
-              umma_f16(tmem_base + kTmemO + t * kTile, da, db, idesc_o, (i | kk) != 0 ? 1u : 0u);
-            }
-            umma_commit(&sh.p_empty[t]);
+      } else {
+        constexpr uint32_t idesc_o = make_idesc_f16_f32(kTile, kVRows);  // O and its checksum columns: 128 queries x (kDim + 16)
+        int v_waited = -1;
+        while (j < cta_tiles) {
+          if (v_waited != j) {
+            if (!mbar_wait_bounded(&sh.v_full, j & 1, abort_flag, kTimeoutNs)) break;
+            v_waited = j;
           }
-          if (!alive) break;
-          umma_commit(&sh.v_empty);
+          if (!mbar_wait_bounded(&sh.p_full[t], j & 1, abort_flag, kTimeoutNs)) break;
+          tcgen05_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            uint64_t da = make_smem_desc_sw128(smem_u32(smem_p + t * kTileBytes + (kk >> 2) * kSlabBytes)) + 2 * (kk & 3);
+            uint64_t db = make_smem_desc_sw128(smem_u32(smem_v + (kk >> 2) * kVSlabBytes)) + 2 * (kk & 3);
+            umma_f16(tmem_base + kTmemO + t * kOCols, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&sh.p_empty[t]);
+          const int before = j;
+          advance(j, t);
+          if (j != before) umma_commit(&sh.v_empty);  // that was the last product that reads V_j
         }
       }
     }
   } else {
-    reg_acquire<104>();
+    reg_acquire<kSoftmaxRegs>();
     // ------------------------------------------------------------- softmax / verifier: two threads per query row
     const int t = (group - 1) >> 1;  // query tile of this warpgroup
     const int c = (group - 1) & 1;   // key half of S / dim half of O this warpgroup works on
@@ -241,28 +306,32 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const int half = quarter & 1;
       const int r_local = half * 32 + lane;
       const int row_in_tile = quarter * 32 + lane;
-      const int tg = threadIdx.x & 127;
-      const int bar_tile = 1 + t;                         // 256-thread barrier of the two warpgroups of tile t (ids 1, 2)
-      const int bar_pair = 3 + 2 * (group - 1) + pair;    // 64-thread barrier of this 64-row band (ids 3..10)
+      const int bar_tile = 1 + t;                       // 256-thread barrier of the two warpgroups of tile t (ids 1, 2)
+      const int bar_pair = 3 + 2 * (group - 1) + pair;  // 64-thread barrier of this 64-row band (ids 3..10)
       const int tile_cols = seq / 64;
       const size_t head_cache = static_cast<size_t>(bh) * tile_cols * tile_cols * 64;
       const int q_tile0 = q0 + t * kTile;
       const int q_band = q_tile0 / 64 + pair;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      const uint32_t s_addr = lane_addr + kTmemS + t * kTile + c * 64;  // this half's 64 score columns
-      const uint32_t o_addr = lane_addr + kTmemO + t * kTile + c * kHalfDim;  // this half's output dims
+      const uint32_t s_addr = lane_addr + kTmemS + c * 64;                     // this half's 64 score columns
+      const uint32_t o_addr = lane_addr + kTmemO + t * kOCols + c * kHalfDim;  // this half's output dims
+      const uint32_t x_addr = lane_addr + kTmemO + t * kOCols + kDim;          // the checksum columns of the row
       uint8_t* p_row = smem_p + t * kTileBytes + c * kSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
-      const bool fault_here = p.fault_bh == bh && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kTile;
+      const bool fault_head = p.fault_bh == bh;
+      const bool fault_here = fault_head && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kTile;
       const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE && (p.fault_index % kTile) / 64 == c;
+      const bool score_fault2 = fault_head && p.fault_stage == FT_ATTN_FAULT_SCORE && p.fault2_value != 0.0f && p.fault2_query >= q_tile0 &&
+                                p.fault2_query < q_tile0 + kTile && (p.fault2_index % kTile) / 64 == c;
       const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_index / kHalfDim == c;
       const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
       TileScratch& scratch = sh.scratch[t][c][pair];
+      uint32_t replays = 0;  // times this band went through the replay path (the phase of its barrier)
 
-      float m_run = -INFINITY, l_run = 0.0f, exp_sum = 0.0f, exp_weighted = 0.0f, max_ratio = 0.0f;  // the sums: this half's share
+      float m_run = -INFINITY, max_ratio = 0.0f;
       bool alive = true;
       const int my_tiles = tiles_of(t);
-      int drain_from = my_tiles;      // when a wait is abandoned: first key tile whose named barriers are still owed ...
-      bool drain_skip_first = false;  // ... unless that tile's two barriers were already passed
+      // when a wait is abandoned: the first key tile whose band barrier / tile barrier this warp still owes the others
+      int owed_pair_from = my_tiles, owed_tile_from = my_tiles;
       for (int j = 0; j < my_tiles; ++j) {
         const int buf = j & 1;
         // Keys of this tile the row may attend to are those with local index <= key_limit: all 128, up to the query in
@@ -272,24 +341,16 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         if (causal && j == first_qtile + t) key_limit = row_in_tile;
         if ((j + 1) * kTile > p.valid_seq) key_limit = min(key_limit, p.valid_seq - 1 - j * kTile);
         const bool diagonal = key_limit < kTile - 1;  // some keys of this tile are masked for this row
-        // per-key sums of V for this half's 64 keys (read in pass 2; published by the 256-thread barrier of the exchange)
-        if (tg < 64) {
-          const size_t key = static_cast<size_t>(bh) * seq + j * kTile + c * 64 + tg;
-          float* meta = reinterpret_cast<float*>(&sh.v_meta[t][buf][(c * 64 + tg) >> 1]);  // pairs laid out for packed FP32 math
-          meta[tg & 1] = __ldg(p.v_sum + key);
-          meta[2 + (tg & 1)] = __ldg(p.v_weighted + key);
-        }
-        // cached expected checksums of this thread's 64x64 tile: fetched before the wait
+        // cached expected checksums of this thread's 64x64 tile: the row's pair is fetched before the wait, the column
+        // values are only asked for (they are read after the partner exchange; until then they would hold registers)
         const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
         const float exp_row = __ldg(p.expected_rows + cache + r_local);
         const float scale_row = __ldg(p.row_scales + cache + r_local);
-        const float exp_col0 = __ldg(p.expected_cols + cache + lane);
-        const float exp_col1 = __ldg(p.expected_cols + cache + 32 + lane);
-        const float scale_col0 = __ldg(p.col_scales + cache + lane);
-        const float scale_col1 = __ldg(p.col_scales + cache + 32 + lane);
+        prefetch_l1(p.expected_cols + cache + 2 * lane);
+        prefetch_l1(p.col_scales + cache + 2 * lane);
         if (!warp_wait(&sh.s_full[t], j & 1, abort_flag)) {
           alive = false;
-          drain_from = j;
+          owed_pair_from = owed_tile_from = j;
           break;
         }
         tcgen05_fence_after();
@@ -298,56 +359,64 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         if (score_fault && p.fault_index / kTile == j && fault_row / 32 == quarter) {
           tmem_add(s_addr + p.fault_index % 64, lane, fault_row % 32, p.fault_value);
         }
-
-        // ---- pass 1: verify this thread's 64x64 score tile, take the half's row maximum
-        float local_max = -INFINITY;
-        {
-          abft_tile_cols_from_tmem(s_addr, lane, half, scratch);
-          float v[64];
-          tmem_ld_32x32b_x32(s_addr, v);
-          tmem_ld_32x32b_x32(s_addr + 32, v + 32);
-          tmem_wait_ld();
-          abft_tile_rows(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
-          if (diagonal) {  // the verifier has seen the raw tile; the maximum only sees keys up to the query
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-              if (c * 64 + i > key_limit) v[i] = -INFINITY;
-            }
-          }
-          {  // two chains of three-input maxima instead of one chain of 64
-            float max_a = v[0], max_b = v[1];
-#pragma unroll
-            for (int i = 2; i < 62; i += 4) {
-              max_a = max3_f32(max_a, v[i], v[i + 1]);
-              max_b = max3_f32(max_b, v[i + 2], v[i + 3]);
-            }
-            local_max = max3_f32(max_a, max_b, fmaxf(v[62], v[63]));
-          }
+        if (score_fault2 && p.fault2_index / kTile == j && (p.fault2_query - q_tile0) / 32 == quarter) {
+          tmem_add(s_addr + p.fault2_index % 64, lane, (p.fault2_query - q_tile0) % 32, p.fault2_value);
         }
+
+        // ---- the one read of this thread's scores: column checksums from the fragment layout, then the row into registers
+        abft_tile_cols_from_tmem(s_addr, lane, half, scratch);
+        float v[64];
+        tmem_ld_32x32b_x32(s_addr, v);
+        tmem_ld_32x32b_x32(s_addr + 32, v + 32);
+        tmem_wait_ld();
+        tcgen05_fence_before();
+        mbar_arrive(&sh.s_free);  // the buffer can take the next score product (the other query tile's)
+        abft_tile_rows(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
+        float local_max = masked_row_max(v, diagonal, c * 64, key_limit);
         asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
         {
+          const float exp_col0 = __ldg(p.expected_cols + cache + lane), exp_col1 = __ldg(p.expected_cols + cache + 32 + lane);
+          const float scale_col0 = __ldg(p.col_scales + cache + lane), scale_col1 = __ldg(p.col_scales + cache + 32 + lane);
           const TileDecision d = abft_tile_decide(lane, scratch, exp_col0, exp_col1, scale_col0, scale_col1, p.score_abs_tol,
                                                   p.score_rel_tol, max_ratio);
-          if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps of the band
-            if (d.corrected && d.bad_row / 32 == half) {
-              // src/s4:493-497 on the accumulator itself: pass 2 reads the corrected score back
-              tmem_add(s_addr + d.bad_col, lane, d.bad_row % 32, 0.5f * (d.row_delta + d.col_delta));
-              // warp-uniform and rare: the maximum of the corrected row is taken from the corrected scores
-              local_max = -INFINITY;
-#pragma unroll 1
-              for (int cc = 0; cc < 2; ++cc) {
-                float v[32];
-                tmem_ld_32x32b_x32(s_addr + cc * 32, v);
-                tmem_wait_ld();
+          if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps of the band; rare
+            bool replayed = false;
+            if (d.corrected) {
+              if (d.bad_row == r_local) {
+                // src/s4:493-497 in registers
+                const float fix = 0.5f * (d.row_delta + d.col_delta);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  if (!diagonal || c * 64 + cc * 32 + i <= key_limit) local_max = fmaxf(local_max, v[i]);
+                for (int i = 0; i < 64; ++i) {
+                  if (i == d.bad_col) v[i] += fix;
                 }
               }
+            } else {
+              // The fault cannot be located: recompute the band's 64 x 64 scores without the tensor core and check again.
+              const __half* q_row = static_cast<const __half*>(p.q) + (static_cast<size_t>(row_base) + q_tile0 + row_in_tile) * kDim;
+              const __half* k_tile = static_cast<const __half*>(p.k) + (static_cast<size_t>(row_base) + j * kTile + c * 64) * kDim;
+              replay_score_row<kDim>(q_row, k_tile, v);
+              TileScratch& again = sh.replay_scratch[t][c][pair];
+              float ignored = 0.0f;
+              abft_tile_rows(v, lane, half, again, __ldg(p.expected_rows + cache + r_local), __ldg(p.row_scales + cache + r_local),
+                             p.score_abs_tol, p.score_rel_tol, ignored);
+              abft_tile_cols_from_rows(v, lane, half, again);
+              uint64_t* rbar = &sh.replay_bar[t][c][pair];
+              mbar_arrive(rbar);
+              if (!warp_wait(rbar, replays & 1, abort_flag)) {  // the partner warp gave up: this tile's band barrier is passed
+                alive = false;
+                owed_pair_from = j + 1;
+                owed_tile_from = j;
+                break;
+              }
+              ++replays;
+              const TileDecision d2 = abft_tile_decide(lane, again, exp_col0, exp_col1, scale_col0, scale_col1, p.score_abs_tol,
+                                                       p.score_rel_tol, ignored);
+              replayed = (d2.bad_rows | d2.bad_cols) == 0;
             }
+            local_max = masked_row_max(v, diagonal, c * 64, key_limit);
             if (half == 0 && lane == 0) {
               atomicAdd(&p.report->score_detected, 1);
-              atomicAdd(d.corrected ? &p.report->score_corrected : &p.report->score_uncorrected, 1);
+              atomicAdd(d.corrected ? &p.report->score_corrected : (replayed ? &p.report->score_replayed : &p.report->score_uncorrected), 1);
               int slot = atomicAdd(&p.report->record_count, 1);
               if (slot < 16) {
                 ft_tile_record rec;
@@ -372,39 +441,40 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         // ---- online softmax state (log2 domain); identical in both threads of the row
         const float m_new = fmaxf(m_run, row_max * p.scale_log2);
         const float alpha = fast_exp2(m_run - m_new);  // 0 for the first tile (m_run = -inf)
+        m_run = m_new;
 
         if (j > 0) {
           // PV of the previous tile must have finished: the P buffer is free and O is quiescent
           if (!warp_wait(&sh.p_empty[t], (j - 1) & 1, abort_flag)) {
             alive = false;
-            drain_from = j;
-            drain_skip_first = true;
+            owed_pair_from = owed_tile_from = j + 1;
             break;
           }
           tcgen05_fence_after();
           if (__any_sync(0xffffffffU, alpha != 1.0f)) {
+            const unsigned long long alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll 1
             for (int cc = 0; cc < kHalfDim / 32; ++cc) {  // this half's output dims
               float o[32];
               tmem_ld_32x32b_x32(o_addr + cc * 32, o);
               tmem_wait_ld();
-              const unsigned long long alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll
               for (int i = 0; i < 32; i += 2) unpack_f32x2(mul_f32x2(pack_f32x2(o[i], o[i + 1]), alpha2), o[i], o[i + 1]);
               tmem_st_32x32b_x32(o_addr + cc * 32, o);
             }
+            if (c == 1) {  // the checksum columns (l and the expected projections) scale with the row like any output column
+              float x[8];
+              tmem_ld_32x32b_x8(x_addr, x);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 8; i += 2) unpack_f32x2(mul_f32x2(pack_f32x2(x[i], x[i + 1]), alpha2), x[i], x[i + 1]);
+              tmem_st_32x32b_x8(x_addr, x);
+            }
             tmem_wait_st();
           }
         }
-        // ---- pass 2: probabilities of this half, FP16 P slab for the MMA, this half's share of the expected projections
-        float l_tile = 0.0f, es_tile = 0.0f, ew_tile = 0.0f;
+        // ---- probabilities of this half: FP16 P slab for the MMA (which also forms l and the expected projections)
         {
-          float v[64];
-          tmem_ld_32x32b_x32(s_addr, v);
-          tmem_ld_32x32b_x32(s_addr + 32, v + 32);
-          tmem_wait_ld();
-          tcgen05_fence_before();
-          mbar_arrive(&sh.s_empty[t]);  // in registers: the score buffer can take S of the next key tile
           if (diagonal) {  // exp2(-inf) = 0: a masked key gets probability zero
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
@@ -413,7 +483,6 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           }
           // two scores per instruction where the arithmetic allows it (packed FP32 pairs)
           const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg_m2 = pack_f32x2(-m_new, -m_new);
-          unsigned long long l2 = pack_f32x2(0.0f, 0.0f), es2 = l2, ew2 = l2;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
             uint32_t packed[4];
@@ -423,58 +492,41 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               float a0, a1;
               unpack_f32x2(fma_f32x2(pack_f32x2(v[i0], v[i0 + 1]), scale2, neg_m2), a0, a1);
               const __half2 h = __floats2half2_rn(fast_exp2(a0), fast_exp2(a1));
-              const float2 r = __half22float2(h);  // what the MMA will multiply by V
-              const unsigned long long r2 = pack_f32x2(r.x, r.y);
-              l2 = add_f32x2(l2, r2);
-              const float4 meta = sh.v_meta[t][buf][(c * 64 + i0) >> 1];
-              es2 = fma_f32x2(r2, pack_f32x2(meta.x, meta.y), es2);
-              ew2 = fma_f32x2(r2, pack_f32x2(meta.z, meta.w), ew2);
               packed[e] = *reinterpret_cast<const uint32_t*>(&h);
             }
             // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
             *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
-          float lo, hi;
-          unpack_f32x2(l2, lo, hi);
-          l_tile = lo + hi;
-          unpack_f32x2(es2, lo, hi);
-          es_tile = lo + hi;
-          unpack_f32x2(ew2, lo, hi);
-          ew_tile = lo + hi;
         }
-        l_run = __fmaf_rn(alpha, l_run, l_tile);
-        exp_sum = __fmaf_rn(alpha, exp_sum, es_tile);
-        exp_weighted = __fmaf_rn(alpha, exp_weighted, ew_tile);
-        m_run = m_new;
         fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
         tcgen05_fence_before();
         mbar_arrive(&sh.p_full[t]);
       }
-      // ---- output stage: projection check of O / l (src/ft_flash_attention_a0.cu:613-662), normalise, store
-      for (int jj = drain_from; jj < my_tiles; ++jj) {  // only after an abandoned wait: the barriers the other warps count on
-        if (jj == drain_from && drain_skip_first) continue;
-        asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
-        asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+      // only after an abandoned wait: the named barriers the other warps of the band / tile still count on
+      for (int jj = min(owed_pair_from, owed_tile_from); jj < my_tiles; ++jj) {
+        if (jj >= owed_pair_from) asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+        if (jj >= owed_tile_from) asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
       }
-      // The two exchange barriers of the output stage are executed by every warp; a warp that gave up skips the work in
-      // between (the run is reported as timed out, its output is not valid).
+      // ---- output stage: projection check of O / l (src/ft_flash_attention_a0.cu:613-662), normalise, store.
+      // Its exchange barrier is executed by every warp; a warp that gave up skips the work around it (the run is
+      // reported as timed out, its output is not valid).
       alive = alive && warp_wait(&sh.p_empty[t], (my_tiles - 1) & 1, abort_flag);
+      float inv_l = 0.0f, es_total = 0.0f, ew_total = 0.0f;
+      float actual_sum = 0.0f, actual_weighted = 0.0f;
+      const int query = q_tile0 + row_in_tile;
+      const bool my_fault = output_fault && fault_row == row_in_tile;
       if (alive) {
         tcgen05_fence_after();
-        sh.final_sums[t][c][row_in_tile] = make_float4(l_run, exp_sum, exp_weighted, 0.0f);
-      }
-      asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
-      if (!alive) asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
-      if (alive) {
-        const float4 other = sh.final_sums[t][c ^ 1][row_in_tile];
-        // totals in a fixed order (half 0 + half 1) so that both threads of the row hold the same bits
-        const float l_total = c == 0 ? l_run + other.x : other.x + l_run;
-        const float es_total = c == 0 ? exp_sum + other.y : other.y + exp_sum;
-        const float ew_total = c == 0 ? exp_weighted + other.z : other.z + exp_weighted;
-        const float inv_l = 1.0f / l_total;
-        const int query = q_tile0 + row_in_tile;
-        const bool my_fault = output_fault && fault_row == row_in_tile;
-        float actual_sum = 0.0f, actual_weighted = 0.0f;
+        {
+          // what the tensor core accumulated beside the output: [0] l, [1]+[2] sum p*vsum (hi and lo pieces),
+          // [3]+[4] sum p*vweighted / kAttnVWeightScale
+          float x[8];
+          tmem_ld_32x32b_x8(x_addr, x);
+          tmem_wait_ld();
+          inv_l = 1.0f / x[0];
+          es_total = x[1] + x[2];
+          ew_total = (x[3] + x[4]) * kAttnVWeightScale;
+        }
 #pragma unroll 1
         for (int cc = 0; cc < kHalfDim / 32; ++cc) {
           float o[32];
@@ -490,8 +542,11 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           }
         }
         sh.final_actual[t][c][row_in_tile] = make_float2(actual_sum, actual_weighted);
-        asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+      }
+      asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+      if (alive) {
         const float2 other_actual = sh.final_actual[t][c ^ 1][row_in_tile];
+        // totals in a fixed order (half 0 + half 1) so that both threads of the row hold the same bits
         const float sum_total = c == 0 ? actual_sum + other_actual.x : other_actual.x + actual_sum;
         const float weighted_total = c == 0 ? actual_weighted + other_actual.y : other_actual.y + actual_weighted;
         const float expected_sum = es_total * inv_l;
@@ -556,18 +611,18 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 }
 
 cudaError_t configure_attention_split() {
-  cudaError_t err = cudaFuncSetAttribute(ft_attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t err = cudaFuncSetAttribute(ft_attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<128>());
   if (err != cudaSuccess) return err;
-  return cudaFuncSetAttribute(ft_attention_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  return cudaFuncSetAttribute(ft_attention_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<64>());
 }
 
 cudaError_t launch_attention_split(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                                    int batch_heads, cudaStream_t stream) {
   dim3 grid((params.seq + kQTiles * kTile - 1) / (kQTiles * kTile), batch_heads);
   if (params.dim == 64) {
-    ft_attention_split_kernel<64><<<grid, kThreads, kSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+    ft_attention_split_kernel<64><<<grid, kThreads, smem_bytes<64>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
   } else {
-    ft_attention_split_kernel<128><<<grid, kThreads, kSmemBytes, stream>>>(tmap_q, tmap_k, tmap_vt, params);
+    ft_attention_split_kernel<128><<<grid, kThreads, smem_bytes<128>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
   }
   return cudaGetLastError();
 }

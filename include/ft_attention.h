@@ -20,7 +20,9 @@
  *     column checksum verifier as the GEMM (expected_row = Q rowsum(K-tile),
  *     expected_col = colsum(Q-tile) K^T, cached by _prepare); a single faulty score
  *     is located at the row/column intersection and corrected in registers before
- *     the softmax; tiles with several bad rows or columns are reported;
+ *     the softmax; a tile with several bad rows or columns is recomputed without
+ *     the tensor core, checked again and counted as replayed (a14:935-959), or as
+ *     uncorrected when the recomputed tile still fails the check;
  *   - output stage: the reference's projection check of P V (a0:585-662): the
  *     expected sum and position-weighted sum of each output row are carried
  *     through the online softmax from per-key sums of V, a single faulty output
@@ -73,19 +75,27 @@ typedef struct {
   int query;
   int index;
   float value;
+  /* A second fault of the score stage in the same (batch, head), for runs that must show a tile with several faults
+   * (the reference injects one fault per run; its replay path, src/ft_flash_attention_a14.cu:935-959, is reached by
+   * faults its row locator cannot place).  Ignored unless stage == FT_ATTN_FAULT_SCORE and value2 != 0. */
+  int query2;
+  int index2;
+  float value2;
 } ft_attn_fault;
 
 typedef struct {
   int status;            /* FT_OK or FT_ERR_TIMEOUT */
   int score_detected;    /* score tiles whose checker fired */
   int score_corrected;   /* of which: one bad row and one bad column, corrected */
-  int score_uncorrected; /* of which: several bad rows/columns, reported only */
+  int score_uncorrected; /* of which: not locatable, and the replayed tile still disagrees with the cached checksums */
   int pv_detected;       /* output rows whose projection check fired */
   int pv_corrected;
   int failed_rows;       /* output rows detected but not locatable */
   int softmax_detected;  /* (row, key tile) pairs whose moment or state check fired (protect_softmax) */
   int softmax_corrected; /* of which: one probability located and replaced by the verifier's */
   int softmax_replayed;  /* of which: the row of the tile, or the running state, taken from the verifier */
+  int score_replayed;    /* score tiles whose fault could not be located (several bad rows or columns): recomputed on
+                            the CUDA cores from Q and K, verified again and accepted (src/ft_flash_attention_a14.cu:935-959) */
   int n_records;
   float max_score_noise; /* max |delta|/threshold over score checksums that passed */
   float prepare_ms;

@@ -41,6 +41,7 @@ typedef struct {
   int n_records;
   float max_score_noise;
   float min_margin; /* nearest score-stage decision to its threshold, relative */
+  int score_replayed; /* tiles whose fault could not be located: recomputed, verified again and accepted */
 } ftq_attn_stats;
 
 float ftq_half_to_float(uint16_t h) {
@@ -145,18 +146,18 @@ static void band_sums_f32(const float* x, int rows, int d, float* sums, float* m
 void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint16_t* v16, int batch_heads, int seq, int valid_seq, int dim,
                            float score_abs, float score_rel, float pv_abs, float pv_rel, float softmax_abs, float softmax_rel,
                            int protect_softmax, int causal, int fault_stage, int fault_bh,
-                           int fault_query, int fault_index, float fault_value, float* out, ftq_attn_stats* stats,
-                           ftq_tile_record* records, int max_records) {
+                           int fault_query, int fault_index, float fault_value, int fault2_query, int fault2_index, float fault2_value,
+                           float* out, ftq_attn_stats* stats, ftq_tile_record* records, int max_records) {
   const int bands = seq / 64;
   const float scale_log2 = 1.44269504088896340736f / sqrtf((float)dim);
   int score_detected = 0, score_corrected = 0, score_uncorrected = 0, pv_detected = 0, pv_corrected = 0, failed_rows = 0;
-  int softmax_detected = 0, softmax_corrected = 0, softmax_replayed = 0;
+  int softmax_detected = 0, softmax_corrected = 0, softmax_replayed = 0, score_replayed = 0;
   int n_records = 0;
   float max_noise = 0.0f, min_margin = INFINITY;
 
 #pragma omp parallel for schedule(dynamic, 1) reduction(+ : score_detected, score_corrected, score_uncorrected, pv_detected, \
                                                             pv_corrected, failed_rows, softmax_detected, softmax_corrected, \
-                                                            softmax_replayed) reduction(max : max_noise)                  \
+                                                            softmax_replayed, score_replayed) reduction(max : max_noise)   \
     reduction(min : min_margin)
   for (int bh = 0; bh < batch_heads; ++bh) {
     const size_t head = (size_t)bh * seq * dim;
@@ -214,49 +215,78 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
           }
         if (fault_stage == 1 && fault_bh == bh && fault_query / 64 == qb && fault_index / 128 == j)
           s[(fault_query % 64) * 128 + fault_index % 128] += fault_value;
+        if (fault_stage == 1 && fault_bh == bh && fault2_value != 0.0f && fault2_query / 64 == qb && fault2_index / 128 == j)
+          s[(fault2_query % 64) * 128 + fault2_index % 128] += fault2_value;
         /* verify the two 64x64 tiles */
         for (int c2 = 0; c2 < 2; ++c2) {
           int kb = j * 2 + c2;
           int nbr = 0, nbc = 0, bad_row = -1, bad_col = -1;
           float row_delta = 0.0f, col_delta = 0.0f;
-          for (int r = 0; r < 64; ++r) {
-            float expected, scale, actual = 0.0f;
-            strided_dot(qf + (size_t)(qb * 64 + r) * dim, k_sums + (size_t)kb * dim, k_mags + (size_t)kb * dim, dim, 1, &expected, &scale);
-            for (int c = 0; c < 64; ++c) actual += s[r * 128 + c2 * 64 + c];
-            float delta = expected - actual, thr = threshold(score_abs, score_rel, scale);
-            float margin = fabsf(fabsf(delta) - thr) / thr;
-            if (margin < min_margin) min_margin = margin;
-            if (fabsf(delta) > thr) {
-              if (nbr++ == 0) {
-                bad_row = r;
-                row_delta = delta;
+          int first_nbr = 0, first_nbc = 0, first_bad_row = -1, first_bad_col = -1, replayed_tile = 0;
+          float first_row_delta = 0.0f, first_col_delta = 0.0f;
+          /* pass 0: the tile as the tensor core (and the fault hook) left it; pass 1, only when the fault of pass 0
+           * cannot be located: the tile recomputed without the tensor core (a14:935-959) and checked again */
+          for (int pass = 0; pass < 2; ++pass) {
+            nbr = nbc = 0;
+            bad_row = bad_col = -1;
+            row_delta = col_delta = 0.0f;
+            for (int r = 0; r < 64; ++r) {
+              float expected, scale, actual = 0.0f;
+              strided_dot(qf + (size_t)(qb * 64 + r) * dim, k_sums + (size_t)kb * dim, k_mags + (size_t)kb * dim, dim, 1, &expected, &scale);
+              for (int c = 0; c < 64; ++c) actual += s[r * 128 + c2 * 64 + c];
+              float delta = expected - actual, thr = threshold(score_abs, score_rel, scale);
+              float margin = fabsf(fabsf(delta) - thr) / thr;
+              if (margin < min_margin) min_margin = margin;
+              if (fabsf(delta) > thr) {
+                if (nbr++ == 0) {
+                  bad_row = r;
+                  row_delta = delta;
+                }
+              } else if (pass == 0 && fabsf(delta) / thr > max_noise) {
+                max_noise = fabsf(delta) / thr;
               }
-            } else if (fabsf(delta) / thr > max_noise) {
-              max_noise = fabsf(delta) / thr;
+            }
+            for (int c = 0; c < 64; ++c) {
+              float expected, scale, actual = 0.0f;
+              strided_dot(kf + (size_t)(kb * 64 + c) * dim, q_sums + (size_t)qb * dim, q_mags + (size_t)qb * dim, dim, 0, &expected, &scale);
+              for (int r = 0; r < 64; ++r) actual += s[r * 128 + c2 * 64 + c];
+              float delta = expected - actual, thr = threshold(score_abs, score_rel, scale);
+              float margin = fabsf(fabsf(delta) - thr) / thr;
+              if (margin < min_margin) min_margin = margin;
+              if (fabsf(delta) > thr) {
+                if (nbc++ == 0) {
+                  bad_col = c;
+                  col_delta = delta;
+                }
+              } else if (pass == 0 && fabsf(delta) / thr > max_noise) {
+                max_noise = fabsf(delta) / thr;
+              }
+            }
+            if (pass == 0) {
+              first_nbr = nbr, first_nbc = nbc, first_bad_row = bad_row, first_bad_col = bad_col;
+              first_row_delta = row_delta, first_col_delta = col_delta;
+              if ((nbr == 0 && nbc == 0) || (nbr == 1 && nbc == 1)) break;
+              for (int r = 0; r < 64; ++r)
+                for (int c = 0; c < 64; ++c) {
+                  const float* qr = qf + (size_t)(qb * 64 + r) * dim;
+                  const float* kr = kf + (size_t)(j * 128 + c2 * 64 + c) * dim;
+                  float a = 0.0f;
+                  for (int d = 0; d < dim; ++d) a = fmaf(qr[d], kr[d], a);
+                  s[r * 128 + c2 * 64 + c] = a;
+                }
+            } else {
+              replayed_tile = nbr == 0 && nbc == 0;
             }
           }
-          for (int c = 0; c < 64; ++c) {
-            float expected, scale, actual = 0.0f;
-            strided_dot(kf + (size_t)(kb * 64 + c) * dim, q_sums + (size_t)qb * dim, q_mags + (size_t)qb * dim, dim, 0, &expected, &scale);
-            for (int r = 0; r < 64; ++r) actual += s[r * 128 + c2 * 64 + c];
-            float delta = expected - actual, thr = threshold(score_abs, score_rel, scale);
-            float margin = fabsf(fabsf(delta) - thr) / thr;
-            if (margin < min_margin) min_margin = margin;
-            if (fabsf(delta) > thr) {
-              if (nbc++ == 0) {
-                bad_col = c;
-                col_delta = delta;
-              }
-            } else if (fabsf(delta) / thr > max_noise) {
-              max_noise = fabsf(delta) / thr;
-            }
-          }
+          nbr = first_nbr, nbc = first_nbc, bad_row = first_bad_row, bad_col = first_bad_col;
+          row_delta = first_row_delta, col_delta = first_col_delta;
           if (nbr > 0 || nbc > 0) {
             int corrected = nbr == 1 && nbc == 1;
             if (corrected) s[bad_row * 128 + c2 * 64 + bad_col] = fmaf(0.5f, row_delta + col_delta, s[bad_row * 128 + c2 * 64 + bad_col]);
             ++score_detected;
             score_corrected += corrected;
-            score_uncorrected += !corrected;
+            score_replayed += !corrected && replayed_tile;
+            score_uncorrected += !corrected && !replayed_tile;
             if (records != NULL) {
               int slot;
 #pragma omp atomic capture
@@ -439,4 +469,5 @@ void ftq_attention_forward(const uint16_t* q16, const uint16_t* k16, const uint1
   stats->n_records = n_records;
   stats->max_score_noise = max_noise;
   stats->min_margin = min_margin;
+  stats->score_replayed = score_replayed;
 }

@@ -11,13 +11,15 @@ class AttnStats(ctypes.Structure):
     _fields_ = [("score_detected", ctypes.c_int), ("score_corrected", ctypes.c_int), ("score_uncorrected", ctypes.c_int),
                 ("pv_detected", ctypes.c_int), ("pv_corrected", ctypes.c_int), ("failed_rows", ctypes.c_int),
                 ("softmax_detected", ctypes.c_int), ("softmax_corrected", ctypes.c_int), ("softmax_replayed", ctypes.c_int),
-                ("n_records", ctypes.c_int), ("max_score_noise", ctypes.c_float), ("min_margin", ctypes.c_float)]
+                ("n_records", ctypes.c_int), ("max_score_noise", ctypes.c_float), ("min_margin", ctypes.c_float),
+                ("score_replayed", ctypes.c_int)]
 
 
 def forward(q, k, v, score_abs=1e-2, score_rel=2e-5, pv_abs=2e-3, pv_rel=2e-3, fault=None, max_records=64, protect_softmax=False,
             softmax_abs=2e-5, softmax_rel=2e-5, causal=False):
     """q, k, v: numpy float16 arrays [B, H, N, D], any N (zero-padded here to whole 128-row tiles).
-    fault = (stage, batch, head, query, index, value).  Returns (out float32 [B,H,N,D], stats, records)."""
+    fault = (stage, batch, head, query, index, value[, query2, index2, value2]): a score fault may carry a second one
+    in the same head.  Returns (out float32 [B,H,N,D], stats, records)."""
     lib = oracle_lib.load().lib
     b, h, valid, d = q.shape
     n = (valid + 127) // 128 * 128
@@ -29,12 +31,14 @@ def forward(q, k, v, score_abs=1e-2, score_rel=2e-5, pv_abs=2e-3, pv_rel=2e-3, f
     out = np.empty((b, h, valid, d), dtype=np.float32)
     stats = AttnStats()
     records = (oracle_lib.TileRecord * max_records)()
-    stage, fb, fh, fq, fi, fv = fault if fault is not None else (0, 0, 0, 0, 0, 0.0)
+    stage, fb, fh, fq, fi, fv = fault[:6] if fault is not None else (0, 0, 0, 0, 0, 0.0)
+    fq2, fi2, fv2 = fault[6:9] if fault is not None and len(fault) >= 9 else (0, 0, 0.0)
     ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
     lib.ftq_attention_forward(ptr(q16), ptr(k16), ptr(v16), b * h, n, valid, d, ctypes.c_float(score_abs), ctypes.c_float(score_rel),
                               ctypes.c_float(pv_abs), ctypes.c_float(pv_rel), ctypes.c_float(softmax_abs), ctypes.c_float(softmax_rel),
                               int(bool(protect_softmax)), int(bool(causal)), int(stage), int(fb * h + fh), int(fq), int(fi),
-                              ctypes.c_float(fv), ptr(out), ctypes.byref(stats), records, max_records)
+                              ctypes.c_float(fv), int(fq2), int(fi2), ctypes.c_float(fv2), ptr(out), ctypes.byref(stats), records,
+                              max_records)
     return out, stats, list(records[:stats.n_records])
 
 

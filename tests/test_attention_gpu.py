@@ -80,8 +80,48 @@ def test_score_faults_match_oracle(ftg, exact_prepare):
     op.close()
 
 
-def test_two_score_faults_in_one_tile_are_reported_not_corrected(ftg):
-    # the C-ABI takes one fault per run, so the second bad checksum comes from a stale cache: K changes after prepare
+@pytest.mark.parametrize("protect_softmax", [False, True])
+def test_score_tile_with_several_faults_is_replayed(ftg, protect_softmax):
+    """Two faults in one 64x64 score tile cannot be located by the row/column intersection: the tile is recomputed on
+    the CUDA cores, passes the check the second time and counts as replayed (src/ft_flash_attention_a14.cu:935-959);
+    the output equals the clean one.  Patterns: two rows and two columns, one row with two columns, one column with two
+    rows; both kernels (the split-row default and the whole-row kernel that carries the softmax-stage protection)."""
+    b, h, n = 1, 2, 512
+    q, k, v = _qkv(b, h, n, seed=21)
+    op = ftg.FtAttention(q, k, v, protect_softmax=protect_softmax)
+    clean = op.new_output()
+    op.run(clean)
+    assert op.report().score_detected == 0
+    out = op.new_output()
+    bands = n // 64
+    cases = [(0, 70, 200, 8.0, 100, 230, -5.0), (1, 300, 64, -6.0, 300, 100, 9.0), (0, 10, 450, 4.0, 40, 450, 7.0),
+             (1, 511, 511, 64.0, 450, 449, -32.0)]
+    for head, q1, k1, v1, q2, k2, v2 in cases:
+        assert q1 // 64 == q2 // 64 and k1 // 64 == k2 // 64
+        fault = (ftg.FAULT_SCORE, 0, head, q1, k1, v1, q2, k2, v2)
+        op.run(out, fault)
+        rep = op.report()
+        want, stats, records = oa.forward(_np(q), _np(k), _np(v), fault=fault, protect_softmax=protect_softmax)
+        assert stats.min_margin > 1e-3
+        assert (rep.score_detected, rep.score_corrected, rep.score_replayed, rep.score_uncorrected) == (1, 0, 1, 0) == \
+               (stats.score_detected, stats.score_corrected, stats.score_replayed, stats.score_uncorrected)
+        got, exp = rep.records[0], records[0]
+        assert (got.tile, got.bad_row_count, got.bad_col_count, got.corrected) == (exp.tile, exp.bad_row_count, exp.bad_col_count, 0)
+        assert got.tile == ((head * bands) + q1 // 64) * bands + k1 // 64
+        assert (rep.pv_detected, rep.failed_rows, rep.softmax_detected) == (0, 0, 0)
+        np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
+        np.testing.assert_allclose(_np(out), want, atol=2e-3, rtol=0)
+    # faults in two different tiles of one run are two single faults: both located and corrected
+    fault = (ftg.FAULT_SCORE, 0, 1, 20, 30, 5.0, 400, 300, -5.0)
+    op.run(out, fault)
+    rep = op.report()
+    assert (rep.score_detected, rep.score_corrected, rep.score_replayed, rep.score_uncorrected) == (2, 2, 0, 0)
+    np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
+    op.close()
+
+
+def test_stale_cache_tiles_stay_uncorrected_after_replay(ftg):
+    # K changes after prepare: the cached checksums are stale, so the replayed tiles disagree with them as well
     b, h, n = 1, 1, 256
     q, k, v = _qkv(b, h, n, seed=9)
     op = ftg.FtAttention(q, k, v)
@@ -90,6 +130,7 @@ def test_two_score_faults_in_one_tile_are_reported_not_corrected(ftg):
     op.run(out)
     rep = op.report()
     assert rep.score_detected >= n // 64 and rep.score_corrected == 0 and rep.score_uncorrected == rep.score_detected
+    assert rep.score_replayed == 0
     assert all(r.bad_col_count >= 1 and r.corrected == 0 for r in rep.records)
     op.close()
 

@@ -135,3 +135,19 @@ def test_sequence_lengths_that_are_not_whole_tiles():
     got, stats, _ = oa.forward(q, k, v, protect_softmax=True, fault=(2, 0, 0, 130, 199, 0.25))
     assert (stats.softmax_detected, stats.softmax_corrected) == (1, 1)
     np.testing.assert_allclose(got, clean, atol=1e-6, rtol=0)
+
+
+def test_oracle_replays_a_tile_with_two_faults():
+    """Two faults in one 64x64 score tile: not locatable, the tile is recomputed, passes the second check and counts as
+    replayed; the output is the clean one bit for bit (the recomputation is the oracle's own score arithmetic)."""
+    rng = np.random.default_rng(5)
+    q, k, v = (rng.standard_normal((1, 1, 256, 64)).astype(np.float16) for _ in range(3))
+    clean, stats0, _ = oa.forward(q, k, v)
+    assert (stats0.score_detected, stats0.score_replayed) == (0, 0)
+    out, stats, records = oa.forward(q, k, v, fault=(1, 0, 0, 70, 130, 6.0, 100, 180, -4.0))
+    assert (stats.score_detected, stats.score_corrected, stats.score_replayed, stats.score_uncorrected) == (1, 0, 1, 0)
+    assert (records[0].bad_row_count, records[0].bad_col_count, records[0].corrected) == (2, 2, 0)
+    np.testing.assert_array_equal(out, clean)
+    # in different tiles they are two single faults
+    out, stats, _ = oa.forward(q, k, v, fault=(1, 0, 0, 70, 130, 6.0, 200, 10, -4.0))
+    assert (stats.score_detected, stats.score_corrected, stats.score_replayed) == (2, 2, 0)
