@@ -317,13 +317,6 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const uint32_t o_addr = lane_addr + kTmemO + t * kOCols + c * kHalfDim;  // this half's output dims
       const uint32_t x_addr = lane_addr + kTmemO + t * kOCols + kDim;          // the checksum columns of the row
       uint8_t* p_row = smem_p + t * kTileBytes + c * kSlabBytes + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
-      const bool fault_head = p.fault_bh == bh;
-      const bool fault_here = fault_head && p.fault_query >= q_tile0 && p.fault_query < q_tile0 + kTile;
-      const bool score_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_SCORE && (p.fault_index % kTile) / 64 == c;
-      const bool score_fault2 = fault_head && p.fault_stage == FT_ATTN_FAULT_SCORE && p.fault2_value != 0.0f && p.fault2_query >= q_tile0 &&
-                                p.fault2_query < q_tile0 + kTile && (p.fault2_index % kTile) / 64 == c;
-      const bool output_fault = fault_here && p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_index / kHalfDim == c;
-      const int fault_row = p.fault_query - q_tile0;  // row in this tile, when fault_here
       TileScratch& scratch = sh.scratch[t][c][pair];
       uint32_t replays = 0;  // times this band went through the replay path (the phase of its barrier)
 
@@ -356,11 +349,14 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         tcgen05_fence_after();
 
         // test hook: the fault enters the accumulator itself, before any checksum
-        if (score_fault && p.fault_index / kTile == j && fault_row / 32 == quarter) {
-          tmem_add(s_addr + p.fault_index % 64, lane, fault_row % 32, p.fault_value);
-        }
-        if (score_fault2 && p.fault2_index / kTile == j && (p.fault2_query - q_tile0) / 32 == quarter) {
-          tmem_add(s_addr + p.fault2_index % 64, lane, (p.fault2_query - q_tile0) % 32, p.fault2_value);
+        if (p.fault_stage == FT_ATTN_FAULT_SCORE && p.fault_bh == bh) {  // uniform over the CTA
+          const int r1 = p.fault_query - q_tile0, r2 = p.fault2_query - q_tile0;
+          if (r1 >= 0 && r1 < kTile && p.fault_index / 64 == j * 2 + c && r1 / 32 == quarter) {
+            tmem_add(s_addr + p.fault_index % 64, lane, r1 % 32, p.fault_value);
+          }
+          if (p.fault2_value != 0.0f && r2 >= 0 && r2 < kTile && p.fault2_index / 64 == j * 2 + c && r2 / 32 == quarter) {
+            tmem_add(s_addr + p.fault2_index % 64, lane, r2 % 32, p.fault2_value);
+          }
         }
 
         // ---- the one read of this thread's scores: column checksums from the fragment layout, then the row into registers
@@ -394,24 +390,20 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               // The fault cannot be located: recompute the band's 64 x 64 scores without the tensor core and check again.
               const __half* q_row = static_cast<const __half*>(p.q) + (static_cast<size_t>(row_base) + q_tile0 + row_in_tile) * kDim;
               const __half* k_tile = static_cast<const __half*>(p.k) + (static_cast<size_t>(row_base) + j * kTile + c * 64) * kDim;
-              replay_score_row<kDim>(q_row, k_tile, v);
-              TileScratch& again = sh.replay_scratch[t][c][pair];
-              float ignored = 0.0f;
-              abft_tile_rows(v, lane, half, again, __ldg(p.expected_rows + cache + r_local), __ldg(p.row_scales + cache + r_local),
-                             p.score_abs_tol, p.score_rel_tol, ignored);
-              abft_tile_cols_from_rows(v, lane, half, again);
-              uint64_t* rbar = &sh.replay_bar[t][c][pair];
-              mbar_arrive(rbar);
-              if (!warp_wait(rbar, replays & 1, abort_flag)) {  // the partner warp gave up: this tile's band barrier is passed
+              float rv[64];
+              bool wait_ok = true;
+              replayed = replay_and_verify<kDim>(q_row, k_tile, rv, lane, half, &sh.replay_scratch[t][c][pair], p.expected_rows + cache,
+                                                 p.row_scales + cache, p.expected_cols + cache, p.col_scales + cache, p.score_abs_tol,
+                                                 p.score_rel_tol, &sh.replay_bar[t][c][pair], replays & 1, abort_flag, kTimeoutNs, &wait_ok);
+              if (!wait_ok) {  // the partner warp gave up: this tile's band barrier is passed, its tile barrier is owed
                 alive = false;
                 owed_pair_from = j + 1;
                 owed_tile_from = j;
                 break;
               }
               ++replays;
-              const TileDecision d2 = abft_tile_decide(lane, again, exp_col0, exp_col1, scale_col0, scale_col1, p.score_abs_tol,
-                                                       p.score_rel_tol, ignored);
-              replayed = (d2.bad_rows | d2.bad_cols) == 0;
+#pragma unroll
+              for (int i = 0; i < 64; ++i) v[i] = rv[i];
             }
             local_max = masked_row_max(v, diagonal, c * 64, key_limit);
             if (half == 0 && lane == 0) {
@@ -514,7 +506,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       float inv_l = 0.0f, es_total = 0.0f, ew_total = 0.0f;
       float actual_sum = 0.0f, actual_weighted = 0.0f;
       const int query = q_tile0 + row_in_tile;
-      const bool my_fault = output_fault && fault_row == row_in_tile;
+      const bool my_fault = p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_bh == bh && p.fault_query == query && p.fault_index / kHalfDim == c;
       if (alive) {
         tcgen05_fence_after();
         {
