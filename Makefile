@@ -9,7 +9,7 @@ NVCCFLAGS ?= -O3 -std=c++17 -lineinfo $(ARCH) -Xcompiler -fPIC -Xptxas -v
 CSRC      := ft_gemm_b200/csrc
 LIB       := ft_gemm_b200/lib/libft_gemm_b200.so
 OBJS      := build/obj/prepare.o build/obj/prepare_mma.o build/obj/abft_gemm.o build/obj/api.o build/obj/noalloc.o build/obj/ft_attention.o build/obj/ft_attention_split.o build/obj/api_attention.o build/obj/gemm_softmax.o
-HDRS      := include/ft_gemm.h include/ft_attention.h include/ft_gemm_softmax.h $(CSRC)/kernels.h $(CSRC)/attention_kernels.h $(CSRC)/abft_tile_check.cuh $(CSRC)/sm100_ptx.cuh
+HDRS      := include/ft_gemm.h include/ft_attention.h include/ft_gemm_softmax.h $(CSRC)/kernels.h $(CSRC)/attention_kernels.h $(CSRC)/attention_device.cuh $(CSRC)/abft_tile_check.cuh $(CSRC)/sm100_ptx.cuh
 
 # the campaign the 100 % single-fault correction claim is quoted on: 8192^3, N(0,1) inputs, 1000 single faults U[1,256]
 # with random sign + 50 double faults, relative tolerance 2e-6 (the reference's default 2e-5 puts the threshold near 6.7
@@ -37,19 +37,19 @@ $(LIB): $(OBJS)
 
 cli: build/stage_abft_fp8_gemm build/fault_campaign build/cublaslt_fp8_bench build/ft_flash_attention build/gemm_softmax_abft
 
-build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(LIB)
+build/stage_abft_fp8_gemm: $(CSRC)/cli/stage_abft_fp8_gemm.cpp $(CSRC)/cli/cli_common.h $(HDRS) $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -lnccl -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
-build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(LIB)
+build/fault_campaign: $(CSRC)/cli/fault_campaign.cpp $(CSRC)/cli/cli_common.h $(HDRS) $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
-build/ft_flash_attention: $(CSRC)/cli/ft_flash_attention.cpp $(CSRC)/cli/cli_common.h $(LIB)
+build/ft_flash_attention: $(CSRC)/cli/ft_flash_attention.cpp $(CSRC)/cli/cli_common.h $(HDRS) $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
-build/gemm_softmax_abft: $(CSRC)/cli/gemm_softmax_abft.cpp $(CSRC)/cli/cli_common.h $(LIB)
+build/gemm_softmax_abft: $(CSRC)/cli/gemm_softmax_abft.cpp $(CSRC)/cli/cli_common.h $(HDRS) $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
-build/cublaslt_fp8_bench: $(CSRC)/cli/cublaslt_fp8_bench.cpp $(CSRC)/cli/cli_common.h $(LIB)
+build/cublaslt_fp8_bench: $(CSRC)/cli/cublaslt_fp8_bench.cpp $(CSRC)/cli/cli_common.h $(HDRS) $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -lcublasLt -lcublas -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
 oracle:

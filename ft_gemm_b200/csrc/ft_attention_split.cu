@@ -60,6 +60,7 @@ constexpr int kProducerRegs = 32;
 constexpr int kSoftmaxRegs = 112;
 static_assert(128 * kProducerRegs + 512 * kSoftmaxRegs <= kThreads * kLaunchRegs, "setmaxnreg.inc would wait for registers the CTA does not own");
 constexpr uint64_t kTimeoutNs = 2000000000ull;
+constexpr float kRescaleStep = 8.0f;  // log2 units: the exponent reference follows the row maximum in steps of at least this
 constexpr uint32_t kTmemS = 0;    // the score buffer, shared by the two query tiles
 constexpr uint32_t kTmemO = 128;  // output accumulators of tile A, B: kDim + kAttnVExtra columns each
 
@@ -430,10 +431,18 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
         const float row_max = fmaxf(local_max, sh.row_max[t][buf][c ^ 1][row_in_tile]);
 
-        // ---- online softmax state (log2 domain); identical in both threads of the row
-        const float m_new = fmaxf(m_run, row_max * p.scale_log2);
-        const float alpha = fast_exp2(m_run - m_new);  // 0 for the first tile (m_run = -inf)
-        m_run = m_new;
+        // ---- online softmax state (log2 domain); identical in both threads of the row.  The reference point of the
+        // exponentials moves only when the tile's maximum exceeds it by more than kRescaleStep: probabilities then stay
+        // below 2^kRescaleStep (exact in FP16 up to 2^16, and l, O and the checksum columns all carry the same factor,
+        // which the final division removes), and the pass over O that a moved reference costs becomes rare instead of
+        // happening whenever any of the warp's 32 rows sees a new maximum.
+        const float m_tile = row_max * p.scale_log2;
+        float alpha = 1.0f;
+        if (m_tile > m_run + kRescaleStep) {  // always for the first tile (m_run = -inf)
+          alpha = fast_exp2(m_run - m_tile);  // 0 for the first tile
+          m_run = m_tile;
+        }
+        const float m_new = m_run;
 
         if (j > 0) {
           // PV of the previous tile must have finished: the P buffer is free and O is quiescent

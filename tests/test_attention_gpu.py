@@ -215,8 +215,10 @@ def test_softmax_stage_protection(ftg):
     op.run(clean)
     rep = op.report()
     assert (rep.softmax_detected, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
-    # the protection changes nothing when nothing is wrong (the two kernels add the row sums in a different order)
-    assert float((clean - plain).abs().max()) < 2e-6
+    # The protection changes nothing when nothing is wrong.  The two kernels round their FP16 probabilities against
+    # different exponent references (the split-row kernel moves its reference in steps of 2^8, the whole-row kernel
+    # follows the running maximum), so they agree to FP16 rounding of the probabilities, not to the last bit.
+    assert float((clean - plain).abs().max()) < 5e-4
     want, _, _ = oa.forward(_np(q), _np(k), _np(v), protect_softmax=True)
     np.testing.assert_allclose(_np(clean), want, atol=2e-3, rtol=0)
     out = op.new_output()
@@ -282,7 +284,7 @@ def test_causal_forward_and_faults(ftg, n):
     protected = op.new_output()
     op.run(protected)
     # the protected form runs in the whole-row kernel, which adds the row sums in another order than the split-row one
-    assert float((protected - clean).abs().max()) < 2e-6 and op.report().softmax_detected == 0
+    assert float((protected - clean).abs().max()) < 5e-4 and op.report().softmax_detected == 0  # FP16 rounding of the probabilities against different exponent references
     fault = (ftg.FAULT_SOFTMAX, 0, 1, n - 1, n - 3, 0.25)
     op.run(out, fault)
     rep = op.report()
@@ -365,7 +367,8 @@ def test_sequence_lengths_that_are_not_whole_tiles(ftg, n, d, causal):
         op.run(out, (2, 0, 0, last, key // 2 if causal else key, 0.25))
         rep = op.report()
         assert (rep.softmax_detected, rep.softmax_corrected) == (1, 1)
-        np.testing.assert_allclose(_np(out), _np(clean), atol=1e-5, rtol=0)
+        # `clean` came from the split-row kernel, this output from the whole-row kernel: FP16 rounding of the probabilities apart
+        np.testing.assert_allclose(_np(out), _np(clean), atol=5e-4, rtol=0)
         op.close()
 
 
