@@ -96,6 +96,29 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int gro
   nb = in_group / group_m;
 }
 
+// Work item `w` of a launch -> its output tile.  Items below `split_from` are whole tiles (256 columns); every tile from
+// there on is cut into `split` column slices of 256 / split columns, each an item of its own (GemmParams::split).
+// Returns false for a slice that lies entirely past the last column of the window (ragged N): such an item is skipped
+// by every role alike.
+struct WorkItem {
+  int mb, nb;   // row block (of the form's tile height) and 256-column block, relative to the window
+  int col_off;  // first column of the slice inside the 256-column block
+  int width;    // columns of the slice: 256, 128 or 64
+};
+__device__ __forceinline__ bool work_item(int w, int num_m, int num_n, int group, int split_from, int split, int cols, WorkItem& item) {
+  int t = w, slice = 0;
+  item.width = kBlockN;
+  if (w >= split_from) {
+    const int r = w - split_from;
+    t = split_from + r / split;
+    slice = r % split;
+    item.width = kBlockN / split;
+  }
+  tile_coords(t, num_m, num_n, group, item.mb, item.nb);
+  item.col_off = slice * item.width;
+  return item.nb * kBlockN + item.col_off < cols;
+}
+
 __device__ __forceinline__ bool any_over_epilogue(bool flag) {
   uint32_t out;
   asm volatile(
@@ -140,6 +163,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int first_mb = p.row0 / Cfg::kTileM;
   const int first_nb = p.col0 / kBlockN;
   const int num_tiles = num_m * num_n;
+  const int split_from = min(p.split_from, num_tiles);
+  const int num_items = split_from + (num_tiles - split_from) * p.split;  // whole tiles, then column slices of the rest
   const int num_kb = (p.k + kBlockK - 1) / kBlockK;    // a short last K block is zero-filled by the copy engine
   const int kGroupM = max(1, p.group_rows / Cfg::kTileM);  // row blocks walked together (see GemmParams::group_rows)
   constexpr bool profiling = kProfile;
@@ -185,13 +210,14 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t phase = 0;
       bool alive = true;
       long long waited = 0;
-      for (int t = worker; t < num_tiles && alive; t += workers) {
-        int mb, nb;
-        tile_coords(t, num_m, num_n, kGroupM, mb, nb);
-        mb += first_mb;
-        nb += first_nb;
+      for (int w = worker; w < num_items && alive; w += workers) {
+        WorkItem item;
+        if (!work_item(w, num_m, num_n, kGroupM, split_from, p.split, p.cols, item)) continue;
+        const int mb = item.mb + first_mb, nb = item.nb + first_nb;
         const int a_row = mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM;
-        const int b_row = nb * kBlockN + static_cast<int>(rank) * Cfg::kBRows;
+        // Each CTA of a pair stages its half of the slice's B rows.  The copy always brings a full box (the byte count
+        // of a stage does not change); for a narrow slice the rows behind the ones the MMA reads are simply not used.
+        const int b_row = nb * kBlockN + item.col_off + static_cast<int>(rank) * (kPair ? item.width / 2 : 0);
         for (int kb = 0; kb < num_kb; ++kb) {
           const long long t0 = profiling ? clock64() : 0;
           if (!mbar_wait_bounded(&tail.empty[s], phase ^ 1, abort_flag, p.wait_timeout_ns)) {
@@ -221,7 +247,6 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (the leader only, in the pair form)
     if (rank == 0 && elect_one()) {
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(Cfg::kTileM, kBlockN);
       int s = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -229,7 +254,10 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       bool alive = true;
       long long wait_full = 0, wait_tmem = 0;
       const long long role_start = profiling ? clock64() : 0;
-      for (int t = worker; t < num_tiles && alive; t += workers) {
+      for (int w = worker; w < num_items && alive; w += workers) {
+        WorkItem item;
+        if (!work_item(w, num_m, num_n, kGroupM, split_from, p.split, p.cols, item)) continue;
+        const uint32_t idesc = make_idesc_e4m3_f32(Cfg::kTileM, item.width);
         long long t0 = profiling ? clock64() : 0;
         if (!mbar_wait_bounded(&tail.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.wait_timeout_ns)) break;
         if (profiling) wait_tmem += clock64() - t0;
@@ -295,20 +323,21 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     float max_ratio = 0.0f;
     long long epi_wait = 0, tiles_done = 0;
     const long long epi_start = profiling ? clock64() : 0;
-    for (int t = worker; t < num_tiles; t += workers) {
-      int mb, nb;
-      tile_coords(t, num_m, num_n, kGroupM, mb, nb);
-      mb += first_mb;
-      nb += first_nb;
+    for (int w = worker; w < num_items; w += workers) {
+      WorkItem item;
+      if (!work_item(w, num_m, num_n, kGroupM, split_from, p.split, p.cols, item)) continue;
+      const int mb = item.mb + first_mb, nb = item.nb + first_nb;
+      const int col_base = nb * kBlockN + item.col_off;  // first column of C this item covers
+      const int item_groups = item.width / kGroupCols;
       {
         // The cached expected checksums of this tile's (up to) four ABFT tiles are asked for while the main loop still runs:
         // with few tiles per CTA nothing else hides their latency.  Lines of row blocks or column groups past the
         // matrix are not touched.
         const int pf_row = (mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM) / kGroupCols + pair;
         if (pf_row * kGroupCols < p.m) {
-          const int pf_groups = min(kGroups, (p.n - nb * kBlockN + kGroupCols - 1) / kGroupCols);
+          const int pf_groups = min(item_groups, (p.n - col_base + kGroupCols - 1) / kGroupCols);
           for (int g = 0; g < pf_groups; ++g) {
-            const size_t cache = static_cast<size_t>(pf_row * tile_cols + nb * kGroups + g) * kGroupCols;
+            const size_t cache = static_cast<size_t>(pf_row * tile_cols + col_base / kGroupCols + g) * kGroupCols;
             prefetch_l1(p.expected_rows + cache + r_local);
             prefetch_l1(p.row_scales + cache + r_local);
             prefetch_l1(p.expected_cols + cache + 2 * lane);
@@ -333,10 +362,10 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const bool band_valid = tile_row * kGroupCols < p.m;
       const int valid_rows = min(kGroupCols, p.m - tile_row * kGroupCols);
       // 64-column groups of this tile that hold at least one column of C (src/s3:418-419)
-      const int groups_here = min(kGroups, (p.n - nb * kBlockN + kGroupCols - 1) / kGroupCols);
+      const int groups_here = min(item_groups, (p.n - col_base + kGroupCols - 1) / kGroupCols);
 #pragma unroll 1
       for (int g = 0; g < groups_here; ++g) {
-        const int valid_cols = min(kGroupCols, p.n - nb * kBlockN - g * kGroupCols);
+        const int valid_cols = min(kGroupCols, p.n - col_base - g * kGroupCols);
         if (!band_valid) {  // uniform over the two warps of the band
           if (g == groups_here - 1) {
             tcgen05_fence_before();
@@ -348,7 +377,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
           continue;
         }
-        const int tile_id = tile_row * tile_cols + nb * kGroups + g;
+        const int tile_id = tile_row * tile_cols + col_base / kGroupCols + g;
         const size_t cache = static_cast<size_t>(tile_id) * kGroupCols;
         const float exp_row = __ldg(p.expected_rows + cache + r_local);
         const float scale_row = __ldg(p.row_scales + cache + r_local);
@@ -504,7 +533,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
 
         // C is column-major [N,M]: for a fixed column the 32 lanes write 32 consecutive floats
-        float* cptr = p.c + static_cast<size_t>(nb * kBlockN + g * kGroupCols) * p.m + grow;
+        float* cptr = p.c + static_cast<size_t>(col_base + g * kGroupCols) * p.m + grow;
         if (valid_cols == kGroupCols && valid_rows == kGroupCols) {
 #pragma unroll
           for (int c = 0; c < kGroupCols; ++c) __stcs(cptr + static_cast<size_t>(c) * p.m, v[c]);

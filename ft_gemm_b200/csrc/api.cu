@@ -88,6 +88,7 @@ struct ft_gemm_handle {
   int m = 0, n = 0, k = 0;
   int sm_count = 0;
   int grid = 0;
+  int max_workers = 0;  // persistent CTAs (pairs in the 2-CTA form) a launch may use
   ft_options options{};
   const void* a = nullptr;
   const void* b = nullptr;
@@ -209,6 +210,36 @@ void fill_params(const ft_gemm_handle* h, float* c, GemmParams* params) {
   const int row_blocks = (h->m + tile_m - 1) / tile_m;
   const int groups = (row_blocks + per_group - 1) / per_group;
   params->group_rows = (row_blocks + groups - 1) / groups * tile_m;  // groups of equal height
+  params->split_from = 0x7fffffff;  // whole tiles only, unless the caller of the launch decides otherwise
+  params->split = 1;
+}
+
+// How the tail of a launch is cut into column slices (GemmParams::split_from / split).  Model, in units of one whole
+// tile's main loop: a worker's time is its whole tiles, then its slices (a slice of 256/s columns costs c(s)/s, the
+// narrower MMA shapes being a little less efficient), each overlapped with the previous item's epilogue, plus the one
+// epilogue that overlaps nothing.  e = epilogue / main loop of a whole tile, about 0.2 at K = 8192 and growing as K
+// shrinks.  The smallest s within 2 % of the best wins.
+void choose_split(int tiles, int workers, int k, int* split_from, int* split) {
+  *split_from = tiles;
+  *split = 1;
+  if (workers <= 0 || tiles <= 0) return;
+  const int full = tiles >= workers ? (tiles / workers) * workers : 0;
+  const int tail = tiles - full;
+  if (tail == 0) return;
+  const double e = std::min(4.0, 0.2 * 8192.0 / std::max(k, 1));
+  const int rounds_full = full / workers;
+  double best_time = 0.0;
+  for (int s = 1; s <= 4; s *= 2) {
+    const double c = s == 1 ? 1.0 : (s == 2 ? 1.04 : 1.3);
+    const int tail_rounds = (tail * s + workers - 1) / workers;
+    const double main = c / s, epi = e / s;
+    const double time = rounds_full * std::max(1.0, e) + tail_rounds * std::max(main, epi) + std::min(main, epi);
+    if (s == 1 || time < 0.98 * best_time) {
+      best_time = time;
+      *split = s;
+    }
+  }
+  *split_from = full;
 }
 
 // Largest chunk count g <= kMaxPipeChunks for which M/g and N/g are whole tiles; 1 = no pipelining.
@@ -350,9 +381,11 @@ int ft_gemm_fp8_abft_prepare(ft_gemm_handle** handle, const void* a, const void*
   int sm_cap = opts.sm_limit > 0 ? std::min(opts.sm_limit, h->sm_count) : h->sm_count;
   if (h->pair) {
     int tiles = (m / 256) * ((n + 255) / 256);
+    h->max_workers = std::max(1, sm_cap / 2);
     h->grid = 2 * std::max(1, std::min(tiles, sm_cap / 2));
   } else {
     int tiles = ((m + 127) / 128) * ((n + 255) / 256);
+    h->max_workers = std::max(1, sm_cap);
     h->grid = std::min(tiles, sm_cap);
   }
 
@@ -498,7 +531,10 @@ int ft_gemm_fp8_abft_run_window(ft_gemm_handle* h, float* c, const ft_fault* fau
     params.clear_counters = reinterpret_cast<int*>(h->report_pair + (h->report_index ^ 1));
   }
   int tiles = ((rows + tile_m - 1) / tile_m) * ((cols + 255) / 256);
-  int grid = h->pair ? std::min(h->grid, 2 * tiles) : std::min(h->grid, tiles);
+  choose_split(tiles, h->max_workers, h->k, &params.split_from, &params.split);
+  const int items = params.split_from + (tiles - params.split_from) * params.split;
+  const int workers = std::min(h->max_workers, items);
+  const int grid = h->pair ? 2 * workers : workers;
   FT_CUDA(launch_abft_gemm(h->tmap_a, h->tmap_b, params, grid, h->pair, stream));
   h->last_stream = stream;
   return FT_OK;

@@ -50,6 +50,12 @@ struct GemmParams {
   // a quarter of the L2, between 1024 and 8192 rows: at K = 8192 that is 4096 rows (measured at 8192^3: 2048 rows -1.6 %,
   // 8192 rows -7 %; 8192 x 8192 x 4096 gains 3.7 % with 8192 rows over 2048).
   int group_rows;
+  // Column slices for the tail of a launch.  The tiles are dealt out round robin to the persistent CTAs (pairs); when
+  // their number is not a multiple of the worker count the last round keeps only some workers busy, and with few tiles
+  // per worker the epilogue of the last tile overlaps nothing.  Tiles from index split_from on are therefore cut into
+  // `split` (1, 2 or 4) column slices of 256 / split columns, each scheduled as an item of its own: the last round
+  // spreads over more workers, and a worker's last epilogue covers a slice instead of a tile.
+  int split_from, split;
   FaultParams faults;
   // optional per-CTA cycle counters (8 x uint64 per CTA), nullptr in normal runs:
   // [0] producer waiting for a free stage, [1] MMA waiting for a full stage, [2] MMA waiting for a drained
