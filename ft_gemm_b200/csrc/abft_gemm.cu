@@ -16,19 +16,24 @@
 //     mbarrier full/empty pairs;
 //   * warp 1: one thread issues tcgen05.mma kind::f8f6f4 from shared-memory
 //     descriptors into one of two 256-column TMEM accumulators;
-//   * warps 2-5: epilogue.  Each thread owns one accumulator row; per 64-column
-//     group it loads 64 values from TMEM into registers, forms the row sum
-//     serially, the column sums by a transpose-reduce butterfly of warp
-//     shuffles, exchanges them with its partner warp (the other 32 rows of the
-//     64-row ABFT tile), decides, corrects the faulty element in its registers and
-//     only then stores.  The epilogue of tile i runs while the main loop of tile
-//     i+1 fills the other accumulator.
+//   * warps 2-9: epilogue, two sets of four warps (one warp per TMEM lane quarter
+//     in each set); set e takes the 64-column groups g = e, e+2 of a tile, so that
+//     every scheduler has two epilogue warps to switch between.  Each thread owns
+//     one accumulator row; per group the warp first reads its 32 x 64 block in the
+//     16x256b fragment layout and forms the column sums over its rows (packed
+//     additions, 14 shuffles), then loads the row's 64 values into registers,
+//     forms the row sum serially (the reference's order), exchanges the column
+//     sums with its partner warp (the other 32 rows of the 64-row ABFT tile),
+//     decides, corrects the faulty element in its registers and only then
+//     stores.  The epilogue of tile i runs while the main loop of tile i+1 fills
+//     the other accumulator.
 //
 // Every wait is bounded: on expiry the kernel sets report->status and leaves.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "abft_tile_check.cuh"
 #include "kernels.h"
 #include "sm100_ptx.cuh"
 
@@ -41,8 +46,9 @@ constexpr int kUmmaK = 32;
 constexpr int kABytes = kBlockM * kBlockK;
 constexpr int kTmemColumns = 512;
 constexpr int kAccumulators = 2;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kEpilogueSets = 2;  // sets of four epilogue warps; a set covers all four TMEM lane quarters
+constexpr int kEpilogueThreads = 128 * kEpilogueSets;
+constexpr int kThreads = 64 + kEpilogueThreads;
 constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
 constexpr int kGroups = kBlockN / kGroupCols;
 constexpr int kMaxStages = 7;
@@ -77,13 +83,15 @@ struct SharedTail {
   uint64_t tmem_empty[kAccumulators];
   uint32_t tmem_base;
   int abort_flag;
-  EpilogueScratch scratch[2][2];  // [row pair][parity]
+  EpilogueScratch scratch[kEpilogueSets][2];  // [epilogue set][row pair]
 };
 
 template <bool kPair>
 constexpr int smem_bytes() {
   return Config<kPair>::kStages * Config<kPair>::kStageBytes + static_cast<int>(sizeof(SharedTail));
 }
+
+static_assert(smem_bytes<true>() <= 232448 && smem_bytes<false>() <= 232448, "more dynamic shared memory than a CTA can have on sm_100");
 
 // tile index -> (row block of kTileM rows, column block of 256 columns)
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int group, int& mb, int& nb) {
@@ -124,7 +132,7 @@ __device__ __forceinline__ bool any_over_epilogue(bool flag) {
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %1, 0;\n\t"
-      "barrier.cta.red.or.pred q, 3, 128, p;\n\t"
+      "barrier.cta.red.or.pred q, 3, 256, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(out)
       : "r"(static_cast<uint32_t>(flag))
@@ -313,11 +321,12 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else {
     // ------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int set = (warp - 2) >> 2;  // which of the two epilogue sets: it takes the column groups g with g % 2 == set
     const int pair = quarter >> 1;  // which 64-row ABFT band of this CTA's 128 rows
     const int half = quarter & 1;   // which 32 rows of that band
     const int r_local = half * 32 + lane;
     const int tile_cols = (p.n + kGroupCols - 1) / kGroupCols;
-    uint32_t groups_done = 0;  // selects the scratch buffer; counts across tiles because a ragged tile may hold an odd number of groups
+    uint32_t groups_done = 0;  // groups this warp has checked so far
     int acc = 0;
     uint32_t acc_phase = 0;
     float max_ratio = 0.0f;
@@ -336,7 +345,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int pf_row = (mb * Cfg::kTileM + static_cast<int>(rank) * kBlockM) / kGroupCols + pair;
         if (pf_row * kGroupCols < p.m) {
           const int pf_groups = min(item_groups, (p.n - col_base + kGroupCols - 1) / kGroupCols);
-          for (int g = 0; g < pf_groups; ++g) {
+          for (int g = set; g < pf_groups; g += kEpilogueSets) {
             const size_t cache = static_cast<size_t>(pf_row * tile_cols + col_base / kGroupCols + g) * kGroupCols;
             prefetch_l1(p.expected_rows + cache + r_local);
             prefetch_l1(p.row_scales + cache + r_local);
@@ -363,11 +372,21 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int valid_rows = min(kGroupCols, p.m - tile_row * kGroupCols);
       // 64-column groups of this tile that hold at least one column of C (src/s3:418-419)
       const int groups_here = min(item_groups, (p.n - col_base + kGroupCols - 1) / kGroupCols);
+      // this set's groups: set, set + 2, ...; after its last one (or at once, when it has none) the set lets go of the accumulator
+      const int last_group = groups_here - 1 - ((groups_here - 1 - set) & 1);  // largest g < groups_here with g % 2 == set; < set if none
+      if (last_group < set) {
+        tcgen05_fence_before();
+        if (kPair) {
+          mbar_arrive_cluster(map_to_cta(smem_u32(&tail.tmem_empty[acc]), 0));
+        } else {
+          mbar_arrive(&tail.tmem_empty[acc]);
+        }
+      }
 #pragma unroll 1
-      for (int g = 0; g < groups_here; ++g) {
+      for (int g = set; g < groups_here; g += kEpilogueSets) {
         const int valid_cols = min(kGroupCols, p.n - col_base - g * kGroupCols);
         if (!band_valid) {  // uniform over the two warps of the band
-          if (g == groups_here - 1) {
+          if (g == last_group) {
             tcgen05_fence_before();
             if (kPair) {
               mbar_arrive_cluster(map_to_cta(smem_u32(&tail.tmem_empty[acc]), 0));
@@ -386,12 +405,16 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const float scale_col0 = __ldg(p.col_scales + cache + lane);
         const float scale_col1 = __ldg(p.col_scales + cache + 32 + lane);
 
-        float v[kGroupCols];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN + g * kGroupCols;
+        // Column sums over this warp's 32 rows from a read in the fragment layout.  A test fault is added to the
+        // accumulator below, in registers; the column it lands in gets its share here.
+        float col_sum_a, col_sum_b;  // columns 2*lane and 2*lane+1
+        tmem_column_sums_32x64(taddr, lane, col_sum_a, col_sum_b);
+        float v[kGroupCols];
         tmem_ld_32x32b_x32(taddr, v);
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
-        if (g == groups_here - 1) {
+        if (g == last_group) {
           // the accumulator is now entirely in registers: hand it back to the MMA warp (of the leader)
           tcgen05_fence_before();
           if (kPair) {
@@ -414,6 +437,14 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   if (c == fc) v[c] += p.faults.value[f];
                 }
               }
+              // the warp that holds the row also holds its share of the column's checksum: the lane with column fc adds the value
+              if (fr / 32 == half && (fc >> 1) == lane) {
+                if ((fc & 1) == 0) {
+                  col_sum_a += p.faults.value[f];
+                } else {
+                  col_sum_b += p.faults.value[f];
+                }
+              }
             }
           }
         }
@@ -427,33 +458,12 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const bool row_bad = fabsf(row_delta) > row_thr;
         if (!row_bad) max_ratio = fmaxf(max_ratio, __fdividef(fabsf(row_delta), row_thr));
 
-        // column sums over this warp's 32 rows: transpose-reduce butterfly
-        float w[32];
-        {
-          const bool upper = (lane & 16) != 0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float send = upper ? v[i] : v[i + 32];
-            float keep = upper ? v[i + 32] : v[i];
-            w[i] = keep + __shfl_xor_sync(0xffffffffU, send, 16);
-          }
-          int n = 16;
-#pragma unroll
-          for (int off = 8; off >= 1; off >>= 1) {
-            const bool up = (lane & off) != 0;
-#pragma unroll
-            for (int i = 0; i < n; ++i) {
-              float send = up ? w[i] : w[i + n];
-              float keep = up ? w[i + n] : w[i];
-              w[i] = keep + __shfl_xor_sync(0xffffffffU, send, off);
-            }
-            n >>= 1;
-          }
-        }
-        // w[0], w[1] = sums of columns 2*lane, 2*lane+1 over 32 rows
-        EpilogueScratch& sc = tail.scratch[pair][groups_done & 1];
+        EpilogueScratch& sc = tail.scratch[set][pair];
+        // the partner warp may still be reading the previous group's sums (shared memory has no room for a second copy
+        // beside seven pipeline stages): meet it once before writing, once after
+        if (groups_done != 0) asm volatile("bar.sync %0, 64;" ::"r"(1 + 3 * set + pair) : "memory");
         ++groups_done;
-        *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(w[0], w[1]);
+        *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(col_sum_a, col_sum_b);
         const uint32_t row_mask = __ballot_sync(0xffffffffU, row_bad);
         const int first_lane = row_mask != 0 ? __ffs(row_mask) - 1 : 0;
         const float first_delta = __shfl_sync(0xffffffffU, row_delta, first_lane);
@@ -462,11 +472,8 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           sc.rows[half].first = row_mask != 0 ? half * 32 + first_lane : -1;
           sc.rows[half].delta = first_delta;
         }
-        if (pair == 0) {
-          named_barrier_sync<1, 64>();
-        } else {
-          named_barrier_sync<2, 64>();
-        }
+        // 64-thread barrier of this set's band: ids 1, 2 (set 0) and 4, 5 (set 1); id 3 is the epilogue-wide one
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + 3 * set + pair) : "memory");
 
         // every warp of the pair checks all 64 columns (lane: columns lane, lane+32)
         const float col_sum0 = sc.colpart[0][lane] + sc.colpart[1][lane];

@@ -103,12 +103,13 @@ __device__ __forceinline__ void abft_tile_cols_from_rows(const float (&v)[64], i
   *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(w[0], w[1]);
 }
 
-// Column part straight from tensor memory: the warp's 32 lanes x 64 columns at `taddr` (lane field = first lane of the
+// Column sums straight from tensor memory: the warp's 32 lanes x 64 columns at `taddr` (lane field = first lane of the
 // warp's quarter) are read a second time in the 16-lane x 256-bit fragment layout, in which a thread holds two adjacent
 // columns of four rows per 8-column block.  Three packed additions per block fold the four rows, then a
 // transpose-reduce over the eight row groups (lane bits 2..4) leaves the sums of columns 2*lane and 2*lane+1 in each
-// thread: 14 shuffles instead of 63, and the additions work on FP32 pairs.
-__device__ __forceinline__ void abft_tile_cols_from_tmem(uint32_t taddr, int lane, int half, TileScratch& sc) {
+// thread (c0, c1): 14 shuffles instead of 63, and the additions work on FP32 pairs.  abft_tile_cols_from_tmem publishes
+// them as the warp's column part of a tile check.
+__device__ __forceinline__ void tmem_column_sums_32x64(uint32_t taddr, int lane, float& c0, float& c1) {
   float a[32], b[32];
   tmem_ld_16x256b_x8(taddr, a);                // lanes +0 .. +15
   tmem_ld_16x256b_x8(taddr + (16u << 16), b);  // lanes +16 .. +31
@@ -132,8 +133,12 @@ __device__ __forceinline__ void abft_tile_cols_from_tmem(uint32_t taddr, int lan
     n >>= 1;
   }
   // block index kept = lane >> 2, columns 8*(lane>>2) + 2*(lane&3) + {0,1} = 2*lane + {0,1}
-  float c0, c1;
   unpack_f32x2(s[0], c0, c1);
+}
+
+__device__ __forceinline__ void abft_tile_cols_from_tmem(uint32_t taddr, int lane, int half, TileScratch& sc) {
+  float c0, c1;
+  tmem_column_sums_32x64(taddr, lane, c0, c1);
   *reinterpret_cast<float2*>(&sc.colpart[half][2 * lane]) = make_float2(c0, c1);
 }
 
