@@ -562,8 +562,28 @@ def main():
         cublaslt["tflops"] = max(rates) if rates else None
 
     fix_rate = None
+    smaller = None
     if rank == 0 and world == 1 and not args.no_extras:
         fix_rate = _fault_fix_rate(local_rank)
+        # the smaller configurations (M=N=K = 1024 and 4096 are named ones; 2048 lies between) through the stage program with
+        # the reference's timing method (3 warm-up + 10 timed, one event pair per call, src/s4:692-702) and with one event
+        # pair around all repeats, beside the autotuned cuBLASLt comparator timed both ways
+        smaller = {}
+        for size in (1024, 2048, 4096):
+            ours = _program("stage_abft_fp8_gemm", "--m", size, "--n", size, "--k", size, "--dist", "normal", "--warmup", 3, "--repeat", 10)
+            theirs = _program("cublaslt_fp8_bench", "--m", size, "--n", size, "--k", size, "--dist", "normal", "--warmup", 20, "--repeat", 50)
+            entry = {}
+            if ours is not None and "fused_gemm_tflops" in ours:
+                entry.update({"per_call_tflops": float(ours["fused_gemm_tflops"]), "batched_tflops": float(ours["batched_fused_gemm_tflops"]),
+                              "first_call_tflops": float(ours["first_call_tflops"]), "amortized_tflops": float(ours["amortized_tflops"]),
+                              "prepare_ms": float(ours["metadata_prepare_time_ms"]), "verification": ours.get("verification")})
+            if theirs is not None and "throughput_tflops" in theirs:
+                entry.update({"cublaslt_batched_tflops": float(theirs["throughput_tflops"]),
+                              "cublaslt_per_call_tflops": float(theirs["per_call_throughput_tflops"])})
+            if "per_call_tflops" in entry and "cublaslt_per_call_tflops" in entry:
+                entry["frac_of_cublaslt_per_call"] = entry["per_call_tflops"] / entry["cublaslt_per_call_tflops"]
+                entry["frac_of_cublaslt_batched"] = entry["batched_tflops"] / entry["cublaslt_batched_tflops"]
+            smaller[f"{size}^3"] = entry
 
     if rank == 0:
         peak, peak_note = _peaks(elapsed_ms * 1e-3)
@@ -600,6 +620,8 @@ def main():
             line["strong_scaling"] = strong
         if fix_rate is not None:
             line["fault_fix_rate"] = fix_rate
+        if smaller is not None:
+            line["smaller_configs"] = smaller
         if e2e is not None:
             line["e2e"] = e2e
         if attention is not None:
