@@ -26,6 +26,10 @@ int main(int argc, char** argv) {
   int fault_batch = args.get_int("--fault-batch", 0), fault_head = args.get_int("--fault-head", 0);
   int fault_query = args.get_int("--fault-query", -1), fault_index = args.get_int("--fault-index", -1);
   float fault_value = args.get_float("--fault-value", 1.0f);
+  // a second score fault (beyond the reference's options): in the same 64x64 score tile as the first it makes the tile
+  // unlocatable, which is what the replay path is for
+  int fault2_query = args.get_int("--fault2-query", -1), fault2_index = args.get_int("--fault2-index", -1);
+  float fault2_value = args.get_float("--fault2-value", 0.0f);
   ft_attn_options opt;
   ft_attn_options_default(&opt);
   opt.score_abs_tol = args.get_float("--score-abs-tol", opt.score_abs_tol);
@@ -46,6 +50,7 @@ int main(int argc, char** argv) {
         "Usage: %s [--batch N --heads N --sequence N --head-dim 64|128 --warmup N --repeat N --causal]\n"
         "       [--protect-softmax --softmax-abs-tol X --softmax-rel-tol X --exact-prepare]\n"
         "       [--fault-stage none|score|softmax|softmax-state|output --fault-batch N --fault-head N --fault-query N --fault-index N --fault-value X]\n"
+        "       [--fault2-query N --fault2-index N --fault2-value X]   (a second score fault in the same batch and head)\n"
         "       [--score-abs-tol X --score-rel-tol X --pv-abs-tol X --pv-rel-tol X]\n"
         "       [--verify-abs-tol X --verify-rel-tol X --verify-rows N --dist normal|grid]\n",
         argv[0]);
@@ -111,7 +116,12 @@ int main(int argc, char** argv) {
   float total_ms = 0.0f;
   CLI_CUDA(cudaEventElapsedTime(&total_ms, start, stop));
   float average_ms = total_ms / repeat;
-  ft_attn_fault fault{stage, fault_batch, fault_head, fault_query, fault_index, fault_value};
+  ft_attn_fault fault{stage, fault_batch, fault_head, fault_query, fault_index, fault_value, 0, 0, 0.0f};
+  if (stage == FT_ATTN_FAULT_SCORE && fault2_value != 0.0f) {
+    fault.query2 = fault2_query < 0 ? fault_query : fault2_query;
+    fault.index2 = fault2_index < 0 ? fault_index : fault2_index;
+    fault.value2 = fault2_value;
+  }
   CLI_FT(ft_attention_fp16_abft_run(handle, d_out, stage == FT_ATTN_FAULT_NONE ? nullptr : &fault, stream));
   CLI_FT(ft_attention_fp16_abft_report(handle, &report));
 
@@ -161,7 +171,9 @@ int main(int argc, char** argv) {
   }
   bool fault_pass;
   if (stage == FT_ATTN_FAULT_SCORE) {
-    fault_pass = report.score_detected > 0 && report.score_corrected > 0 && report.failed_rows == 0;
+    // a0:735-750 asks for a corrected score; a tile with two faults is replayed instead (a14:935-959)
+    fault_pass = report.score_detected > 0 && (report.score_corrected > 0 || report.score_replayed > 0) && report.score_uncorrected == 0 &&
+                 report.failed_rows == 0;
   } else if (stage == FT_ATTN_FAULT_SOFTMAX) {  // pass rules of src/ft_flash_attention_a0.cu:735-750
     fault_pass = report.softmax_detected > 0 && (report.softmax_corrected > 0 || report.softmax_replayed > 0) && report.failed_rows == 0;
   } else if (stage == FT_ATTN_FAULT_SOFTMAX_STATE) {

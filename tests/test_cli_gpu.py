@@ -62,6 +62,8 @@ def test_stage_program_added_flags():
     if torch.cuda.device_count() >= 2:
         rc, rep, _ = run("stage_abft_fp8_gemm", "--m", 1024, "--n", 512, "--k", 256, "--repeat", 2, "--gpus", 2, "--inject-fault")
         assert rc == 0 and (rep["gpus"], rep["rows_per_gpu"], rep["bad_tiles"], rep["corrected_tiles"]) == ("2", "512", "1", "1")
+        # the record came through the all-gather with the tile id of the whole product: tile 64 = tile row 8, the first of GPU 1
+        assert rep["report_gather"].startswith("ncclAllGather") and rep["fault_record_0"].startswith("tile=64 gpu=1 bad_rows=1 bad_cols=1 row=32 col=32")
 
 
 def test_stage_program_rejects_bad_shapes():
@@ -104,6 +106,10 @@ def test_attention_program():
                      "score", "--fault-value", 4.0)
     assert rc == 0 and rep["shape"].endswith("causal=1") and (rep["score_detected"], rep["score_corrected"]) == ("1", "1")
     assert rep["fault_target"].startswith("batch=0 head=0 query=256 index=128")  # causal default of a14:261
+    # two faults in one score tile: not locatable, the tile is replayed on the CUDA cores and the output verifies
+    rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--repeat", 1, "--fault-stage", "score",
+                     "--fault-value", 4.0, "--fault2-query", 260, "--fault2-index", 300, "--fault2-value", -3.0)
+    assert rc == 0 and (rep["score_detected"], rep["score_corrected"], rep["score_replayed"], rep["score_uncorrected"]) == ("1", "0", "1", "0")
     rc, _, err = run("ft_flash_attention", "--sequence", 256, "--causal", "--fault-stage", "score", "--fault-query", 10, "--fault-index", 20)
     assert rc == 1 and "must not exceed" in err
     rc, rep, _ = run("ft_flash_attention", "--batch", 1, "--heads", 2, "--sequence", 512, "--head-dim", 64, "--repeat", 1, "--fault-stage",
