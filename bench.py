@@ -444,7 +444,8 @@ def main():
         c_pin = torch.empty((n, m_rank), dtype=torch.float32).pin_memory()
         # plain pinned copies alone, one at a time: the floor the call cannot beat on this host at this rank count
         d_tmp = torch.empty_like(c)
-        h2d_s = d2h_s = float("inf")
+        h2d_s = d2h_s = both_s = float("inf")
+        side = torch.cuda.Stream(device=device)
         for _ in range(3):  # the first pass also pays for mapping the pinned pages; the best of three is the floor
             barrier()
             t0 = time.perf_counter()
@@ -456,6 +457,15 @@ def main():
             c_pin.copy_(d_tmp, non_blocking=True)
             barrier()
             d2h_s = min(d2h_s, max_over_ranks(time.perf_counter() - t0))
+            # both directions at once, as in the call: inputs in on one stream while the output goes out on another
+            t0 = time.perf_counter()
+            a.copy_(a_pin, non_blocking=True)
+            b.copy_(b_pin, non_blocking=True)
+            with torch.cuda.stream(side):
+                c_pin.copy_(d_tmp, non_blocking=True)
+            side.synchronize()
+            barrier()
+            both_s = min(both_s, max_over_ranks(time.perf_counter() - t0))
         del d_tmp
         host = ftg.HostAbftGemm(m_rank, n, k)
         host(a_pin, b_pin, c_pin)  # creates device buffers and the cache
@@ -475,9 +485,9 @@ def main():
                "steps": steps_e2e, "ms_per_step": dt / steps_e2e * 1e3,
                "note": "cache reused (inputs unchanged between steps, as in the steady-state metric)",
                "copy_floor": {"h2d_gbs_per_rank": h2d_bytes / h2d_s / 1e9, "d2h_gbs_per_rank": d2h_bytes / d2h_s / 1e9,
-                              "ms": max(h2d_s, d2h_s) * 1e3,
-                              "note": "slowest rank's plain pinned cudaMemcpyAsync of the same bytes, all ranks at once; the two "
-                                      "directions overlap in the call, so the longer one is its floor"}}
+                              "ms": both_s * 1e3, "one_direction_ms": max(h2d_s, d2h_s) * 1e3,
+                              "note": "slowest rank's plain pinned cudaMemcpyAsync of the same bytes, all ranks at once: each "
+                                      "direction alone (GB/s) and both at once on two streams (ms), which is the floor of the call"}}
         t0 = time.perf_counter()
         host(a_pin, b_pin, c_pin, prepare=True)
         torch.cuda.synchronize()
