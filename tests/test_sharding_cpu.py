@@ -97,9 +97,10 @@ def _attn_worker(rank, world, port, out):
     first, count = shard_heads(6, rank, world)  # 6 (batch, head) pairs over 2 ranks
     seq = 256  # 4 bands: 16 score tiles per head
     recs = [TileRecord(tile=5 + rank, bad_row_count=1, bad_col_count=1, bad_row=2, bad_col=3, row_delta=-1.0, col_delta=-1.0, corrected=1)]
-    mine = AttnReport(0, 1, 1, 0, rank, rank, 0, 0, 0, 0, 0.01 * (rank + 1), 0.5, recs)
+    mine = AttnReport(0, 1, 1, 0, rank, rank, 0, 0, 0, 0, 0.01 * (rank + 1), 0.5, recs, score_replayed=2 * rank + 1)
     total = gather_attention_reports(mine, first, 3, seq)
-    out.put((rank, total.score_detected, total.score_corrected, total.pv_detected, total.max_score_noise, [r.tile for r in total.records]))
+    out.put((rank, total.score_detected, total.score_corrected, total.pv_detected, total.max_score_noise, [r.tile for r in total.records],
+             total.score_replayed))
     dist.destroy_process_group()
 
 
@@ -116,6 +117,6 @@ def test_attention_counters_all_gather_gloo_world2():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, detected, corrected, pv, noise, tiles in results:
-        assert (detected, corrected, pv) == (2, 2, 1) and noise == pytest.approx(0.02)
+    for rank, detected, corrected, pv, noise, tiles, replayed in results:
+        assert (detected, corrected, pv, replayed) == (2, 2, 1, 4) and noise == pytest.approx(0.02)
         assert tiles == [5, 3 * 16 + 6]  # rank 1 owns heads 3..5: its local tile 6 is tile 6 of head 3
