@@ -355,7 +355,7 @@ abft_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
       const long long t0 = profiling ? clock64() : 0;
-      // one thread polls the barrier; the other 127 sleep in the hardware barrier below until it has seen the phase
+      // one thread polls the barrier; the other 255 sleep in the hardware barrier below until it has seen the phase
       bool ok = true;
       if (warp == 2 && lane == 0) ok = mbar_wait_bounded(&tail.tmem_full[acc], acc_phase, abort_flag, p.wait_timeout_ns);
       if (any_over_epilogue(!ok)) break;

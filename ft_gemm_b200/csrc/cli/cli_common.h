@@ -219,7 +219,7 @@ inline void print_common_header(const CommonOptions& o, const char* version_key,
   bool pair = o.m % 256 == 0;
   std::printf("instruction_tile: %s, cta_tile: 128x256x128, tma_stage_k: 128, stages: %d\n", pair ? "256x256x32 (2 CTAs)" : "128x256x32",
               pair ? 7 : 4);
-  std::printf("threads_per_cta: 192, producer_warps: 1, mma_warps: 1, epilogue_warps: 4, tmem_accumulators: 2\n");
+  std::printf("threads_per_cta: 320, producer_warps: 1, mma_warps: 1, epilogue_warps: 8, tmem_accumulators: 2\n");
   std::printf("pipeline: TMA producer || tcgen05.mma issuer || TMEM epilogue with fused ABFT verifier (persistent)\n");
   std::printf("layout: A=[M,K] row-major, B=[N,K] column-major, C=[N,M] column-major\n");
   std::printf("shape: M=%d N=%d K=%d, abft_tiles=%d, cta_tiles=%d\n", o.m, o.n, o.k, tile_count, cta_tiles);
