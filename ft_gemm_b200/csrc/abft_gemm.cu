@@ -50,7 +50,6 @@ constexpr int kEpilogueSets = 2;  // sets of four epilogue warps; a set covers a
 constexpr int kEpilogueThreads = 128 * kEpilogueSets;
 constexpr int kThreads = 64 + kEpilogueThreads;
 constexpr int kGroupCols = 64;  // = FT_ABFT_TILE
-constexpr int kGroups = kBlockN / kGroupCols;
 constexpr int kMaxStages = 7;
 
 template <bool kPair>
