@@ -73,6 +73,7 @@ struct SplitShared {
   int abort_flag;
   TileScratch scratch[kQTiles][2][2];      // [query tile][key half][row pair]
   TileScratch replay_scratch[kQTiles][2][2];
+  float col_expect[kQTiles][2][2][2][64];  // [query tile][key half][row pair][expected | scale][column]: the band's cached column checksums
   float row_max[kQTiles][2][2][kTile];     // [query tile][parity][key half][row]: the half's row maximum of this key tile
   float2 final_actual[kQTiles][2][kTile];  // [query tile][dim half][row]: {sum_d o, sum_d w_d o} over the half's dims
 };
@@ -335,13 +336,16 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         if (causal && j == first_qtile + t) key_limit = row_in_tile;
         if ((j + 1) * kTile > p.valid_seq) key_limit = min(key_limit, p.valid_seq - 1 - j * kTile);
         const bool diagonal = key_limit < kTile - 1;  // some keys of this tile are masked for this row
-        // cached expected checksums of this thread's 64x64 tile: the row's pair is fetched before the wait, the column
-        // values are only asked for (they are read after the partner exchange; until then they would hold registers)
+        // Cached expected checksums of this thread's 64x64 tile, asked for before the wait.  The row's pair goes to
+        // registers.  The column side (64 expectations + 64 scales per band) travels by asynchronous copy straight into
+        // shared memory -- the band's first warp brings the expectations, its second the scales, two adjacent columns per
+        // lane -- so that it costs no register while the scores are worked on and its latency is over when the partner
+        // exchange needs it.
         const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
+        cp_async_8(&sh.col_expect[t][c][pair][half][2 * lane], (half == 0 ? p.expected_cols : p.col_scales) + cache + 2 * lane);
+        cp_async_commit();
         const float exp_row = __ldg(p.expected_rows + cache + r_local);
         const float scale_row = __ldg(p.row_scales + cache + r_local);
-        prefetch_l1(p.expected_cols + cache + 2 * lane);
-        prefetch_l1(p.col_scales + cache + 2 * lane);
         if (!warp_wait(&sh.s_full[t], j & 1, abort_flag)) {
           alive = false;
           owed_pair_from = owed_tile_from = j;
@@ -370,10 +374,11 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         mbar_arrive(&sh.s_free);  // the buffer can take the next score product (the other query tile's)
         abft_tile_rows(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
         float local_max = masked_row_max(v, diagonal, c * 64, key_limit);
+        cp_async_wait_all();  // this lane's piece of the cached column checksums has landed; the barrier publishes all of them
         asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
         {
-          const float exp_col0 = __ldg(p.expected_cols + cache + lane), exp_col1 = __ldg(p.expected_cols + cache + 32 + lane);
-          const float scale_col0 = __ldg(p.col_scales + cache + lane), scale_col1 = __ldg(p.col_scales + cache + 32 + lane);
+          const float exp_col0 = sh.col_expect[t][c][pair][0][lane], exp_col1 = sh.col_expect[t][c][pair][0][32 + lane];
+          const float scale_col0 = sh.col_expect[t][c][pair][1][lane], scale_col1 = sh.col_expect[t][c][pair][1][32 + lane];
           const TileDecision d = abft_tile_decide(lane, scratch, exp_col0, exp_col1, scale_col0, scale_col1, p.score_abs_tol,
                                                   p.score_rel_tol, max_ratio);
           if ((d.bad_rows | d.bad_cols) != 0) {  // uniform over the two warps of the band; rare

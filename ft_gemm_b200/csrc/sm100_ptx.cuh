@@ -63,6 +63,14 @@ __device__ __forceinline__ void prefetch_l1(const void* ptr) {
   asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
 }
 
+// Asynchronous 8-byte copy global -> shared without a register in between (completion: cp_async_wait_all by the issuing
+// thread, then a barrier before other threads read).
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // One lane of a converged warp, chosen by the hardware.  Unlike a test of the lane index, the compiler knows that the
 // code under it runs in a single thread and keeps the descriptors of tcgen05.mma and of the tensor copies in uniform registers.
 __device__ __forceinline__ bool elect_one() {
