@@ -74,6 +74,7 @@ struct SplitShared {
   TileScratch scratch[kQTiles][2][2];      // [query tile][key half][row pair]
   TileScratch replay_scratch[kQTiles][2][2];
   float col_expect[kQTiles][2][2][2][64];  // [query tile][key half][row pair][expected | scale][column]: the band's cached column checksums
+  float row_expect[kQTiles][2][2][2][64];  // the same for its rows
   float row_max[kQTiles][2][2][kTile];     // [query tile][parity][key half][row]: the half's row maximum of this key tile
   float2 final_actual[kQTiles][2][kTile];  // [query tile][dim half][row]: {sum_d o, sum_d w_d o} over the half's dims
 };
@@ -343,9 +344,9 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         // exchange needs it.
         const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
         cp_async_8(&sh.col_expect[t][c][pair][half][2 * lane], (half == 0 ? p.expected_cols : p.col_scales) + cache + 2 * lane);
+        cp_async_4(&sh.row_expect[t][c][pair][0][r_local], p.expected_rows + cache + r_local);  // read back by this thread only
+        cp_async_4(&sh.row_expect[t][c][pair][1][r_local], p.row_scales + cache + r_local);
         cp_async_commit();
-        const float exp_row = __ldg(p.expected_rows + cache + r_local);
-        const float scale_row = __ldg(p.row_scales + cache + r_local);
         if (!warp_wait(&sh.s_full[t], j & 1, abort_flag)) {
           alive = false;
           owed_pair_from = owed_tile_from = j;
@@ -372,9 +373,10 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         tmem_wait_ld();
         tcgen05_fence_before();
         mbar_arrive(&sh.s_free);  // the buffer can take the next score product (the other query tile's)
-        abft_tile_rows(v, lane, half, scratch, exp_row, scale_row, p.score_abs_tol, p.score_rel_tol, max_ratio);
+        cp_async_wait_all();  // this lane's pieces of the cached checksums have landed; the band barrier below publishes the column side
+        abft_tile_rows(v, lane, half, scratch, sh.row_expect[t][c][pair][0][r_local], sh.row_expect[t][c][pair][1][r_local],
+                       p.score_abs_tol, p.score_rel_tol, max_ratio);
         float local_max = masked_row_max(v, diagonal, c * 64, key_limit);
-        cp_async_wait_all();  // this lane's piece of the cached column checksums has landed; the barrier publishes all of them
         asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
         {
           const float exp_col0 = sh.col_expect[t][c][pair][0][lane], exp_col1 = sh.col_expect[t][c][pair][0][32 + lane];
