@@ -509,6 +509,14 @@ def main():
         times = sorted(timed_region(lambda: attn.run(out), attn_steps) for _ in range(3))
         attn_ms = times[1] / attn_steps
         clean = ftg.gather_attention_reports(attn.report(), first, batch_heads, seq, device=device)
+        # a forward pass whose Q, K, V are new every call: metadata rebuilt in the handle's buffers, then the kernel
+
+        def refreshed_forward():
+            attn.refresh(q, kk_, v)
+            attn.run(out)
+        refreshed_forward()
+        fresh_times = sorted(timed_region(refreshed_forward, attn_steps) for _ in range(3))
+        fresh_ms = fresh_times[1] / attn_steps
         attn.run(out, (ftg.FAULT_SCORE, 0, count // 2, seq // 2 + 1, seq - 96, 12.0))  # one fault per rank
         faulty = ftg.gather_attention_reports(attn.report(), first, batch_heads, seq, device=device)
         sdpa = None
@@ -531,7 +539,9 @@ def main():
         attn_tflops = 4.0 * batch_heads * seq * seq * dim / (attn_ms * 1e-3) / 1e12
         attention = {"workload": f"ft_attention_fwd B*H={batch_heads} N={seq} D={dim} FP16, non-causal, heads sharded over {world} GPU(s)",
                      "ms": attn_ms, "tflops": attn_tflops, "frac_of_fp16_peak": attn_tflops / world / fp16_peak,
-                     "prepare_ms": clean.prepare_ms, "clean": [clean.score_detected, clean.pv_detected, clean.failed_rows],
+                     "prepare_ms": clean.prepare_ms, "refresh_and_forward_ms": fresh_ms,
+                     "refresh_and_forward_tflops": 4.0 * batch_heads * seq * seq * dim / (fresh_ms * 1e-3) / 1e12,
+                     "clean": [clean.score_detected, clean.pv_detected, clean.failed_rows],
                      "score_fault": [faulty.score_detected, faulty.score_corrected, faulty.pv_detected],
                      "score_checksum_noise_ratio": clean.max_score_noise, "torch_sdpa_fp16_no_checks": sdpa}
         attn.close()

@@ -69,11 +69,12 @@ def _lib():
         lib.ft_attn_options_default.restype = None
         lib.ft_attention_fp16_abft_prepare.argtypes = [ctypes.POINTER(vp), vp, vp, vp, ci, ci, ci, ci,
                                                        ctypes.POINTER(FtAttnOptions), vp]
+        lib.ft_attention_fp16_abft_refresh.argtypes = [vp, vp, vp, vp, vp]
         lib.ft_attention_fp16_abft_run.argtypes = [vp, vp, ctypes.POINTER(FtAttnFault), vp]
         lib.ft_attention_fp16_abft_report.argtypes = [vp, ctypes.POINTER(FtAttnReport)]
         lib.ft_attention_fp16_abft_destroy.argtypes = [vp]
-        for name in ("ft_attention_fp16_abft_prepare", "ft_attention_fp16_abft_run", "ft_attention_fp16_abft_report",
-                     "ft_attention_fp16_abft_destroy"):
+        for name in ("ft_attention_fp16_abft_prepare", "ft_attention_fp16_abft_refresh", "ft_attention_fp16_abft_run",
+                     "ft_attention_fp16_abft_report", "ft_attention_fp16_abft_destroy"):
             getattr(lib, name).restype = ci
         _bound = True
     return lib
@@ -153,6 +154,18 @@ class FtAttention:
                 ctypes.byref(self.handle), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
                 ctypes.c_void_p(v.data_ptr()), self.batch, self.heads, self.seq, self.dim, ctypes.byref(options),
                 _stream_ptr(stream)))
+
+    def refresh(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, stream: Optional[torch.cuda.Stream] = None):
+        """New Q, K, V of the prepared shape: rebuilds the metadata in the handle's buffers, nothing is allocated."""
+        for t, name in ((q, "Q"), (k, "K"), (v, "V")):
+            if (not t.is_cuda or t.dtype != torch.float16 or not t.is_contiguous() or t.shape != self.q.shape
+                    or t.device != self.q.device):
+                raise ValueError(f"{name} must be a contiguous float16 CUDA tensor shaped like the prepared Q, on its device")
+        with torch.cuda.device(q.device):
+            _abi.check(self.lib.ft_attention_fp16_abft_refresh(self.handle, ctypes.c_void_p(q.data_ptr()),
+                                                               ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
+                                                               _stream_ptr(stream)))
+        self.q, self.k, self.v = q, k, v
 
     def new_output(self) -> torch.Tensor:
         return torch.empty(self.q.shape, dtype=torch.float32, device=self.q.device)

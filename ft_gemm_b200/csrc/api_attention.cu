@@ -80,6 +80,45 @@ struct ft_attn_handle {
   cudaStream_t last_stream = nullptr;
 };
 
+// The metadata of the current Q, K, V: V^T with its checksum rows, band sums of Q and K, the score-checksum cache
+// (src/ft_flash_attention_a14.cu:571-621, 1294-1322 in this build's form).  Everything it writes was allocated by _prepare.
+static int fill_attention_metadata(ft_attn_handle* h, cudaStream_t stream) {
+  const void *q = h->q, *k = h->k, *v = h->v;
+  const int seq = h->seq, head_dim = h->dim;
+  const size_t bh = static_cast<size_t>(h->batch) * h->heads;
+  const int nbands = seq / 64;
+  const ft_attn_options& opts = h->options;
+  cudaError_t err = cudaMemsetAsync(h->report, 0, sizeof(AttnDeviceReport), stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
+  if (err == cudaSuccess) err = cudaEventRecord(h->ev0, stream);
+  if (err == cudaSuccess) err = launch_attn_prepare_v(v, h->vt, h->v_sum, h->v_weighted, static_cast<int>(bh), seq, head_dim, stream);
+  if (err == cudaSuccess) err = launch_band_sums_f16(q, h->q_sums, h->q_mags, bh * seq, head_dim, stream);
+  if (err == cudaSuccess) err = launch_band_sums_f16(k, h->k_sums, h->k_mags, bh * seq, head_dim, stream);
+  // per head: S = Q K^T is the GEMM A = Q [N, D], B = K [N, D]
+  if (opts.exact_prepare != 0) {
+    if (err == cudaSuccess) {
+      err = launch_expected_f16(q, h->k_sums, h->k_mags, h->expected_rows, h->row_scales, seq, seq / 64, head_dim, 0, static_cast<int>(bh), stream);
+    }
+    if (err == cudaSuccess) {
+      err = launch_expected_f16(k, h->q_sums, h->q_mags, h->expected_cols, h->col_scales, seq, seq / 64, head_dim, 1, static_cast<int>(bh), stream);
+    }
+  } else {
+    if (err == cudaSuccess) err = launch_split_band_pieces_f16(h->k_sums, h->k_mags, h->k_ws, h->k_wm, nbands, head_dim, static_cast<int>(bh), stream);
+    if (err == cudaSuccess) err = launch_split_band_pieces_f16(h->q_sums, h->q_mags, h->q_ws, h->q_wm, nbands, head_dim, static_cast<int>(bh), stream);
+    if (err == cudaSuccess) {
+      err = launch_expected_mma_f16(h->tmap_q, h->tmap_k_ws, h->tmap_k_wm, h->expected_rows, h->row_scales, seq, nbands, head_dim, 0,
+                                    static_cast<int>(bh), h->sm_count, h->prepare_status, stream);
+    }
+    if (err == cudaSuccess) {
+      err = launch_expected_mma_f16(h->tmap_k, h->tmap_q_ws, h->tmap_q_wm, h->expected_cols, h->col_scales, seq, nbands, head_dim, 1,
+                                    static_cast<int>(bh), h->sm_count, h->prepare_status, stream);
+    }
+  }
+  if (err == cudaSuccess) err = cudaEventRecord(h->ev1, stream);
+  if (err != cudaSuccess) return noalloc_fail(FT_ERR_CUDA, "attention prepare failed: %s", cudaGetErrorString(err));
+  return FT_OK;
+}
+
 extern "C" {
 
 void ft_attn_options_default(ft_attn_options* o) {
@@ -228,38 +267,7 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
     if (rc == FT_OK) rc = make_f16_map(&h->tmap_k_ws, h->k_ws, ws_rows, head_dim, 96u);
     if (rc == FT_OK) rc = make_f16_map(&h->tmap_k_wm, h->k_wm, wm_rows, head_dim, 64u);
   }
-  if (rc == FT_OK) {
-    err = cudaMemsetAsync(h->report, 0, sizeof(AttnDeviceReport), stream);
-    if (err == cudaSuccess) err = cudaMemsetAsync(h->prepare_status, 0, sizeof(int), stream);
-    if (err == cudaSuccess) err = cudaEventRecord(h->ev0, stream);
-    if (err == cudaSuccess) err = launch_attn_prepare_v(v, h->vt, h->v_sum, h->v_weighted, static_cast<int>(bh), seq, head_dim, stream);
-    if (err == cudaSuccess) err = launch_band_sums_f16(q, h->q_sums, h->q_mags, bh * seq, head_dim, stream);
-    if (err == cudaSuccess) err = launch_band_sums_f16(k, h->k_sums, h->k_mags, bh * seq, head_dim, stream);
-    // per head: S = Q K^T is the GEMM A = Q [N, D], B = K [N, D]
-    if (opts.exact_prepare != 0) {
-      if (err == cudaSuccess) {
-        err = launch_expected_f16(q, h->k_sums, h->k_mags, h->expected_rows, h->row_scales, seq, seq / 64, head_dim, 0,
-                                  static_cast<int>(bh), stream);
-      }
-      if (err == cudaSuccess) {
-        err = launch_expected_f16(k, h->q_sums, h->q_mags, h->expected_cols, h->col_scales, seq, seq / 64, head_dim, 1,
-                                  static_cast<int>(bh), stream);
-      }
-    } else {
-      if (err == cudaSuccess) err = launch_split_band_pieces_f16(h->k_sums, h->k_mags, h->k_ws, h->k_wm, nbands, head_dim, static_cast<int>(bh), stream);
-      if (err == cudaSuccess) err = launch_split_band_pieces_f16(h->q_sums, h->q_mags, h->q_ws, h->q_wm, nbands, head_dim, static_cast<int>(bh), stream);
-      if (err == cudaSuccess) {
-        err = launch_expected_mma_f16(h->tmap_q, h->tmap_k_ws, h->tmap_k_wm, h->expected_rows, h->row_scales, seq, nbands, head_dim, 0,
-                                      static_cast<int>(bh), h->sm_count, h->prepare_status, stream);
-      }
-      if (err == cudaSuccess) {
-        err = launch_expected_mma_f16(h->tmap_k, h->tmap_q_ws, h->tmap_q_wm, h->expected_cols, h->col_scales, seq, nbands, head_dim, 1,
-                                      static_cast<int>(bh), h->sm_count, h->prepare_status, stream);
-      }
-    }
-    if (err == cudaSuccess) err = cudaEventRecord(h->ev1, stream);
-    if (err != cudaSuccess) rc = noalloc_fail(FT_ERR_CUDA, "attention prepare failed: %s", cudaGetErrorString(err));
-  }
+  if (rc == FT_OK) rc = fill_attention_metadata(h, stream);
   h->last_stream = stream;
   if (rc != FT_OK) {
     ft_attention_fp16_abft_destroy(h);
@@ -267,6 +275,37 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   }
   *handle = h;
   return FT_OK;
+}
+
+int ft_attention_fp16_abft_refresh(ft_attn_handle* h, const void* q, const void* k, const void* v, void* stream_ptr) {
+  if (h == nullptr || q == nullptr || k == nullptr || v == nullptr) return noalloc_fail(FT_ERR_INVALID, "null handle or operand pointer");
+  if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0) {
+    return noalloc_fail(FT_ERR_INVALID, "Q, K and V must be 16-byte aligned");
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const size_t bh = static_cast<size_t>(h->batch) * h->heads;
+  if (h->valid_seq != h->seq) {
+    // the padding rows of the handle's copies are zero since _prepare; only the real rows are replaced
+    const size_t src_pitch = static_cast<size_t>(h->valid_seq) * h->dim * 2, dst_pitch = static_cast<size_t>(h->seq) * h->dim * 2;
+    const void* sources[3] = {q, k, v};
+    for (int i = 0; i < 3; ++i) {
+      ATTN_CUDA(cudaMemcpy2DAsync(h->padded[i], dst_pitch, sources[i], src_pitch, src_pitch, bh, cudaMemcpyDeviceToDevice, stream));
+    }
+  } else {
+    if (q != h->q) {
+      const int rc = make_f16_map(&h->tmap_q, q, bh * h->seq, h->dim);
+      if (rc != FT_OK) return rc;
+    }
+    if (k != h->k) {
+      const int rc = make_f16_map(&h->tmap_k, k, bh * h->seq, h->dim);
+      if (rc != FT_OK) return rc;
+    }
+    h->q = q;
+    h->k = k;
+    h->v = v;
+  }
+  h->last_stream = stream;
+  return fill_attention_metadata(h, stream);
 }
 
 int ft_attention_generate_f16(void* out, size_t count, uint32_t seed, int dist, float sigma, void* stream_ptr) {

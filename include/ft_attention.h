@@ -112,6 +112,13 @@ void ft_attn_options_default(ft_attn_options* options);
 int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const void* k, const void* v, int batch, int heads,
                                    int sequence, int head_dim, const ft_attn_options* options, void* stream);
 
+/* Rebuilds the metadata (V^T with its checksum rows, band sums, the score-checksum cache) for new contents of Q, K, V of the
+ * shape given to _prepare, without allocating: what a forward pass calls when its operands changed, which in attention is
+ * every call.  The pointers may differ from those given to _prepare (16-byte aligned).  Replaces re-running the metadata
+ * kernels of the reference's main() (src/ft_flash_attention_a14.cu:1294-1322, 1369-1430) on the buffers it already holds.
+ * Asynchronous on `stream`; a later _run on the same stream sees the new metadata. */
+int ft_attention_fp16_abft_refresh(ft_attn_handle* handle, const void* q, const void* k, const void* v, void* stream);
+
 /* Replaces one launch of the fused forward kernel with its fault parameters
  * (src/ft_flash_attention_a14.cu:1324-1359).  Asynchronous; `fault` may be NULL. */
 int ft_attention_fp16_abft_run(ft_attn_handle* handle, float* out, const ft_attn_fault* fault, void* stream);

@@ -135,6 +135,39 @@ def test_stale_cache_tiles_stay_uncorrected_after_replay(ftg):
     op.close()
 
 
+@pytest.mark.parametrize("n,d", [(256, 128), (333, 128), (512, 64)])
+def test_refresh_rebuilds_the_metadata_without_a_new_handle(ftg, n, d):
+    """A handle refreshed with new Q, K, V (new pointers, or the old buffers changed in place) gives bit for bit what a fresh
+    handle gives; the sequence length that is not a whole tile goes through the handle's padded copies."""
+    b, h = 1, 2
+    q1, k1, v1 = _qkv(b, h, n, d, seed=21)
+    q2, k2, v2 = _qkv(b, h, n, d, seed=22)
+    fresh = ftg.FtAttention(q2, k2, v2)
+    want = fresh.new_output()
+    fresh.run(want)
+    assert fresh.report().score_detected == 0
+    fresh.close()
+
+    op = ftg.FtAttention(q1, k1, v1)
+    out = op.new_output()
+    op.run(out)
+    assert op.report().score_detected == 0
+    op.refresh(q2, k2, v2)  # other buffers
+    op.run(out)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    assert torch.equal(out, want)
+    q2.copy_(q1), k2.copy_(k1), v2.copy_(v1)  # the same buffers, new contents: stale until refreshed
+    op.refresh(q2, k2, v2)
+    op.run(out)
+    rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
+    np.testing.assert_allclose(_np(out), oa.truth_fp64(_np(q1), _np(k1), _np(v1)), atol=4e-3, rtol=0)
+    with pytest.raises(ValueError):
+        op.refresh(q2[:, :1], k2[:, :1], v2[:, :1])
+    op.close()
+
+
 def test_output_faults_match_oracle(ftg):
     b, h, n = 2, 2, 256
     q, k, v = _qkv(b, h, n, seed=11)
