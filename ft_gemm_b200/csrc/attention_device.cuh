@@ -31,7 +31,7 @@ __device__ __forceinline__ void replay_score_row(const __half* __restrict__ q_ro
 // The replay of a score tile whose fault could not be located, kept out of line: it runs once in a blue moon, and
 // inlined its register needs would be charged to the softmax loop around it.  Each of the 64 threads of the band
 // recomputes its row into `rv` (64 floats in local memory), the rows and columns are checked against the cached
-// checksums once more, and the verdict comes back: true when the recomputed tile passes.  The two warps of the band meet
+// checksums once more, and the outcome comes back: true when the recomputed tile passes.  The two warps of the band meet
 // on `bar` (an mbarrier with 64 arrivals per phase; `parity` is the phase of this use) with a bounded wait: *wait_ok is
 // cleared when the partner never came.
 template <int kDim>

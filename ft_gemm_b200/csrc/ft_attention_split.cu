@@ -94,7 +94,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Every lane polls the barrier itself (no CTA-level barrier around the wait); the verdict is made uniform over the warp.
+// Every lane polls the barrier itself (no CTA-level barrier around the wait); the outcome is made uniform over the warp.
 // A warp whose wait was abandoned stops working but keeps executing the named barriers of the remaining key tiles
 // (see the drain loop in the kernel), so that the warps it shares those barriers with are never left waiting.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
