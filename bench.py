@@ -545,6 +545,17 @@ def main():
                      "score_fault": [faulty.score_detected, faulty.score_corrected, faulty.pv_detected],
                      "score_checksum_noise_ratio": clean.max_score_noise, "torch_sdpa_fp16_no_checks": sdpa}
         attn.close()
+        # the same forward with the reference's softmax-stage protection on (verifier copies of every probability)
+        guarded = ftg.FtAttention(q, kk_, v, protect_softmax=True)
+        for _ in range(3):
+            guarded.run(out)
+        guarded_times = sorted(timed_region(lambda: guarded.run(out), attn_steps) for _ in range(3))
+        guarded_ms = guarded_times[1] / attn_steps
+        guarded_report = ftg.gather_attention_reports(guarded.report(), first, batch_heads, seq, device=device)
+        attention["with_softmax_protection"] = {"ms": guarded_ms, "tflops": 4.0 * batch_heads * seq * seq * dim / (guarded_ms * 1e-3) / 1e12,
+                                                "clean": [guarded_report.score_detected, guarded_report.softmax_detected,
+                                                          guarded_report.pv_detected, guarded_report.failed_rows]}
+        guarded.close()
         del q, kk_, v, out
 
     # ---- same-box cuBLASLt FP8 without ABFT: the overhead reference (not part of the product path).  Two ways: through

@@ -164,9 +164,6 @@ int ft_attention_fp16_abft_prepare(ft_attn_handle** handle, const void* q, const
   // other lengths the handle keeps zero-padded copies of Q, K and V; padded keys are masked, padded queries not stored.
   const int valid_seq = seq;
   seq = (seq + 127) / 128 * 128;
-  if (head_dim == 64 && options != nullptr && options->protect_softmax != 0) {
-    return noalloc_fail(FT_ERR_UNSUPPORTED, "the softmax-stage protection is built for head_dim 128 only");
-  }
   if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0) {
     return noalloc_fail(FT_ERR_INVALID, "Q, K and V must be 16-byte aligned");
   }
@@ -375,13 +372,13 @@ int ft_attention_fp16_abft_run(ft_attn_handle* h, float* out, const ft_attn_faul
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   ATTN_CUDA(cudaMemsetAsync(h->report, 0, 64, stream));  // the counters; the records are guarded by record_count
-  // The split-row kernel (two threads per query row) is the default; the whole-row kernel carries the softmax-stage
-  // protection and can be selected for comparison with FT_ATTENTION_KERNEL=row in the environment.
+  // The split-row kernel (two threads per query row) is the default, with or without the softmax-stage protection; the
+  // whole-row kernel (head dimension 128) can be selected for comparison with FT_ATTENTION_KERNEL=row in the environment.
   static const bool force_row = [] {
     const char* choice = std::getenv("FT_ATTENTION_KERNEL");
     return choice != nullptr && std::strcmp(choice, "row") == 0;
   }();
-  if (params.protect_softmax != 0 || (force_row && h->dim == 128)) {
+  if (force_row && h->dim == 128) {
     ATTN_CUDA(launch_attention(h->tmap_q, h->tmap_k, h->tmap_vt, params, h->batch * h->heads, stream));
   } else {
     ATTN_CUDA(launch_attention_split(h->tmap_q, h->tmap_k, h->tmap_vt_ext, params, h->batch * h->heads, stream));

@@ -1,6 +1,6 @@
-// Fault-tolerant flash-attention forward, split-row form (the default kernel; the
-// form with one thread per whole row in ft_attention.cu serves the softmax-stage
-// protection).
+// Fault-tolerant flash-attention forward, split-row form (the default kernel, with
+// or without the softmax-stage protection; the form with one thread per whole row
+// in ft_attention.cu is kept for comparison).
 //
 // One CTA owns 256 queries of one (batch, head) as two 128-query tiles A and B that
 // share every 128-key K / V^T tile.  Every query row is worked on by TWO threads:
@@ -94,6 +94,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Hides a value from the optimiser so that a verifier copy is really recomputed.
+__device__ __forceinline__ float opaque(float x) {
+  asm volatile("" : "+f"(x));
+  return x;
+}
+
 // Every lane polls the barrier itself (no CTA-level barrier around the wait); the outcome is made uniform over the warp.
 // A warp whose wait was abandoned stops working but keeps executing the named barriers of the remaining key tiles
 // (see the drain loop in the kernel), so that the warps it shares those barriers with are never left waiting.
@@ -143,7 +149,69 @@ __device__ __forceinline__ float masked_row_max(const float (&v)[64], bool maske
 
 }  // namespace
 
-template <int kDim>
+// The rare half of the softmax-stage protection, kept out of line: a chunk of eight probabilities whose moments
+// disagree with the verifier's (src/ft_flash_attention_a14.cu:1014-1074).  Primary (with the test hook's fault) and
+// verifier values are recomputed from the scores; if the deltas of the three moments exceed the tolerance, one key is
+// located by their ratios and takes the verifier's value, otherwise the whole chunk does.  Leaves the chunk's FP16
+// probabilities in `packed` and what remains of sum(primary - verifier) in *remaining (zero after a replacement, the
+// tolerated difference otherwise); false when the deltas are within tolerance.
+__device__ __noinline__ bool repair_probability_chunk(const float* x, float scale_log2, float m_new, float m_check, int fault_at,
+                                                      float fault_value, int first_key, int seq, float abs_tol, float rel_tol,
+                                                      AttnDeviceReport* report, uint32_t* packed, float* remaining) {
+  float pr[8], qv[8];
+  float u0 = 0.0f, u1 = 0.0f, u2 = 0.0f, c0 = 0.0f, c1 = 0.0f, c2 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    pr[i] = fast_exp2(__fmaf_rn(x[i], scale_log2, -m_new));
+    qv[i] = fast_exp2(opaque(__fmaf_rn(x[i], scale_log2, -m_check)));
+    if (i == fault_at) pr[i] += fault_value;
+    const float w = static_cast<float>(2 * (first_key + i) - (seq - 1));
+    u0 += pr[i];
+    u1 = __fmaf_rn(w, pr[i], u1);
+    u2 = __fmaf_rn(w * w, pr[i], u2);
+    c0 += qv[i];
+    c1 = __fmaf_rn(w, qv[i], c1);
+    c2 = __fmaf_rn(w * w, qv[i], c2);
+  }
+  const float delta0 = u0 - c0, delta1 = u1 - c1, delta2 = u2 - c2;
+  const float thr0 = __fmaf_rn(rel_tol, fmaxf(1.0f, fabsf(c0)), abs_tol);
+  const float thr1 = __fmaf_rn(rel_tol, fmaxf(1.0f, fabsf(c1)), abs_tol);
+  const float thr2 = __fmaf_rn(rel_tol, fmaxf(1.0f, fabsf(c2)), abs_tol);
+  const bool bad = fabsf(delta0) > thr0 || fabsf(delta1) > thr1 || fabsf(delta2) > thr2;
+  if (bad) atomicAdd(&report->softmax_detected, 1);
+  int recovery_key = -1;
+  if (bad && fabsf(delta0) > thr0) {
+    const float observed_weight = delta1 / delta0;
+    const int key_index = __float2int_rn(0.5f * (observed_weight + static_cast<float>(seq - 1)));
+    const float second_residual = fabsf(delta2 / delta0 - observed_weight * observed_weight);
+    if (key_index >= first_key && key_index < first_key + 8 && fabsf(observed_weight - static_cast<float>(2 * key_index - (seq - 1))) <= 0.25f &&
+        second_residual <= fmaxf(1.0f, fabsf(observed_weight)) * 0.5f) {
+      recovery_key = key_index - first_key;
+    }
+  }
+  if (bad) atomicAdd(recovery_key >= 0 ? &report->softmax_corrected : &report->softmax_replayed, 1);
+  float left = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (bad && (recovery_key < 0 || recovery_key == i)) pr[i] = qv[i];
+    left += pr[i] - qv[i];
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __half2 h = __floats2half2_rn(pr[2 * e], pr[2 * e + 1]);
+    packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *remaining = left;
+  return bad;
+}
+
+// kProtect adds the reference's softmax-stage protection (src/ft_flash_attention_a14.cu:964-1099) for the thread's half
+// of the row: a verifier copy of the exponent reference and of every probability; the moments sum, sum w, sum w^2
+// (w = 2 key - (N - 1)) of the differences, checked per chunk of eight keys while the chunk's scores are still in
+// registers; replacement of one located probability or of the chunk from the verifier; a duplicate of the running
+// state (m, l).  At the end the protected denominator of the row's two threads
+// checks the one the PV product accumulated in its checksum column.
+template <int kDim, bool kProtect>
 __global__ void __launch_bounds__(kThreads, 1)
 ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_vt, const __grid_constant__ AttnParams p) {
@@ -324,6 +392,8 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       uint32_t replays = 0;  // times this band went through the replay path (the phase of its barrier)
 
       float m_run = -INFINITY, max_ratio = 0.0f;
+      // kProtect: running denominator of this half of the row and the verifier's duplicate of the state
+      float l_run = 0.0f, m_verify = -INFINITY, l_verify = 0.0f;
       bool alive = true;
       const int my_tiles = tiles_of(t);
       // when a wait is abandoned: the first key tile whose band barrier / tile barrier this warp still owes the others
@@ -450,6 +520,22 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           m_run = m_tile;
         }
         const float m_new = m_run;
+        float m_check = m_new, alpha_check = alpha;
+        if (kProtect) {
+          // the verifier follows its own copy of the maximum and of the reference point, by the same rule
+          const float verifier_max = opaque(row_max);
+          if (c == 0 && fabsf(row_max - verifier_max) > p.softmax_abs_tol) {
+            atomicAdd(&p.report->softmax_detected, 1);
+            atomicAdd(&p.report->softmax_replayed, 1);
+          }
+          const float m_tile_check = verifier_max * p.scale_log2;
+          m_check = m_verify;
+          alpha_check = 1.0f;
+          if (m_tile_check > m_verify + kRescaleStep) {
+            alpha_check = fast_exp2(opaque(m_verify - m_tile_check));
+            m_check = m_tile_check;
+          }
+        }
 
         if (j > 0) {
           // PV of the previous tile must have finished: the P buffer is free and O is quiescent
@@ -491,19 +577,83 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           }
           // two scores per instruction where the arithmetic allows it (packed FP32 pairs)
           const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg_m2 = pack_f32x2(-m_new, -m_new);
+          if (!kProtect) {
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            uint32_t packed[4];
+            for (int ch = 0; ch < 8; ++ch) {
+              uint32_t packed[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i0 = ch * 8 + 2 * e;
-              float a0, a1;
-              unpack_f32x2(fma_f32x2(pack_f32x2(v[i0], v[i0 + 1]), scale2, neg_m2), a0, a1);
-              const __half2 h = __floats2half2_rn(fast_exp2(a0), fast_exp2(a1));
-              packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+              for (int e = 0; e < 4; ++e) {
+                const int i0 = ch * 8 + 2 * e;
+                float a0, a1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(v[i0], v[i0 + 1]), scale2, neg_m2), a0, a1);
+                const __half2 h = __floats2half2_rn(fast_exp2(a0), fast_exp2(a1));
+                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+              *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-            *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          } else {
+            const unsigned long long neg_check2 = pack_f32x2(-m_check, -m_check);
+            const int fault_key = p.fault_stage == FT_ATTN_FAULT_SOFTMAX && p.fault_bh == bh && p.fault_query == q_tile0 + row_in_tile &&
+                                          p.fault_index / 64 == j * 2 + c
+                                      ? p.fault_index % 64
+                                      : -1;
+            const int first_key = j * kTile + c * 64;
+            unsigned long long cl2 = 0;  // a packed pair of zeros: sum of the verifier's probabilities
+            float l_extra = 0.0f;        // sum over the chunks that went to the out-of-line check of (primary - verifier)
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              uint32_t packed[4];
+              uint32_t differ = 0;  // primary and verifier run the same instructions on the same inputs: any differing bit is a finding
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i0 = ch * 8 + 2 * e;
+                const unsigned long long x2 = pack_f32x2(v[i0], v[i0 + 1]);
+                float a0, a1, b0, b1;
+                unpack_f32x2(fma_f32x2(x2, scale2, neg_m2), a0, a1);
+                unpack_f32x2(fma_f32x2(x2, scale2, neg_check2), b0, b1);
+                const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+                const float q0 = fast_exp2(opaque(b0)), q1 = fast_exp2(opaque(b1));  // the verifier's copies
+                differ |= (__float_as_uint(p0) ^ __float_as_uint(q0)) | (__float_as_uint(p1) ^ __float_as_uint(q1));
+                cl2 = add_f32x2(cl2, pack_f32x2(q0, q1));
+                const __half2 h = __floats2half2_rn(p0, p1);
+                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              // A chunk with a finding (or the test hook's fault) takes the out-of-line path: moments of both copies with
+              // the reference's weights and tolerance, location, replacement (repair_probability_chunk).
+              if (differ != 0 || (fault_key >> 3) == ch) {
+                float x8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x8[i] = v[ch * 8 + i];
+                float extra = 0.0f;
+                repair_probability_chunk(x8, p.scale_log2, m_new, m_check, (fault_key >> 3) == ch ? (fault_key & 7) : -1, p.fault_value,
+                                         first_key + ch * 8, seq, p.softmax_abs_tol, p.softmax_rel_tol, p.report, packed, &extra);
+                l_extra += extra;
+              }
+              *reinterpret_cast<uint4*>(p_row + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            // running denominator and the duplicate of the state (a14:1075-1098)
+            {
+              float lo, hi;
+              unpack_f32x2(cl2, lo, hi);
+              l_run = __fmaf_rn(alpha, l_run, lo + hi + l_extra);  // the primary sum: the verifier's plus what the findings left
+              l_verify = __fmaf_rn(alpha_check, l_verify, lo + hi);
+              m_verify = m_check;
+              if (p.fault_stage == FT_ATTN_FAULT_SOFTMAX_STATE && p.fault_bh == bh && p.fault_query == q_tile0 + row_in_tile &&
+                  p.fault_index / 64 == j * 2 + c) {
+                l_run += p.fault_value;  // test hook: the fault enters the running denominator
+              }
+              auto exceeds = [&](float actual, float expected) {
+                return fabsf(actual - expected) > __fmaf_rn(p.softmax_rel_tol, fmaxf(1.0f, fabsf(expected)), p.softmax_abs_tol);
+              };
+              const bool m_bad = m_run != m_verify && exceeds(m_run, m_verify);  // both are -inf only before the first tile
+              if (m_bad || exceeds(l_run, l_verify)) {
+                atomicAdd(&p.report->softmax_detected, 1);
+                atomicAdd(&p.report->softmax_replayed, 1);
+                m_run = m_verify;
+                l_run = l_verify;
+              }
+            }
           }
         }
         fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
@@ -523,6 +673,15 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       float actual_sum = 0.0f, actual_weighted = 0.0f;
       const int query = q_tile0 + row_in_tile;
       const bool my_fault = p.fault_stage == FT_ATTN_FAULT_OUTPUT && p.fault_bh == bh && p.fault_query == query && p.fault_index / kHalfDim == c;
+      float l_protected = 0.0f;
+      if (kProtect) {
+        // the protected denominator is the sum of the two halves' registers (fixed order: both threads hold the same bits);
+        // the exchange uses the parity of the row-maximum buffer that the last key tile did not use
+        sh.row_max[t][my_tiles & 1][c][row_in_tile] = l_run;
+        asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+        const float other_l = sh.row_max[t][my_tiles & 1][c ^ 1][row_in_tile];
+        l_protected = c == 0 ? l_run + other_l : other_l + l_run;
+      }
       if (alive) {
         tcgen05_fence_after();
         {
@@ -531,7 +690,19 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           float x[8];
           tmem_ld_32x32b_x8(x_addr, x);
           tmem_wait_ld();
-          inv_l = 1.0f / x[0];
+          float l_total = x[0];
+          if (kProtect) {
+            // The tensor core summed the FP16-rounded probabilities, the registers the unrounded ones: they agree to a
+            // fraction of the FP16 rounding step.  Beyond that the protected registers decide.
+            if (fabsf(l_total - l_protected) > 1.0e-3f * l_protected) {
+              if (c == 0) {
+                atomicAdd(&p.report->softmax_detected, 1);
+                atomicAdd(&p.report->softmax_replayed, 1);
+              }
+              l_total = l_protected;
+            }
+          }
+          inv_l = 1.0f / l_total;
           es_total = x[1] + x[2];
           ew_total = (x[3] + x[4]) * kAttnVWeightScale;
         }
@@ -619,18 +790,27 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 }
 
 cudaError_t configure_attention_split() {
-  cudaError_t err = cudaFuncSetAttribute(ft_attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<128>());
-  if (err != cudaSuccess) return err;
-  return cudaFuncSetAttribute(ft_attention_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<64>());
+  cudaError_t err = cudaFuncSetAttribute(ft_attention_split_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<128>());
+  if (err == cudaSuccess) err = cudaFuncSetAttribute(ft_attention_split_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<64>());
+  if (err == cudaSuccess) err = cudaFuncSetAttribute(ft_attention_split_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<128>());
+  if (err == cudaSuccess) err = cudaFuncSetAttribute(ft_attention_split_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<64>());
+  return err;
 }
 
 cudaError_t launch_attention_split(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k, const CUtensorMap& tmap_vt, const AttnParams& params,
                                    int batch_heads, cudaStream_t stream) {
   dim3 grid((params.seq + kQTiles * kTile - 1) / (kQTiles * kTile), batch_heads);
+  const bool protect = params.protect_softmax != 0;
   if (params.dim == 64) {
-    ft_attention_split_kernel<64><<<grid, kThreads, smem_bytes<64>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
+    if (protect) {
+      ft_attention_split_kernel<64, true><<<grid, kThreads, smem_bytes<64>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
+    } else {
+      ft_attention_split_kernel<64, false><<<grid, kThreads, smem_bytes<64>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
+    }
+  } else if (protect) {
+    ft_attention_split_kernel<128, true><<<grid, kThreads, smem_bytes<128>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
   } else {
-    ft_attention_split_kernel<128><<<grid, kThreads, smem_bytes<128>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
+    ft_attention_split_kernel<128, false><<<grid, kThreads, smem_bytes<128>(), stream>>>(tmap_q, tmap_k, tmap_vt, params);
   }
   return cudaGetLastError();
 }

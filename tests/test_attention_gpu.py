@@ -85,7 +85,7 @@ def test_score_tile_with_several_faults_is_replayed(ftg, protect_softmax):
     """Two faults in one 64x64 score tile cannot be located by the row/column intersection: the tile is recomputed on
     the CUDA cores, passes the check the second time and counts as replayed (src/ft_flash_attention_a14.cu:935-959);
     the output equals the clean one.  Patterns: two rows and two columns, one row with two columns, one column with two
-    rows; both kernels (the split-row default and the whole-row kernel that carries the softmax-stage protection)."""
+    rows; with and without the softmax-stage protection."""
     b, h, n = 1, 2, 512
     q, k, v = _qkv(b, h, n, seed=21)
     op = ftg.FtAttention(q, k, v, protect_softmax=protect_softmax)
@@ -206,8 +206,6 @@ def test_repeat_runs_are_bit_identical_and_arguments_checked(ftg):
     op.close()
     with pytest.raises(ftg.FtGemmError):
         ftg.FtAttention(q[..., :96].contiguous(), k[..., :96].contiguous(), v[..., :96].contiguous())  # D must be 64 or 128
-    with pytest.raises(ftg.FtGemmError):  # the softmax-stage protection is built for D = 128
-        ftg.FtAttention(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous(), protect_softmax=True)
 
 
 def test_config5_shape_properties(ftg):
@@ -233,10 +231,11 @@ def test_config5_shape_properties(ftg):
     op.close()
 
 
-def test_softmax_stage_protection(ftg):
+@pytest.mark.parametrize("d", [128, 64])
+def test_softmax_stage_protection(ftg, d):
     """protect_softmax adds the reference's third protected stage (a14:964-1099)."""
     b, h, n = 1, 2, 384
-    q, k, v = _qkv(b, h, n, seed=19)
+    q, k, v = _qkv(b, h, n, d, seed=19)
     plain_op = ftg.FtAttention(q, k, v)
     plain = plain_op.new_output()
     plain_op.run(plain)
@@ -248,10 +247,7 @@ def test_softmax_stage_protection(ftg):
     op.run(clean)
     rep = op.report()
     assert (rep.softmax_detected, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0)
-    # The protection changes nothing when nothing is wrong.  The two kernels round their FP16 probabilities against
-    # different exponent references (the split-row kernel moves its reference in steps of 2^8, the whole-row kernel
-    # follows the running maximum), so they agree to FP16 rounding of the probabilities, not to the last bit.
-    assert float((clean - plain).abs().max()) < 5e-4
+    assert torch.equal(clean, plain)  # the protection changes nothing when nothing is wrong
     want, _, _ = oa.forward(_np(q), _np(k), _np(v), protect_softmax=True)
     np.testing.assert_allclose(_np(clean), want, atol=2e-3, rtol=0)
     out = op.new_output()
@@ -275,10 +271,45 @@ def test_softmax_stage_protection(ftg):
     op.run(out, (ftg.FAULT_SCORE, 0, 1, 77, 200, 6.0))
     rep = op.report()
     assert (rep.score_corrected, rep.softmax_detected, rep.pv_detected) == (1, 0, 0)
-    op.run(out, (ftg.FAULT_OUTPUT, 0, 0, 10, 100, 0.5))
+    op.run(out, (ftg.FAULT_OUTPUT, 0, 0, 10, 100 % d, 0.5))
     rep = op.report()
     assert (rep.pv_corrected, rep.softmax_detected, rep.failed_rows) == (1, 0, 0)
     op.close()
+
+
+def test_whole_row_kernel_when_selected(ftg):
+    """FT_ATTENTION_KERNEL=row selects the kernel with one thread per query row (read once per process, hence the child)."""
+    import os
+    import subprocess
+    import sys
+    code = """
+import numpy as np, torch, ft_gemm_b200 as ftg
+from tests import oracle_attention as oa
+g = torch.Generator(device='cpu').manual_seed(31)
+q, k, v = (torch.randn((1, 2, 384, 128), generator=g).to(torch.float16).cuda() for _ in range(3))
+for protect in (False, True):
+    op = ftg.FtAttention(q, k, v, protect_softmax=protect)
+    clean = op.new_output(); op.run(clean); rep = op.report()
+    assert (rep.status, rep.score_detected, rep.pv_detected, rep.failed_rows, rep.softmax_detected) == (0, 0, 0, 0, 0)
+    truth = oa.truth_fp64(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    np.testing.assert_allclose(clean.cpu().numpy(), truth, atol=4e-3, rtol=0)
+    out = op.new_output(); op.run(out, (ftg.FAULT_SCORE, 0, 1, 77, 200, 6.0)); rep = op.report()
+    assert (rep.score_detected, rep.score_corrected) == (1, 1)
+    assert float((out - clean).abs().max()) < 5e-4
+    op.run(out, (ftg.FAULT_SCORE, 0, 0, 70, 200, 8.0, 100, 230, -5.0)); rep = op.report()  # two faults in one tile
+    assert (rep.score_detected, rep.score_corrected, rep.score_replayed, rep.score_uncorrected) == (1, 0, 1, 0)
+    assert float((out - clean).abs().max()) < 5e-4
+    if protect:
+        op.run(out, (ftg.FAULT_SOFTMAX, 0, 1, 5, 9, 0.25)); rep = op.report()
+        assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 1, 0)
+        assert torch.equal(out, clean)
+    op.close()
+print('row kernel ok')
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, FT_ATTENTION_KERNEL="row", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    done = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and "row kernel ok" in done.stdout, done.stdout[-2000:] + done.stderr[-2000:]
 
 
 @pytest.mark.parametrize("n", [128, 384, 512])
