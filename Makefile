@@ -52,6 +52,21 @@ build/gemm_softmax_abft: $(CSRC)/cli/gemm_softmax_abft.cpp $(CSRC)/cli/cli_commo
 build/cublaslt_fp8_bench: $(CSRC)/cli/cublaslt_fp8_bench.cpp $(CSRC)/cli/cli_common.h $(HDRS) $(LIB)
 	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -Iinclude -o $@ $< -Lft_gemm_b200/lib -lft_gemm_b200 -lcublasLt -lcublas -Xlinker -rpath -Xlinker '$$ORIGIN/../ft_gemm_b200/lib'
 
+# Diagnostic build of the attention kernel with its timeline trace compiled in (FT_TRACE in ft_attention_split.cu); the
+# product library is not touched:  make trace && ./build/trace/ft_flash_attention --batch 4 --heads 32 --sequence 4096 --trace
+TRACE_OBJS := $(filter-out build/obj/ft_attention_split.o,$(OBJS)) build/trace/ft_attention_split.o
+trace: build/trace/ft_flash_attention
+
+build/trace/ft_attention_split.o: $(CSRC)/ft_attention_split.cu $(HDRS)
+	@mkdir -p build/trace
+	$(NVCC) $(NVCCFLAGS) -DFT_ATTENTION_TRACE -c -o $@ $<
+
+build/trace/libft_gemm_b200.so: $(TRACE_OBJS)
+	$(NVCC) $(ARCH) -shared -o $@ $(TRACE_OBJS)
+
+build/trace/ft_flash_attention: $(CSRC)/cli/ft_flash_attention.cpp $(CSRC)/cli/cli_common.h $(HDRS) build/trace/libft_gemm_b200.so
+	$(NVCC) -O2 -std=c++17 -Wno-deprecated-gpu-targets -DFT_ATTENTION_TRACE -Iinclude -o $@ $< -Lbuild/trace -lft_gemm_b200 -Xlinker -rpath -Xlinker '$$ORIGIN'
+
 oracle:
 	$(MAKE) -C oracle
 
@@ -63,4 +78,4 @@ fault_campaign: build/fault_campaign
 clean:
 	rm -rf build/obj
 
-.PHONY: all lib cli oracle fault_campaign clean
+.PHONY: trace all lib cli oracle fault_campaign clean

@@ -19,6 +19,56 @@ static float half_bits_to_float(uint16_t h) {
   return __half2float(__half(raw));
 }
 
+#ifdef FT_ATTENTION_TRACE
+// Exported only by a library built with -DFT_ATTENTION_TRACE (`make trace`): the timeline table of one CTA of the last
+// launch, [18 actors][64 slots][8 events] cycle counts (layout described beside FT_TRACE in ft_attention_split.cu).
+extern "C" int ft_attention_trace_read(long long* out, int count);
+
+static void print_phase_trace(int key_tiles) {
+  constexpr int kActors = 18, kSlots = 64, kEvents = 8;
+  std::vector<long long> table(static_cast<size_t>(kActors) * kSlots * kEvents);
+  if (ft_attention_trace_read(table.data(), static_cast<int>(table.size())) != 0) {
+    std::printf("phase_trace: unavailable\n");
+    return;
+  }
+  auto at = [&](int actor, int slot, int event) { return table[(static_cast<size_t>(actor) * kSlots + slot) * kEvents + event]; };
+  const int first = 2, last = std::min(key_tiles, kSlots) - 2;  // steady state: skip the first and the last two key tiles
+  if (last <= first) {
+    std::printf("phase_trace: needs at least 6 key tiles\n");
+    return;
+  }
+  const char* names[8] = {"wait_for_scores", "read_scores_and_column_sums", "row_sums_and_maximum", "band_barrier", "decision_and_tile_barrier",
+                          "maximum_exchange_and_wait_for_pv", "exponentials_and_p_store", "hand_off_and_loop_head"};
+  double sums[8] = {0, 0, 0, 0, 0, 0, 0, 0}, period = 0.0, lag = 0.0;
+  int samples = 0;
+  for (int w = 0; w < 16; ++w) {
+    for (int j = first; j < last; ++j) {
+      for (int e = 0; e < 7; ++e) sums[e] += static_cast<double>(at(w, j, e + 1) - at(w, j, e));
+      sums[7] += static_cast<double>(at(w, j + 1, 0) - at(w, j, 7));
+      period += static_cast<double>(at(w, j + 1, 0) - at(w, j, 0));
+      ++samples;
+    }
+  }
+  for (int j = first; j < last; ++j) lag += static_cast<double>(at(8, j, 1) - at(0, j, 1));
+  std::printf("phase_trace_cycles_per_key_tile (one CTA, mean over 16 softmax warps and key tiles %d..%d)\n", first, last - 1);
+  for (int e = 0; e < 8; ++e) std::printf("  %s: %.0f\n", names[e], sums[e] / samples);
+  std::printf("  period: %.0f\n", period / samples);
+  std::printf("  tile_b_behind_tile_a: %.0f\n", lag / (last - first));
+  double qk_wait_k = 0, qk_wait_s = 0, qk_issue = 0, pv_wait_p = 0, pv_issue = 0;
+  int uses = 0;
+  for (int u = 2 * first; u < 2 * last; ++u) {
+    qk_wait_k += static_cast<double>(at(16, u, 1) - at(16, u, 0));
+    qk_wait_s += static_cast<double>(at(16, u, 2) - at(16, u, 1));
+    qk_issue += static_cast<double>(at(16, u, 3) - at(16, u, 2));
+    pv_wait_p += static_cast<double>(at(17, u, 2) - at(17, u, 1));
+    pv_issue += static_cast<double>(at(17, u, 3) - at(17, u, 2));
+    ++uses;
+  }
+  std::printf("  score_issuer_per_product: wait_for_k %.0f, wait_for_score_buffer %.0f, issue %.0f\n", qk_wait_k / uses, qk_wait_s / uses, qk_issue / uses);
+  std::printf("  pv_issuer_per_product: wait_for_p %.0f, issue %.0f\n", pv_wait_p / uses, pv_issue / uses);
+}
+#endif
+
 int main(int argc, char** argv) {
   ArgReader args{argc, argv};
   int batch = args.get_int("--batch", 1), heads = args.get_int("--heads", 2), sequence = args.get_int("--sequence", 128);
@@ -212,6 +262,9 @@ int main(int argc, char** argv) {
   std::printf("pv_corrected: %d\n", report.pv_corrected);
   std::printf("failed_rows: %d\n", report.failed_rows);
   std::printf("verified_rows: %zu\n", rows_to_check);
+#ifdef FT_ATTENTION_TRACE
+  if (args.has_flag("--trace")) print_phase_trace(sequence / 128);
+#endif
   std::printf("max_absolute_error: %.6e\n", max_absolute_error);
   std::printf("max_tolerance_ratio: %.6e\n", max_tolerance_ratio);
   std::printf("mismatches: %d\n", mismatches);

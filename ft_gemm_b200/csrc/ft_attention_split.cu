@@ -44,6 +44,27 @@
 
 namespace ftg {
 
+// Optional timeline of one CTA (library built with -DFT_ATTENTION_TRACE, `make trace`): lane 0 of every softmax warp and
+// the two MMA issuer threads store clock64() at fixed points of each key tile; ft_attention_trace_read copies the table
+// out.  Without the flag the macro is empty and the kernel is unchanged.
+//   actors 0..15  softmax warps (tile A: 0-7, tile B: 8-15; key half = (actor / 4) % 2), slot = key tile, events:
+//                 0 starts waiting for S, 1 has S, 2 S handed back, 3 before / 4 after the band barrier,
+//                 5 after the tile barrier, 6 before the exponentials, 7 P handed to the PV issuer
+//   actor 16      score-MMA issuer, slot = use of the S buffer: 0 loop top, 1 has K, 2 has the S buffer, 3 issued
+//   actor 17      PV-MMA issuer, slot = 2 * key tile + query tile: 0 loop top, 1 has V, 2 has P, 3 issued
+#ifdef FT_ATTENTION_TRACE
+constexpr int kTraceActors = 18, kTraceSlots = 64, kTraceEvents = 8;
+__device__ long long g_attention_trace[kTraceActors * kTraceSlots * kTraceEvents];
+#define FT_TRACE(actor, slot, event)                                                                                   \
+  do {                                                                                                                 \
+    if (traced && (slot) < kTraceSlots) g_attention_trace[((actor) * kTraceSlots + (slot)) * kTraceEvents + (event)] = clock64(); \
+  } while (0)
+#else
+#define FT_TRACE(actor, slot, event) \
+  do {                               \
+  } while (0)
+#endif
+
 namespace {
 
 constexpr int kTile = 128;             // queries per tile, keys per tile; the head dimension kDim is 128 or 64
@@ -235,6 +256,10 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   const int lane = threadIdx.x & 31;
   const int group = warp >> 2;  // 0: producer + MMA; 1..4: softmax of (tile, key half) = (A,0), (A,1), (B,0), (B,1)
   const int bh = blockIdx.y;
+#ifdef FT_ATTENTION_TRACE
+  // one CTA in the middle of the grid; of a softmax warp its lane 0 (in warpgroup 0 only the elected threads reach a trace point)
+  const bool traced = blockIdx.x == gridDim.x / 2 && blockIdx.y == gridDim.y / 2 && (threadIdx.x < 128 || (threadIdx.x & 31) == 0);
+#endif
   // causal CTAs get longer towards the end of the sequence: the longest are scheduled first
   const int q_block = p.causal != 0 ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
   const int q0 = q_block * kQTiles * kTile;
@@ -325,11 +350,14 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         int k_waited = -1;
         uint32_t uses = 0;
         while (alive && j < cta_tiles) {
+          FT_TRACE(16, uses, 0);
           if (k_waited != j) {
             if (!mbar_wait_bounded(&sh.k_full, j & 1, abort_flag, kTimeoutNs)) break;
             k_waited = j;
           }
+          FT_TRACE(16, uses, 1);
           if (uses > 0 && !mbar_wait_bounded(&sh.s_free, (uses - 1) & 1, abort_flag, kTimeoutNs)) break;
+          FT_TRACE(16, uses, 2);
           tcgen05_fence_after();
 #pragma unroll
           for (int kk = 0; kk < kDim / 16; ++kk) {
@@ -338,6 +366,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             umma_f16(tmem_base + kTmemS, da, db, idesc_s, kk != 0 ? 1u : 0u);
           }
           umma_commit(&sh.s_full[t]);
+          FT_TRACE(16, uses, 3);
           const int before = j;
           advance(j, t);
           if (j != before) umma_commit(&sh.k_empty);  // that was the last product that reads K_j
@@ -347,11 +376,14 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         constexpr uint32_t idesc_o = make_idesc_f16_f32(kTile, kVRows);  // O and its checksum columns: 128 queries x (kDim + 16)
         int v_waited = -1;
         while (j < cta_tiles) {
+          FT_TRACE(17, 2 * j + t, 0);
           if (v_waited != j) {
             if (!mbar_wait_bounded(&sh.v_full, j & 1, abort_flag, kTimeoutNs)) break;
             v_waited = j;
           }
+          FT_TRACE(17, 2 * j + t, 1);
           if (!mbar_wait_bounded(&sh.p_full[t], j & 1, abort_flag, kTimeoutNs)) break;
+          FT_TRACE(17, 2 * j + t, 2);
           tcgen05_fence_after();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -360,6 +392,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             umma_f16(tmem_base + kTmemO + t * kOCols, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
           }
           umma_commit(&sh.p_empty[t]);
+          FT_TRACE(17, 2 * j + t, 3);
           const int before = j;
           advance(j, t);
           if (j != before) umma_commit(&sh.v_empty);  // that was the last product that reads V_j
@@ -417,12 +450,14 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         cp_async_4(&sh.row_expect[t][c][pair][0][r_local], p.expected_rows + cache + r_local);  // read back by this thread only
         cp_async_4(&sh.row_expect[t][c][pair][1][r_local], p.row_scales + cache + r_local);
         cp_async_commit();
+        FT_TRACE(warp - 4, j, 0);
         if (!warp_wait(&sh.s_full[t], j & 1, abort_flag)) {
           alive = false;
           owed_pair_from = owed_tile_from = j;
           break;
         }
         tcgen05_fence_after();
+        FT_TRACE(warp - 4, j, 1);
 
         // test hook: the fault enters the accumulator itself, before any checksum
         if (p.fault_stage == FT_ATTN_FAULT_SCORE && p.fault_bh == bh) {  // uniform over the CTA
@@ -443,11 +478,14 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         tmem_wait_ld();
         tcgen05_fence_before();
         mbar_arrive(&sh.s_free);  // the buffer can take the next score product (the other query tile's)
+        FT_TRACE(warp - 4, j, 2);
         cp_async_wait_all();  // this lane's pieces of the cached checksums have landed; the band barrier below publishes the column side
         abft_tile_rows(v, lane, half, scratch, sh.row_expect[t][c][pair][0][r_local], sh.row_expect[t][c][pair][1][r_local],
                        p.score_abs_tol, p.score_rel_tol, max_ratio);
         float local_max = masked_row_max(v, diagonal, c * 64, key_limit);
+        FT_TRACE(warp - 4, j, 3);
         asm volatile("bar.sync %0, 64;" ::"r"(bar_pair) : "memory");
+        FT_TRACE(warp - 4, j, 4);
         {
           const float exp_col0 = sh.col_expect[t][c][pair][0][lane], exp_col1 = sh.col_expect[t][c][pair][0][32 + lane];
           const float scale_col0 = sh.col_expect[t][c][pair][1][lane], scale_col1 = sh.col_expect[t][c][pair][1][32 + lane];
@@ -506,6 +544,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         // ---- the two halves of the row exchange their maxima
         sh.row_max[t][buf][c][row_in_tile] = local_max;
         asm volatile("bar.sync %0, 256;" ::"r"(bar_tile) : "memory");
+        FT_TRACE(warp - 4, j, 5);
         const float row_max = fmaxf(local_max, sh.row_max[t][buf][c ^ 1][row_in_tile]);
 
         // ---- online softmax state (log2 domain); identical in both threads of the row.  The reference point of the
@@ -567,6 +606,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             tmem_wait_st();
           }
         }
+        FT_TRACE(warp - 4, j, 6);
         // ---- probabilities of this half: FP16 P slab for the MMA (which also forms l and the expected projections)
         {
           if (diagonal) {  // exp2(-inf) = 0: a masked key gets probability zero
@@ -659,6 +699,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
         tcgen05_fence_before();
         mbar_arrive(&sh.p_full[t]);
+        FT_TRACE(warp - 4, j, 7);
       }
       // only after an abandoned wait: the named barriers the other warps of the band / tile still count on
       for (int jj = min(owed_pair_from, owed_tile_from); jj < my_tiles; ++jj) {
@@ -816,3 +857,12 @@ cudaError_t launch_attention_split(const CUtensorMap& tmap_q, const CUtensorMap&
 }
 
 }  // namespace ftg
+
+#ifdef FT_ATTENTION_TRACE
+// Copies the timeline table of the last launch to the host: [actor][slot][event] cycle counts (see FT_TRACE above).
+extern "C" int ft_attention_trace_read(long long* out, int count) {
+  const int total = ftg::kTraceActors * ftg::kTraceSlots * ftg::kTraceEvents;
+  if (out == nullptr || count < total) return total;
+  return cudaMemcpyFromSymbol(out, ftg::g_attention_trace, sizeof(long long) * total) == cudaSuccess ? 0 : -1;
+}
+#endif
