@@ -431,6 +431,18 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const int my_tiles = tiles_of(t);
       // when a wait is abandoned: the first key tile whose band barrier / tile barrier this warp still owes the others
       int owed_pair_from = my_tiles, owed_tile_from = my_tiles;
+      // Cached expected checksums of the band's 64x64 tile of key tile jj.  They travel by asynchronous copy straight into
+      // shared memory -- the band's first warp brings the column expectations, its second the column scales, two adjacent
+      // columns per lane, and every thread the pair of its own row -- so that they cost no register while the scores are
+      // worked on and their latency is over when they are needed.
+      auto prefetch_checksums = [&](int jj) {
+        const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + jj * 2 + c) * 64;
+        cp_async_8(&sh.col_expect[t][c][pair][half][2 * lane], (half == 0 ? p.expected_cols : p.col_scales) + cache + 2 * lane);
+        cp_async_4(&sh.row_expect[t][c][pair][0][r_local], p.expected_rows + cache + r_local);  // read back by this thread only
+        cp_async_4(&sh.row_expect[t][c][pair][1][r_local], p.row_scales + cache + r_local);
+        cp_async_commit();
+      };
+      if (my_tiles > 0) prefetch_checksums(0);
       for (int j = 0; j < my_tiles; ++j) {
         const int buf = j & 1;
         // Keys of this tile the row may attend to are those with local index <= key_limit: all 128, up to the query in
@@ -440,16 +452,8 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         if (causal && j == first_qtile + t) key_limit = row_in_tile;
         if ((j + 1) * kTile > p.valid_seq) key_limit = min(key_limit, p.valid_seq - 1 - j * kTile);
         const bool diagonal = key_limit < kTile - 1;  // some keys of this tile are masked for this row
-        // Cached expected checksums of this thread's 64x64 tile, asked for before the wait.  The row's pair goes to
-        // registers.  The column side (64 expectations + 64 scales per band) travels by asynchronous copy straight into
-        // shared memory -- the band's first warp brings the expectations, its second the scales, two adjacent columns per
-        // lane -- so that it costs no register while the scores are worked on and its latency is over when the partner
-        // exchange needs it.
-        const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
-        cp_async_8(&sh.col_expect[t][c][pair][half][2 * lane], (half == 0 ? p.expected_cols : p.col_scales) + cache + 2 * lane);
-        cp_async_4(&sh.row_expect[t][c][pair][0][r_local], p.expected_rows + cache + r_local);  // read back by this thread only
-        cp_async_4(&sh.row_expect[t][c][pair][1][r_local], p.row_scales + cache + r_local);
-        cp_async_commit();
+        // (asked for by prefetch_checksums: for the first tile before the loop, for the others while the previous tile's
+        // probabilities drain into shared memory)
         FT_TRACE(warp - 4, j, 0);
         if (!warp_wait(&sh.s_full[t], j & 1, abort_flag)) {
           alive = false;
@@ -504,6 +508,7 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               }
             } else {
               // The fault cannot be located: recompute the band's 64 x 64 scores without the tensor core and check again.
+              const size_t cache = head_cache + (static_cast<size_t>(q_band) * tile_cols + j * 2 + c) * 64;
               const __half* q_row = static_cast<const __half*>(p.q) + (static_cast<size_t>(row_base) + q_tile0 + row_in_tile) * kDim;
               const __half* k_tile = static_cast<const __half*>(p.k) + (static_cast<size_t>(row_base) + j * kTile + c * 64) * kDim;
               float rv[64];
@@ -696,6 +701,9 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             }
           }
         }
+        // The band's cached checksums were last read before this tile's 256-thread barrier: the next tile's can be asked
+        // for now, while the stores above drain.
+        if (j + 1 < my_tiles) prefetch_checksums(j + 1);
         fence_proxy_async_shared();  // P written with st.shared must be visible to the MMA's reads
         tcgen05_fence_before();
         mbar_arrive(&sh.p_full[t]);
