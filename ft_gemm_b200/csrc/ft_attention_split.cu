@@ -244,7 +244,9 @@ ft_attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   constexpr uint32_t kOCols = kDim + kAttnVExtra;  // TMEM columns of one output accumulator
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // aligned to 1024 bytes by pointer arithmetic on the shared array itself, so that the compiler keeps every access below
+  // in the shared address space (32-bit addresses, LDS / STS) instead of falling back to generic 64-bit addressing
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* smem_q = smem;                      // 2 query tiles
   uint8_t* smem_k = smem + 2 * kTileBytes;     // 1 stage
   uint8_t* smem_v = smem + 3 * kTileBytes;     // 1 stage: two slabs of kVRows x 64 keys
