@@ -52,7 +52,7 @@ typedef struct {
   float softmax_rel_tol; /* default 2e-5 */
   int protect_softmax;   /* 0 (default): score and output stages only; 1: also the reference's softmax-stage
                             protection (verifier copies of the exponent reference and of every probability, moment
-                            check with location, duplicate of the running state; about 1.6x the time) */
+                            check with location, duplicate of the running state; about 1.5x the time) */
   int causal;            /* 0 (default): every key; 1: key <= query only (src/ft_flash_attention_a14.cu:130, 708, 836):
                             key tiles beyond the diagonal are skipped, the diagonal tile is verified unmasked and
                             masked afterwards; score / softmax faults must then have index <= query (a14:278) */
