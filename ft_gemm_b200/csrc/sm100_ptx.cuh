@@ -306,7 +306,10 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
   return remote;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  // Default semantics (release at CTA scope).  A cluster-scope release would first wait for every global store the
+  // thread has in flight, which in an epilogue is the whole previous column group; what this arrival has to order are
+  // the thread's tensor-memory reads, and those are complete (tcgen05.wait::ld) and fenced before it.
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Tile load of a CTA pair member: data lands in THIS CTA's shared memory, the
 // transaction bytes are counted on the barrier at cluster address `bar_cluster`
