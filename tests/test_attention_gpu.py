@@ -391,6 +391,43 @@ def test_head_dim_64(ftg, causal, exact_prepare):
     op.close()
 
 
+@pytest.mark.parametrize("n,d,causal", [(384, 64, True), (333, 64, False), (300, 128, True)])
+def test_softmax_stage_protection_with_masks(ftg, n, d, causal):
+    """The protected forward on causal and padded tiles (masked keys have probability zero in both copies) and with both head
+    dimensions: clean runs equal the unprotected ones bit for bit; probability and state faults are detected and repaired,
+    on the diagonal tile as well."""
+    b, h = 1, 2
+    q, k, v = _qkv(b, h, n, d=d, seed=57 + n)
+    plain_op = ftg.FtAttention(q, k, v, causal=causal)
+    plain = plain_op.new_output()
+    plain_op.run(plain)
+    plain_op.close()
+    op = ftg.FtAttention(q, k, v, causal=causal, protect_softmax=True)
+    clean = op.new_output()
+    op.run(clean)
+    rep = op.report()
+    assert (rep.status, rep.softmax_detected, rep.score_detected, rep.pv_detected, rep.failed_rows) == (0, 0, 0, 0, 0)
+    assert torch.equal(clean, plain)
+    np.testing.assert_allclose(_np(clean), oa.truth_fp64(_np(q), _np(k), _np(v), causal=causal), atol=4e-3, rtol=0)
+    out = op.new_output()
+    last = n - 1
+    for head, query, key, value in [(0, last, last, 0.5), (1, 130, 129, 0.25), (0, 70, 3, 1.0), (1, last, 128, 0.125)]:
+        fault = (ftg.FAULT_SOFTMAX, 0, head, query, key, value)  # key <= query: valid under the causal mask too
+        op.run(out, fault)
+        rep = op.report()
+        _, stats, _ = oa.forward(_np(q), _np(k), _np(v), causal=causal, protect_softmax=True, fault=fault)
+        assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 1, 0) == \
+               (stats.softmax_detected, stats.softmax_corrected, stats.softmax_replayed)
+        assert (rep.pv_detected, rep.failed_rows, rep.score_detected) == (0, 0, 0)
+        assert torch.equal(out, clean)
+    fault = (ftg.FAULT_SOFTMAX_STATE, 0, 1, last, 5, 0.75)
+    op.run(out, fault)
+    rep = op.report()
+    assert (rep.softmax_detected, rep.softmax_corrected, rep.softmax_replayed) == (1, 0, 1)
+    assert torch.equal(out, clean)
+    op.close()
+
+
 @pytest.mark.parametrize("n,d,causal", [(200, 128, False), (333, 64, True), (1, 64, False), (129, 128, True), (2100, 128, False),
                                         (77, 128, True)])
 def test_sequence_lengths_that_are_not_whole_tiles(ftg, n, d, causal):
